@@ -1,0 +1,333 @@
+"""Benchmark of the NVFP4 MoE layer (Gemma-4 26B-A4B shapes) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one pass of the layer over one batch: router projection (library GEMM,
+as in the reference), route_128_top8, route sort, NVFP4 quantise, grouped w13 GEMM,
+GeGLU+requantise, grouped w2 GEMM, weighted reduce.  Workload at every N: the
+prefill configuration, 4096 tokens per GPU with a per-expert router bias ~N(0, 0.5).
+Prints one JSON line (rank 0).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+TOKENS = 4096
+HIDDEN, EXPERTS, TOP_K, INTER = 2816, 128, 8, 704
+FLOP_PER_TOKEN = TOP_K * (2 * 2 * INTER * HIDDEN + 2 * HIDDEN * INTER)  # 95 158 272
+W13_FLOP_PER_TOKEN = TOP_K * 2 * 2 * INTER * HIDDEN                      # 63 438 848
+LAYER_WEIGHT_BYTES = 428212224
+NOMINAL_FP4_TFLOPS = 9000.0
+WORKLOAD = "prefill_4096_tokens_router_bias_N(0,0.5)"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, sm_max, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.file:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                sm_max.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.file.name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(sm_max) if sm_max else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def build_layer(device, rank):
+    import torch
+    from gevva_b200.synthetic import SyntheticLayer
+    layer = SyntheticLayer(seed=rank, max_tokens=TOKENS, device=device, bias_std=0.5)
+    x = layer.inputs(TOKENS, seed=1000 + rank)
+    layer.calibrate(x)
+    layer.bias_row = layer.bias.to(torch.bfloat16)
+    return layer, x
+
+
+def layer_step(layer, x, out, weights, ids):
+    """The timed unit: router projection with bias (one library GEMM) + our kernels."""
+    import torch
+    import gevva_b200
+    logits = torch.addmm(layer.bias_row, x, layer.router_w.t())
+    gevva_b200.route_128_top8(logits, layer.expert_scale, weights=weights, ids=ids)
+    layer.runner.launch_batch(x, ids, weights, out, x.shape[0])
+
+
+def oracle_sample(rank_seed, tokens):
+    """Synthetic inputs for the CPU legs, generated without a GPU."""
+    import numpy as np
+    import torch
+    from tests.oracle_api import Oracle
+    oracle = Oracle()
+    gen = torch.Generator().manual_seed(rank_seed)
+    hw = {k: [] for k in ("w13", "w13_sf", "g13", "w2", "w2_sf", "g2")}
+    for _ in range(EXPERTS):
+        w13 = (torch.randn((2 * INTER, HIDDEN), generator=gen) * 0.02).numpy()
+        c, s, g = oracle.pack_weight(w13)
+        hw["w13"].append(c), hw["w13_sf"].append(s), hw["g13"].append(g)
+        w2 = (torch.randn((HIDDEN, INTER), generator=gen) * 0.02).numpy()
+        c, s, g = oracle.pack_weight(w2)
+        hw["w2"].append(c), hw["w2_sf"].append(s), hw["g2"].append(g)
+    x = torch.randn((tokens, HIDDEN), generator=gen).to(torch.bfloat16)
+    router = (torch.randn((EXPERTS, HIDDEN), generator=gen) * 0.02).to(torch.bfloat16)
+    bias = torch.randn(EXPERTS, generator=gen) * 0.5
+    logits = (x.float() @ router.float().t() + bias).to(torch.bfloat16)
+
+    def bits(t):
+        return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+    s1 = float(x.float().abs().max()) / (6 * 448)
+    s2 = 16.0 / (6 * 448)
+    weights = dict(
+        w13=np.stack(hw["w13"]), w13_sf=np.stack(hw["w13_sf"]), w2=np.stack(hw["w2"]),
+        w2_sf=np.stack(hw["w2_sf"]),
+        alpha1=(np.array(hw["g13"], np.float32) * np.float32(s1)),
+        alpha2=(np.array(hw["g2"], np.float32) * np.float32(s2)),
+        in_scale_q1=np.full(EXPERTS, 1 / s1, np.float32),
+        in_scale_q2=np.full(EXPERTS, 1 / s2, np.float32))
+    scale = bits(torch.ones(EXPERTS, dtype=torch.bfloat16))
+    return oracle, bits(x), bits(logits), scale, weights
+
+
+def time_oracle(oracle, x_bits, logit_bits, scale_bits, weights, repeats):
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        rw, ids = oracle.route(logit_bits, scale_bits)
+        oracle.moe_layer(x_bits, ids, rw, weights)
+        times.append(time.perf_counter() - t0)
+    return times
+
+
+def run_reference(args):
+    """The reference has no CPU path and its GPU kernels are SM120-only, so this arm
+    times the CPU oracle (a restatement: dequantise to fp32, then matmul) with all the
+    host threads OpenMP gives it, on a bounded sample of the same workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = 256
+    oracle, x_bits, logit_bits, scale_bits, weights = oracle_sample(0, sample)
+    threads = oracle.lib.gvo_threads()
+    time_oracle(oracle, x_bits, logit_bits, scale_bits, weights, max(1, min(args.warmup, 1)))
+    times = time_oracle(oracle, x_bits, logit_bits, scale_bits, weights, args.steps)
+    per_step = sum(times) / len(times)
+    value = sample / per_step
+    line = {
+        "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "tokens_per_step": sample,
+                   "note": "CPU oracle port; each step is a 256-token sample of the 4096-token batch"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": f"{sample} of {TOKENS} tokens, all 128 experts' weights"},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    import gevva_b200
+    from gevva_b200 import runtime as rt
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    layer, x = build_layer(device, rank)
+    out = torch.empty_like(x)
+    weights = torch.empty((TOKENS, TOP_K), dtype=torch.float32, device=device)
+    ids = torch.empty((TOKENS, TOP_K), dtype=torch.int32, device=device)
+
+    for _ in range(max(args.warmup, 3)):
+        layer_step(layer, x, out, weights, ids)
+    layer.runner.check()
+
+    # ---- device-resident throughput ("value") -----------------------------------
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        layer_step(layer, x, out, weights, ids)
+    stop.record()
+    barrier()
+    clocks = sampler.stop()
+    elapsed_ms = start.elapsed_time(stop)
+    layer.runner.check()
+
+    # ---- end to end through host buffers ("e2e") -------------------------------
+    host_in = x.cpu().pin_memory()
+    host_out = torch.empty_like(host_in).pin_memory()
+    dev_in = torch.empty_like(x)
+    for _ in range(2):
+        dev_in.copy_(host_in, non_blocking=True)
+        layer_step(layer, dev_in, out, weights, ids)
+        host_out.copy_(out, non_blocking=True)
+    barrier()
+    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record()
+    for _ in range(args.steps):
+        dev_in.copy_(host_in, non_blocking=True)
+        layer_step(layer, dev_in, out, weights, ids)
+        host_out.copy_(out, non_blocking=True)
+    e_stop.record()
+    barrier()
+    e2e_ms = e_start.elapsed_time(e_stop)
+
+    # ---- dominant kernel (grouped w13 GEMM) timed alone inside full steps --------------
+    g0 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    g1 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    h0 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    h1 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    runner = layer.runner
+    for i in range(args.steps):
+        logits = torch.addmm(layer.bias_row, x, layer.router_w.t())
+        gevva_b200.route_128_top8(logits, layer.expert_scale, weights=weights, ids=ids)
+        runner.launch_stages(rt.STAGE_SORT | rt.STAGE_QUANTIZE, TOKENS, input=x, expert_ids=ids)
+        g0[i].record()
+        runner.launch_stages(rt.STAGE_W13, TOKENS)
+        g1[i].record()
+        runner.launch_stages(rt.STAGE_GEGLU, TOKENS)
+        h0[i].record()
+        runner.launch_stages(rt.STAGE_W2, TOKENS)
+        h1[i].record()
+        runner.launch_stages(rt.STAGE_REDUCE, TOKENS, route_weights=weights, output=out)
+    torch.cuda.synchronize()
+    w13_ms = sum(a.elapsed_time(b) for a, b in zip(g0, g1)) / args.steps
+    w2_ms = sum(a.elapsed_time(b) for a, b in zip(h0, h1)) / args.steps
+
+    times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms = float(times[0]), float(times[1])
+
+    if rank == 0:
+        peaks, peak_kind = measured_peaks()
+        fp4_peak = 4.0 * float(peaks["bf16_tflops"])
+        achieved = W13_FLOP_PER_TOKEN * TOKENS / (w13_ms * 1e-3) / 1e12
+        total_tokens = TOKENS * world * args.steps
+        value = total_tokens / (elapsed_ms * 1e-3)
+        launches_per_step = 9  # route, 3 sort kernels, quantise, w13, geglu, w2, reduce
+        line = {
+            "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate)",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "tokens_per_gpu": TOKENS, "experts": EXPERTS,
+                       "top_k": TOP_K, "hidden": HIDDEN, "expert_width": INTER,
+                       "parallelism": "single GPU" if world == 1 else f"{world} data-parallel replicas",
+                       "l2": "inputs larger than L2: 428 MB of expert weights stream every step"},
+            "layer_tflops": FLOP_PER_TOKEN * TOKENS / (elapsed_ms / args.steps * 1e-3) / 1e12,
+            "roofline": {"bound": "tensor", "kernel": "grouped_nvfp4_gemm_kernel (w13)",
+                         "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s",
+                         "frac": achieved / fp4_peak, "traffic": None,
+                         "peak_source": f"4 x bf16_tflops of MEASURED_PEAKS.json ({peak_kind}); "
+                                        "no FP4 entry exists",
+                         "frac_of_nominal_9000": achieved / NOMINAL_FP4_TFLOPS,
+                         "kernel_ms": w13_ms, "w2_kernel_ms": w2_ms,
+                         "w2_tflops": (FLOP_PER_TOKEN - W13_FLOP_PER_TOKEN) * TOKENS / (w2_ms * 1e-3) / 1e12},
+            "e2e": {"value": total_tokens / (e2e_ms * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": TOKENS * HIDDEN * 2, "d2h_bytes_per_step": TOKENS * HIDDEN * 2},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            sample = 128
+            oracle, x_bits, logit_bits, scale_bits, hw = oracle_sample(0, sample)
+            t = time_oracle(oracle, x_bits, logit_bits, scale_bits, hw, 2)[-1]
+            line["cpu_baseline"] = {
+                "value": sample / t, "unit": "tokens/s", "cores": oracle.lib.gvo_threads(),
+                "kind": "port",
+                "sample": f"{sample} of {TOKENS} tokens through the CPU oracle, all 128 experts' weights"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=50)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

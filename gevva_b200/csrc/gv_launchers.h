@@ -1,0 +1,69 @@
+// Host-callable launchers of the MoE kernels; every one only enqueues on `stream`.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace gv {
+
+// Device-resident description of one launch's routing, written by the route sort
+// and read by every later stage without a host round trip.
+struct RoutePlan {
+  int* sorted_experts;     // [R]   expert of sorted row
+  int* sorted_routes;      // [R]   original route (8*token+k) of sorted row
+  int* inverse_routes;     // [R]   sorted row of original route
+  int* expert_offsets;     // [129] first sorted row of each expert, [128] = R
+  int* scale_row_offsets;  // [129] first scale-factor row (128-row padded) of each expert
+  int* tile_expert;        // [R/128 + 128] expert of each 128-row tile
+  int* num_m_tiles;        // [1]
+  int* chunk_hist;         // [ceil(R/1024) * 128] scratch of the multi-block sort
+  int* status;             // [1]   device status word (gv::Status)
+};
+
+void launch_route(const void* logits_bf16, int ld, const void* expert_scale_bf16, float* weights,
+                  int* ids, int tokens, const float* activation_scales,
+                  const float* projection_weight_scale, cudaStream_t stream);
+
+void launch_route_sort(const int* expert_ids, int routes, const RoutePlan& plan,
+                       cudaStream_t stream);
+
+// bf16 [tokens, 2816] -> codes [R, 1408] (sorted order) + swizzled scale bytes.
+void launch_quantize_input(const void* input_bf16, const int* expert_ids, const float* in_scale_q,
+                           const RoutePlan& plan, int tokens, uint8_t* packed, uint8_t* scales,
+                           cudaStream_t stream);
+
+// bf16 [R, 1408] ([up;gate]) -> codes [R, 352] + swizzled scale bytes.
+void launch_geglu_quantize(const void* fused_bf16, const float* in_scale_q, const RoutePlan& plan,
+                           int routes, uint8_t* packed, uint8_t* scales, cudaStream_t stream);
+
+void launch_reduce_routes(const void* routed_bf16, const float* route_weights,
+                          const int* inverse_routes, int tokens, void* output_bf16,
+                          cudaStream_t stream);
+
+// Grouped NVFP4 GEMM: out[r, n] = bf16(alpha[e] * sum_k A[r,k] B[e,n,k]).
+struct GemmOperands {
+  CUtensorMap map_a;        // [row capacity, K/2] bytes, box 128 x 128 B, 128B swizzle
+  CUtensorMap map_b;        // [128*N, K/2] bytes, same box
+  const uint8_t* a_scales;  // activation scale regions
+  const uint8_t* b_scales;  // [128, N, K/16] swizzled per expert
+  const float* alpha;       // [128]
+  void* out;                // bf16 [row capacity, N]
+  int n_out;                // N: 1408 or 2816
+  int k_in;                 // K: 2816 or 704
+};
+
+void launch_grouped_gemm(const GemmOperands& op, const RoutePlan& plan, int sm_count,
+                         cudaStream_t stream);
+
+// Must be called once per device before launch_grouped_gemm (sets the dynamic
+// shared-memory limit).  Returns a cudaError_t value.
+int prepare_grouped_gemm();
+
+// Synthetic-expert packer: fp32 [experts, N, K] -> NVFP4 codes, swizzled scale
+// bytes and the per-expert global scale amax/(6*448).
+void launch_pack_weights(const float* weights, int experts, int n_out, int k_in, uint8_t* codes,
+                         uint8_t* scales, float* global_scales, cudaStream_t stream);
+
+}  // namespace gv

@@ -1,0 +1,340 @@
+// Host side of the C ABI declared in include/gevva_moe.h: owns scratch, builds
+// the TMA tensor maps once, and enqueues the stages of one MoE layer in the order
+// of the reference's Impl::launch (src/nvfp4_cutlass.cu:1827-1886).  No
+// allocation, synchronisation or host-dependent branch on device data happens on
+// the launch path, so a launch can be captured into a CUDA graph like the
+// reference's (src/cuda/runtime/verifier.cuh:1058-1078).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "../../include/gevva_moe.h"
+#include "gv_common.cuh"
+#include "gv_launchers.h"
+
+namespace {
+
+using namespace gv;
+
+constexpr int kMaxTokens = 131072;
+
+struct Scratch {
+  int references = 1;
+  int max_tokens = 0;
+  int routes = 0;
+  uint8_t* input_codes = nullptr;
+  uint8_t* input_sf = nullptr;
+  void* w13_out = nullptr;
+  uint8_t* inter_codes = nullptr;
+  uint8_t* inter_sf = nullptr;
+  void* w2_out = nullptr;
+  int* ints = nullptr;  // one allocation carved into the RoutePlan arrays
+  RoutePlan plan{};
+  size_t input_sf_bytes = 0, inter_sf_bytes = 0, tile_capacity = 0;
+};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) !=
+            cudaSuccess ||
+        result != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// Byte matrix [rows, row_bytes] viewed through a 128-row x 128-byte box with the
+// 128-byte swizzle the MMA descriptors expect.  Out-of-range bytes read as zero.
+bool make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes) {
+  const cuuint64_t dims[2] = {row_bytes, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kTileKBytes), static_cast<cuuint32_t>(kTileM)};
+  const cuuint32_t element_strides[2] = {1, 1};
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return false;
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+            element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+thread_local char g_error_text[256] = "";
+
+int cuda_failure(cudaError_t error, const char* what) {
+  std::snprintf(g_error_text, sizeof(g_error_text), "%s: %s", what, cudaGetErrorString(error));
+  return GEVVA_MOE_CUDA_ERROR;
+}
+
+#define GV_CUDA(call, what)                                  \
+  do {                                                       \
+    const cudaError_t gv_error_ = (call);                    \
+    if (gv_error_ != cudaSuccess) return cuda_failure(gv_error_, what); \
+  } while (0)
+
+void free_scratch(Scratch* s) {
+  if (!s) return;
+  cudaFree(s->input_codes);
+  cudaFree(s->input_sf);
+  cudaFree(s->w13_out);
+  cudaFree(s->inter_codes);
+  cudaFree(s->inter_sf);
+  cudaFree(s->w2_out);
+  cudaFree(s->ints);
+  delete s;
+}
+
+int make_scratch(int tokens, Scratch** out) {
+  Scratch* s = new (std::nothrow) Scratch;
+  if (!s) return GEVVA_MOE_CUDA_ERROR;
+  s->max_tokens = tokens;
+  s->routes = tokens * kTopK;
+  const size_t routes = static_cast<size_t>(s->routes);
+  // Scale regions are padded to 128 rows per expert (src/nvfp4_cutlass.cu:1699-1706).
+  const size_t padded_rows = routes + static_cast<size_t>(kExperts) * 127;
+  s->input_sf_bytes = padded_rows * (kHidden / 16);
+  s->inter_sf_bytes = padded_rows * (kInter / 16);
+  s->tile_capacity = routes / kTileM + kExperts + 1;
+  const size_t chunks = (routes + 1023) / 1024;
+  const size_t int_count = 3 * routes + 2 * (kExperts + 1) + s->tile_capacity + 1 +
+                           chunks * kExperts + 1 + 64;
+  cudaError_t e = cudaSuccess;
+  auto alloc = [&](void** p, size_t bytes) {
+    if (e == cudaSuccess) e = cudaMalloc(p, bytes);
+  };
+  alloc(reinterpret_cast<void**>(&s->input_codes), routes * (kHidden / 2));
+  alloc(reinterpret_cast<void**>(&s->input_sf), s->input_sf_bytes);
+  alloc(&s->w13_out, routes * kW13Out * 2);
+  alloc(reinterpret_cast<void**>(&s->inter_codes), routes * (kInter / 2));
+  alloc(reinterpret_cast<void**>(&s->inter_sf), s->inter_sf_bytes);
+  alloc(&s->w2_out, routes * kHidden * 2);
+  alloc(reinterpret_cast<void**>(&s->ints), int_count * sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(s->input_codes, 0, routes * (kHidden / 2));
+  if (e == cudaSuccess) e = cudaMemset(s->input_sf, 0, s->input_sf_bytes);
+  if (e == cudaSuccess) e = cudaMemset(s->inter_codes, 0, routes * (kInter / 2));
+  if (e == cudaSuccess) e = cudaMemset(s->inter_sf, 0, s->inter_sf_bytes);
+  if (e == cudaSuccess) e = cudaMemset(s->ints, 0, int_count * sizeof(int));
+  if (e != cudaSuccess) {
+    free_scratch(s);
+    return cuda_failure(e, "scratch allocation");
+  }
+  int* cursor = s->ints;
+  auto carve = [&](size_t count) {
+    int* p = cursor;
+    cursor += count;
+    return p;
+  };
+  s->plan.sorted_experts = carve(routes);
+  s->plan.sorted_routes = carve(routes);
+  s->plan.inverse_routes = carve(routes);
+  s->plan.expert_offsets = carve(kExperts + 1);
+  s->plan.scale_row_offsets = carve(kExperts + 1);
+  s->plan.tile_expert = carve(s->tile_capacity);
+  s->plan.num_m_tiles = carve(1);
+  s->plan.chunk_hist = carve(chunks * kExperts);
+  s->plan.status = carve(1);
+  *out = s;
+  return GEVVA_MOE_OK;
+}
+
+}  // namespace
+
+struct gevva_moe {
+  Scratch* scratch = nullptr;
+  gevva_moe_weights weights{};
+  gv::GemmOperands w13{};
+  gv::GemmOperands w2{};
+  int sm_count = 0;
+};
+
+extern "C" {
+
+const char* gevva_moe_strerror(int status) {
+  switch (status) {
+    case GEVVA_MOE_OK: return "ok";
+    case GEVVA_MOE_BAD_EXPERT_ID: return "expert id outside [0,128)";
+    case GEVVA_MOE_WAIT_TIMEOUT: return "bounded device wait expired";
+    case GEVVA_MOE_BAD_ARGUMENT: return "bad argument";
+    case GEVVA_MOE_CUDA_ERROR: return g_error_text[0] ? g_error_text : "CUDA error";
+    case GEVVA_MOE_NO_DEVICE: return "no sm_100 device or driver entry point";
+    case GEVVA_MOE_TOO_LARGE: return "size beyond the supported maximum";
+    default: return "unknown status";
+  }
+}
+
+int gevva_moe_create(gevva_moe** out, const gevva_moe_weights* weights, int max_tokens,
+                     gevva_moe* share_scratch_with, const gevva_moe_options* options) {
+  (void)options;
+  if (!out || !weights || !weights->w13 || !weights->w13_sf || !weights->w2 || !weights->w2_sf ||
+      !weights->alpha1 || !weights->alpha2 || !weights->in_scale_q1 || !weights->in_scale_q2)
+    return GEVVA_MOE_BAD_ARGUMENT;
+  if (max_tokens < 1) return GEVVA_MOE_BAD_ARGUMENT;
+  if (max_tokens > kMaxTokens) return GEVVA_MOE_TOO_LARGE;
+  if (share_scratch_with && share_scratch_with->scratch->max_tokens != max_tokens)
+    return GEVVA_MOE_BAD_ARGUMENT;  // "shared expert capacity mismatch", src/nvfp4_cutlass.cu:1788
+  int device = 0;
+  GV_CUDA(cudaGetDevice(&device), "cudaGetDevice");
+  cudaDeviceProp prop;
+  GV_CUDA(cudaGetDeviceProperties(&prop, device), "cudaGetDeviceProperties");
+  if (prop.major != 10 || !encode_tiled()) return GEVVA_MOE_NO_DEVICE;
+  GV_CUDA(static_cast<cudaError_t>(gv::prepare_grouped_gemm()), "cudaFuncSetAttribute");
+
+  gevva_moe* m = new (std::nothrow) gevva_moe;
+  if (!m) return GEVVA_MOE_CUDA_ERROR;
+  m->weights = *weights;
+  m->sm_count = prop.multiProcessorCount;
+  if (share_scratch_with) {
+    m->scratch = share_scratch_with->scratch;
+    ++m->scratch->references;
+  } else {
+    const int status = make_scratch(max_tokens, &m->scratch);
+    if (status != GEVVA_MOE_OK) {
+      delete m;
+      return status;
+    }
+  }
+  Scratch* s = m->scratch;
+  const uint64_t rows = static_cast<uint64_t>(s->routes);
+  bool ok = true;
+  ok = ok && make_operand_map(&m->w13.map_a, s->input_codes, rows, kHidden / 2);
+  ok = ok && make_operand_map(&m->w13.map_b, weights->w13, static_cast<uint64_t>(kExperts) * kW13Out,
+                              kHidden / 2);
+  ok = ok && make_operand_map(&m->w2.map_a, s->inter_codes, rows, kInter / 2);
+  ok = ok && make_operand_map(&m->w2.map_b, weights->w2, static_cast<uint64_t>(kExperts) * kHidden,
+                              kInter / 2);
+  if (!ok) {
+    gevva_moe_destroy(m);
+    std::snprintf(g_error_text, sizeof(g_error_text), "cuTensorMapEncodeTiled failed");
+    return GEVVA_MOE_CUDA_ERROR;
+  }
+  m->w13.a_scales = s->input_sf;
+  m->w13.b_scales = static_cast<const uint8_t*>(weights->w13_sf);
+  m->w13.alpha = weights->alpha1;
+  m->w13.out = s->w13_out;
+  m->w13.n_out = kW13Out;
+  m->w13.k_in = kHidden;
+  m->w2.a_scales = s->inter_sf;
+  m->w2.b_scales = static_cast<const uint8_t*>(weights->w2_sf);
+  m->w2.alpha = weights->alpha2;
+  m->w2.out = s->w2_out;
+  m->w2.n_out = kHidden;
+  m->w2.k_in = kInter;
+  *out = m;
+  return GEVVA_MOE_OK;
+}
+
+void gevva_moe_destroy(gevva_moe* runner) {
+  if (!runner) return;
+  if (runner->scratch && --runner->scratch->references == 0) free_scratch(runner->scratch);
+  delete runner;
+}
+
+int gevva_moe_route(const void* logits_bf16, int ld, const void* expert_scale_bf16, float* weights,
+                    int* ids, int tokens, const float* act_scales, const float* w_scale,
+                    gevva_stream_t stream) {
+  if (!logits_bf16 || !expert_scale_bf16 || !weights || !ids || ld < kExperts || tokens < 0 ||
+      (act_scales != nullptr) != (w_scale != nullptr))
+    return GEVVA_MOE_BAD_ARGUMENT;
+  if (tokens == 0) return GEVVA_MOE_OK;
+  gv::launch_route(logits_bf16, ld, expert_scale_bf16, weights, ids, tokens, act_scales, w_scale,
+                   stream);
+  GV_CUDA(cudaGetLastError(), "route_128_top8");
+  return GEVVA_MOE_OK;
+}
+
+int gevva_moe_launch_stages(gevva_moe* runner, const void* in, const int* ids,
+                            const float* route_weights, void* out, int tokens, unsigned stages,
+                            gevva_stream_t stream) {
+  if (!runner) return GEVVA_MOE_BAD_ARGUMENT;
+  Scratch* s = runner->scratch;
+  // "expert runner token count exceeds its plan", src/nvfp4_cutlass.cu:1830-1832
+  if (tokens < 1 || tokens > s->max_tokens) return GEVVA_MOE_BAD_ARGUMENT;
+  if ((stages & (GEVVA_MOE_STAGE_SORT | GEVVA_MOE_STAGE_QUANTIZE)) && !ids) return GEVVA_MOE_BAD_ARGUMENT;
+  if ((stages & GEVVA_MOE_STAGE_QUANTIZE) && !in) return GEVVA_MOE_BAD_ARGUMENT;
+  if ((stages & GEVVA_MOE_STAGE_REDUCE) && (!out || !route_weights)) return GEVVA_MOE_BAD_ARGUMENT;
+  const int routes = tokens * kTopK;
+  if (stages & GEVVA_MOE_STAGE_SORT) gv::launch_route_sort(ids, routes, s->plan, stream);
+  if (stages & GEVVA_MOE_STAGE_QUANTIZE)
+    gv::launch_quantize_input(in, ids, runner->weights.in_scale_q1, s->plan, tokens, s->input_codes,
+                              s->input_sf, stream);
+  if (stages & GEVVA_MOE_STAGE_W13) gv::launch_grouped_gemm(runner->w13, s->plan, runner->sm_count, stream);
+  if (stages & GEVVA_MOE_STAGE_GEGLU)
+    gv::launch_geglu_quantize(s->w13_out, runner->weights.in_scale_q2, s->plan, routes,
+                              s->inter_codes, s->inter_sf, stream);
+  if (stages & GEVVA_MOE_STAGE_W2) gv::launch_grouped_gemm(runner->w2, s->plan, runner->sm_count, stream);
+  if (stages & GEVVA_MOE_STAGE_REDUCE)
+    gv::launch_reduce_routes(s->w2_out, route_weights, s->plan.inverse_routes, tokens, out, stream);
+  GV_CUDA(cudaGetLastError(), "moe launch");
+  return GEVVA_MOE_OK;
+}
+
+int gevva_moe_launch(gevva_moe* runner, const void* in, const int* ids, const float* route_weights,
+                     void* out, int tokens, gevva_stream_t stream) {
+  if (!in || !ids) return GEVVA_MOE_BAD_ARGUMENT;
+  unsigned stages = GEVVA_MOE_STAGE_ALL;
+  if (!out) stages &= ~static_cast<unsigned>(GEVVA_MOE_STAGE_REDUCE);
+  return gevva_moe_launch_stages(runner, in, ids, route_weights, out, tokens, stages, stream);
+}
+
+const void* gevva_moe_routed_output(const gevva_moe* runner) {
+  return runner ? runner->scratch->w2_out : nullptr;
+}
+
+const int* gevva_moe_inverse_routes(const gevva_moe* runner) {
+  return runner ? runner->scratch->plan.inverse_routes : nullptr;
+}
+
+int gevva_moe_last_status(gevva_moe* runner) {
+  if (!runner) return GEVVA_MOE_BAD_ARGUMENT;
+  int status = 0;
+  GV_CUDA(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+  GV_CUDA(cudaMemcpy(&status, runner->scratch->plan.status, sizeof(int), cudaMemcpyDeviceToHost),
+          "status read");
+  if (status != 0) GV_CUDA(cudaMemset(runner->scratch->plan.status, 0, sizeof(int)), "status clear");
+  return -status;
+}
+
+int gevva_moe_buffer(const gevva_moe* runner, int buffer_id, void** device_ptr, size_t* bytes) {
+  if (!runner || !device_ptr || !bytes) return GEVVA_MOE_BAD_ARGUMENT;
+  const Scratch* s = runner->scratch;
+  const size_t routes = static_cast<size_t>(s->routes);
+  switch (buffer_id) {
+    case GEVVA_MOE_BUF_INPUT_CODES: *device_ptr = s->input_codes; *bytes = routes * (kHidden / 2); break;
+    case GEVVA_MOE_BUF_INPUT_SF: *device_ptr = s->input_sf; *bytes = s->input_sf_bytes; break;
+    case GEVVA_MOE_BUF_W13_OUT: *device_ptr = s->w13_out; *bytes = routes * kW13Out * 2; break;
+    case GEVVA_MOE_BUF_INTER_CODES: *device_ptr = s->inter_codes; *bytes = routes * (kInter / 2); break;
+    case GEVVA_MOE_BUF_INTER_SF: *device_ptr = s->inter_sf; *bytes = s->inter_sf_bytes; break;
+    case GEVVA_MOE_BUF_W2_OUT: *device_ptr = s->w2_out; *bytes = routes * kHidden * 2; break;
+    case GEVVA_MOE_BUF_SORTED_EXPERTS: *device_ptr = s->plan.sorted_experts; *bytes = routes * 4; break;
+    case GEVVA_MOE_BUF_SORTED_ROUTES: *device_ptr = s->plan.sorted_routes; *bytes = routes * 4; break;
+    case GEVVA_MOE_BUF_INVERSE_ROUTES: *device_ptr = s->plan.inverse_routes; *bytes = routes * 4; break;
+    case GEVVA_MOE_BUF_EXPERT_OFFSETS: *device_ptr = s->plan.expert_offsets; *bytes = (kExperts + 1) * 4; break;
+    case GEVVA_MOE_BUF_SCALE_ROW_OFFSETS: *device_ptr = s->plan.scale_row_offsets; *bytes = (kExperts + 1) * 4; break;
+    case GEVVA_MOE_BUF_TILE_EXPERT: *device_ptr = s->plan.tile_expert; *bytes = s->tile_capacity * 4; break;
+    case GEVVA_MOE_BUF_NUM_TILES: *device_ptr = s->plan.num_m_tiles; *bytes = 4; break;
+    default: return GEVVA_MOE_BAD_ARGUMENT;
+  }
+  return GEVVA_MOE_OK;
+}
+
+int gevva_moe_pack_experts(const float* weights, int experts, int n_out, int k_in, void* codes,
+                           void* scales, float* global_scales, gevva_stream_t stream) {
+  if (!weights || !codes || !scales || !global_scales || experts < 1 || n_out < 128 ||
+      n_out % 128 != 0 || k_in < 64 || k_in % 64 != 0)
+    return GEVVA_MOE_BAD_ARGUMENT;
+  gv::launch_pack_weights(weights, experts, n_out, k_in, static_cast<uint8_t*>(codes),
+                          static_cast<uint8_t*>(scales), global_scales, stream);
+  GV_CUDA(cudaGetLastError(), "pack experts");
+  return GEVVA_MOE_OK;
+}
+
+}  // extern "C"

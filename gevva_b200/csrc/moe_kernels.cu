@@ -1,0 +1,495 @@
+// Router, route sort, NVFP4 quantisers, weighted reduce and the synthetic weight
+// packer: the HBM-bound stages around the two grouped GEMMs.
+//
+// Arithmetic that decides a code or a scale byte is written with explicit
+// round-to-nearest intrinsics so that it equals the IEEE statement of the
+// reference kernels (src/nvfp4_cutlass.cu:290-327, :552-601) bit for bit.
+#include "gv_common.cuh"
+#include "gv_launchers.h"
+
+namespace gv {
+
+// ---------------------------------------------------------------------------
+// Router: top-8 of 128 logits + softmax over the eight + per-expert scale.
+// Reference: route_128_top8_kernel, src/cuda/kernels/routing_sampling.cuh:396-431
+// (a 128-thread CTA and a full CUB radix sort per token).  Here one warp owns one
+// token: four logits per lane, eight rounds of redux.sync arg-max.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t radix_key(float value) {
+  uint32_t bits = __float_as_uint(value);
+  if (bits == 0x80000000u) bits = 0;  // -0 sorts as +0
+  return (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+}
+
+__global__ void __launch_bounds__(128)
+route_128_top8_kernel(const __nv_bfloat16* __restrict__ logits, int ld,
+                      const __nv_bfloat16* __restrict__ expert_scale, float* __restrict__ weights,
+                      int* __restrict__ ids, int rows, const float* __restrict__ activation_scales,
+                      const float* __restrict__ projection_weight_scale) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const uint16_t* src =
+      reinterpret_cast<const uint16_t*>(logits) + static_cast<size_t>(row) * ld + 4 * lane;
+  float value[4];
+  uint32_t key[4];
+  float rescale = 1.0f;
+  if (activation_scales) rescale = __fmul_rn(activation_scales[row], projection_weight_scale[0]);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float v = bf16_bits_to_float(src[j]);
+    if (activation_scales) v = __bfloat162float(__float2bfloat16_rn(__fmul_rn(v, rescale)));
+    value[j] = v;
+    key[j] = radix_key(v);
+  }
+  uint32_t taken = 0;
+  int my_id = 0;
+  float my_key = 0.0f;
+#pragma unroll 1
+  for (int round = 0; round < kTopK; ++round) {
+    uint32_t best_key = 0;
+    uint32_t best_index = 0xffffffffu;
+#pragma unroll
+    for (int j = 3; j >= 0; --j) {
+      if (!((taken >> j) & 1u) && key[j] >= best_key) {  // descending j: ties keep the lower index
+        best_key = key[j];
+        best_index = 4u * lane + j;
+      }
+    }
+    const uint32_t top_key = __reduce_max_sync(0xffffffffu, best_key);
+    const uint32_t candidate = (best_index != 0xffffffffu && best_key == top_key) ? best_index
+                                                                                  : 0xffffffffu;
+    const uint32_t winner = __reduce_min_sync(0xffffffffu, candidate);
+    const int owner = static_cast<int>(winner >> 2);
+    const int slot = static_cast<int>(winner & 3u);
+    float v = value[0];
+    v = slot == 1 ? value[1] : v;
+    v = slot == 2 ? value[2] : v;
+    v = slot == 3 ? value[3] : v;
+    v = __shfl_sync(0xffffffffu, v, owner);
+    if (lane == owner) taken |= 1u << slot;
+    if (lane == round) {
+      my_id = static_cast<int>(winner);
+      my_key = v;
+    }
+  }
+  const float maximum = __shfl_sync(0xffffffffu, my_key, 0);
+  const float e = lane < kTopK ? gv_expf(__fsub_rn(my_key, maximum)) : 0.0f;
+  float ek[kTopK];
+#pragma unroll
+  for (int k = 0; k < kTopK; ++k) ek[k] = __shfl_sync(0xffffffffu, e, k);
+  // Same association as the reference's shuffle-down tree over lanes 0..7.
+  const float denominator =
+      __fadd_rn(__fadd_rn(__fadd_rn(ek[0], ek[4]), __fadd_rn(ek[2], ek[6])),
+                __fadd_rn(__fadd_rn(ek[1], ek[5]), __fadd_rn(ek[3], ek[7])));
+  if (lane < kTopK) {
+    ids[row * kTopK + lane] = my_id;
+    weights[row * kTopK + lane] =
+        __fmul_rn(__fdiv_rn(e, denominator), __bfloat162float(expert_scale[my_id]));
+  }
+}
+
+void launch_route(const void* logits_bf16, int ld, const void* expert_scale_bf16, float* weights,
+                  int* ids, int tokens, const float* activation_scales,
+                  const float* projection_weight_scale, cudaStream_t stream) {
+  route_128_top8_kernel<<<(tokens + 3) / 4, 128, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(logits_bf16), ld,
+      static_cast<const __nv_bfloat16*>(expert_scale_bf16), weights, ids, tokens, activation_scales,
+      projection_weight_scale);
+}
+
+// ---------------------------------------------------------------------------
+// Route sort: stable counting sort of R = 8*T routes by expert, plus the group
+// geometry every later stage reads.  Reference: four variants at
+// src/nvfp4_cutlass.cu:329-550 (one CTA, or cub::DeviceRadixSort above 2560
+// routes).  Here: chunks of 1024 routes; per chunk, per-warp match_any counts give
+// each route its stable rank; chunks are chained by a 128-thread prefix kernel.
+// ---------------------------------------------------------------------------
+constexpr int kSortChunk = 1024;
+
+// Per-warp population of each expert inside a 1024-route chunk.  `warp_counts`
+// must be zero on entry.  Returns the lanes of this warp that share this lane's expert.
+__device__ __forceinline__ uint32_t count_chunk(int expert, int* warp_counts) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const uint32_t peers = __match_any_sync(0xffffffffu, expert);
+  if (expert < kExperts && (peers & (0u - peers)) == (1u << lane))
+    warp_counts[warp * kExperts + expert] = __popc(peers);
+  return peers;
+}
+
+// Exclusive scans of the 128 expert counts and tile counts, and the outputs that
+// depend only on them.  Called by threads 0..127 with `count` = rows of expert tid.
+__device__ __forceinline__ int publish_groups(int count, int routes, const RoutePlan& plan,
+                                              int* scan_scratch /* smem [16] */) {
+  const int expert = threadIdx.x;
+  const int lane = expert & 31, warp = expert >> 5;
+  const int tiles = (count + kTileM - 1) / kTileM;
+  int rows_inclusive = count, tiles_inclusive = tiles;
+#pragma unroll
+  for (int offset = 1; offset < 32; offset <<= 1) {
+    const int r = __shfl_up_sync(0xffffffffu, rows_inclusive, offset);
+    const int t = __shfl_up_sync(0xffffffffu, tiles_inclusive, offset);
+    if (lane >= offset) {
+      rows_inclusive += r;
+      tiles_inclusive += t;
+    }
+  }
+  if (lane == 31) {
+    scan_scratch[warp] = rows_inclusive;
+    scan_scratch[4 + warp] = tiles_inclusive;
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");  // only the first four warps take part
+  int row_base = 0, tile_base = 0;
+  for (int w = 0; w < warp; ++w) {
+    row_base += scan_scratch[w];
+    tile_base += scan_scratch[4 + w];
+  }
+  const int row_begin = row_base + rows_inclusive - count;
+  const int tile_begin = tile_base + tiles_inclusive - tiles;
+  plan.expert_offsets[expert] = row_begin;
+  plan.scale_row_offsets[expert] = tile_begin * kTileM;
+  for (int i = 0; i < tiles; ++i) plan.tile_expert[tile_begin + i] = expert;
+  if (expert == kExperts - 1) {
+    plan.expert_offsets[kExperts] = row_begin + count;
+    plan.scale_row_offsets[kExperts] = (tile_begin + tiles) * kTileM;
+    plan.num_m_tiles[0] = tile_begin + tiles;
+  }
+  (void)routes;
+  return row_begin;
+}
+
+__global__ void __launch_bounds__(kSortChunk)
+route_sort_single_kernel(const int* __restrict__ expert_ids, int routes, RoutePlan plan) {
+  __shared__ int warp_counts[32 * kExperts];
+  __shared__ int begins[kExperts];
+  __shared__ int scan_scratch[16];
+  const int tid = threadIdx.x;
+  for (int i = tid; i < 32 * kExperts; i += kSortChunk) warp_counts[i] = 0;
+  __syncthreads();
+  int expert = kExperts;
+  if (tid < routes) {
+    expert = expert_ids[tid];
+    if (expert < 0 || expert >= kExperts) {
+      atomicExch(plan.status, static_cast<int>(kBadExpertId));
+      expert = kExperts;
+    }
+  }
+  const uint32_t peers = count_chunk(expert, warp_counts);
+  __syncthreads();
+  if (tid < kExperts) {
+    int running = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int c = warp_counts[w * kExperts + tid];
+      warp_counts[w * kExperts + tid] = running;
+      running += c;
+    }
+    begins[tid] = publish_groups(running, routes, plan, scan_scratch);
+  }
+  __syncthreads();
+  if (expert < kExperts) {
+    const int lane = tid & 31, warp = tid >> 5;
+    const int dst = begins[expert] + warp_counts[warp * kExperts + expert] +
+                    __popc(peers & ((1u << lane) - 1u));
+    plan.sorted_experts[dst] = expert;
+    plan.sorted_routes[dst] = tid;
+    plan.inverse_routes[tid] = dst;
+  }
+}
+
+__global__ void __launch_bounds__(kSortChunk)
+route_histogram_kernel(const int* __restrict__ expert_ids, int routes, RoutePlan plan) {
+  __shared__ int warp_counts[32 * kExperts];
+  const int tid = threadIdx.x;
+  for (int i = tid; i < 32 * kExperts; i += kSortChunk) warp_counts[i] = 0;
+  __syncthreads();
+  const int route = blockIdx.x * kSortChunk + tid;
+  int expert = kExperts;
+  if (route < routes) {
+    expert = expert_ids[route];
+    if (expert < 0 || expert >= kExperts) {
+      atomicExch(plan.status, static_cast<int>(kBadExpertId));
+      expert = kExperts;
+    }
+  }
+  count_chunk(expert, warp_counts);
+  __syncthreads();
+  if (tid < kExperts) {
+    int total = 0;
+    for (int w = 0; w < 32; ++w) total += warp_counts[w * kExperts + tid];
+    plan.chunk_hist[blockIdx.x * kExperts + tid] = total;
+  }
+}
+
+__global__ void __launch_bounds__(kExperts)
+route_prefix_kernel(int chunks, int routes, RoutePlan plan) {
+  __shared__ int scan_scratch[16];
+  const int expert = threadIdx.x;
+  int running = 0;
+  for (int c = 0; c < chunks; ++c) {
+    const int v = plan.chunk_hist[c * kExperts + expert];
+    plan.chunk_hist[c * kExperts + expert] = running;
+    running += v;
+  }
+  publish_groups(running, routes, plan, scan_scratch);
+}
+
+__global__ void __launch_bounds__(kSortChunk)
+route_scatter_kernel(const int* __restrict__ expert_ids, int routes, RoutePlan plan) {
+  __shared__ int warp_counts[32 * kExperts];
+  const int tid = threadIdx.x;
+  for (int i = tid; i < 32 * kExperts; i += kSortChunk) warp_counts[i] = 0;
+  __syncthreads();
+  const int route = blockIdx.x * kSortChunk + tid;
+  int expert = kExperts;
+  if (route < routes) {
+    expert = expert_ids[route];
+    if (expert < 0 || expert >= kExperts) expert = kExperts;
+  }
+  const uint32_t peers = count_chunk(expert, warp_counts);
+  __syncthreads();
+  if (tid < kExperts) {
+    int running = plan.expert_offsets[tid] + plan.chunk_hist[blockIdx.x * kExperts + tid];
+    for (int w = 0; w < 32; ++w) {
+      const int c = warp_counts[w * kExperts + tid];
+      warp_counts[w * kExperts + tid] = running;
+      running += c;
+    }
+  }
+  __syncthreads();
+  if (expert < kExperts) {
+    const int lane = tid & 31, warp = tid >> 5;
+    const int dst = warp_counts[warp * kExperts + expert] + __popc(peers & ((1u << lane) - 1u));
+    plan.sorted_experts[dst] = expert;
+    plan.sorted_routes[dst] = route;
+    plan.inverse_routes[route] = dst;
+  }
+}
+
+void launch_route_sort(const int* expert_ids, int routes, const RoutePlan& plan,
+                       cudaStream_t stream) {
+  if (routes <= kSortChunk) {
+    route_sort_single_kernel<<<1, kSortChunk, 0, stream>>>(expert_ids, routes, plan);
+    return;
+  }
+  const int chunks = (routes + kSortChunk - 1) / kSortChunk;
+  route_histogram_kernel<<<chunks, kSortChunk, 0, stream>>>(expert_ids, routes, plan);
+  route_prefix_kernel<<<1, kExperts, 0, stream>>>(chunks, routes, plan);
+  route_scatter_kernel<<<chunks, kSortChunk, 0, stream>>>(expert_ids, routes, plan);
+}
+
+// ---------------------------------------------------------------------------
+// Input quantiser.  Reference: quantize_bf16_sorted_moe, src/nvfp4_cutlass.cu:
+// 290-327 (one CTA per sorted route, 16 scalar loads per thread, byte stores).
+// Here one CTA per token: thread (k, q) quantises 64 consecutive columns of the
+// token for route k and writes 32 code bytes and one 4-byte scale word to the
+// route's sorted row, so the token row is fetched from HBM once and the eight
+// copies come out of L1.
+// ---------------------------------------------------------------------------
+constexpr int kQuadsHidden = kHidden / 64;  // 44
+constexpr int kQuadsInter = kInter / 64;    // 11
+
+__device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* out) {
+  out[0] = __uint_as_float(raw.x << 16);
+  out[1] = __uint_as_float(raw.x & 0xffff0000u);
+  out[2] = __uint_as_float(raw.y << 16);
+  out[3] = __uint_as_float(raw.y & 0xffff0000u);
+  out[4] = __uint_as_float(raw.z << 16);
+  out[5] = __uint_as_float(raw.z & 0xffff0000u);
+  out[6] = __uint_as_float(raw.w << 16);
+  out[7] = __uint_as_float(raw.w & 0xffff0000u);
+}
+
+__global__ void __launch_bounds__(kTopK * kQuadsHidden)
+quantize_input_kernel(const __nv_bfloat16* __restrict__ input, const int* __restrict__ expert_ids,
+                      const float* __restrict__ in_scale_q, RoutePlan plan,
+                      uint8_t* __restrict__ packed, uint8_t* __restrict__ scales) {
+  const int token = blockIdx.x;
+  const int k = threadIdx.x / kQuadsHidden;
+  const int quad = threadIdx.x % kQuadsHidden;
+  const int route = token * kTopK + k;
+  const int expert = expert_ids[route];
+  if (expert < 0 || expert >= kExperts) return;  // flagged by the route sort
+  const int dst = plan.inverse_routes[route];
+  const int row = dst - plan.expert_offsets[expert];
+  const float multiplier = in_scale_q[expert];
+  const uint4* src =
+      reinterpret_cast<const uint4*>(input + static_cast<size_t>(token) * kHidden + quad * 64);
+  uint32_t codes[8];
+  uint32_t scale_word = 0;
+#pragma unroll
+  for (int block = 0; block < 4; ++block) {
+    float values[16];
+    unpack_bf16x8(__ldg(src + 2 * block), values);
+    unpack_bf16x8(__ldg(src + 2 * block + 1), values + 8);
+    scale_word |= quantize_block16(values, multiplier, codes[2 * block], codes[2 * block + 1])
+                  << (8 * block);
+  }
+  uint4* out = reinterpret_cast<uint4*>(packed + static_cast<size_t>(dst) * (kHidden / 2) + quad * 32);
+  out[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+  out[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+  constexpr int groups = kHidden / 16;
+  *reinterpret_cast<uint32_t*>(scales + static_cast<size_t>(plan.scale_row_offsets[expert]) * groups +
+                               sf_offset(row, 4 * quad, groups)) = scale_word;
+}
+
+void launch_quantize_input(const void* input_bf16, const int* expert_ids, const float* in_scale_q,
+                           const RoutePlan& plan, int tokens, uint8_t* packed, uint8_t* scales,
+                           cudaStream_t stream) {
+  quantize_input_kernel<<<tokens, kTopK * kQuadsHidden, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(input_bf16), expert_ids, in_scale_q, plan, packed, scales);
+}
+
+// ---------------------------------------------------------------------------
+// GeGLU + requantise of the w13 output.  Reference: geglu_quantize_sorted_moe,
+// src/nvfp4_cutlass.cu:552-601: v = gelu_erf(gate) * up from the bf16 GEMM output,
+// columns [0,704) = up and [704,1408) = gate.
+// ---------------------------------------------------------------------------
+constexpr int kGegluRowsPerBlock = 32;
+
+__global__ void __launch_bounds__(kGegluRowsPerBlock * kQuadsInter)
+geglu_quantize_kernel(const __nv_bfloat16* __restrict__ fused, const float* __restrict__ in_scale_q,
+                      RoutePlan plan, int routes, uint8_t* __restrict__ packed,
+                      uint8_t* __restrict__ scales) {
+  const int route = blockIdx.x * kGegluRowsPerBlock + threadIdx.x / kQuadsInter;
+  const int quad = threadIdx.x % kQuadsInter;
+  if (route >= routes) return;
+  const int expert = plan.sorted_experts[route];
+  const int row = route - plan.expert_offsets[expert];
+  const float multiplier = in_scale_q[expert];
+  const uint4* up = reinterpret_cast<const uint4*>(fused + static_cast<size_t>(route) * kW13Out + quad * 64);
+  const uint4* gate = reinterpret_cast<const uint4*>(fused + static_cast<size_t>(route) * kW13Out + kInter + quad * 64);
+  uint32_t codes[8];
+  uint32_t scale_word = 0;
+#pragma unroll
+  for (int block = 0; block < 4; ++block) {
+    float u[16], g[16], values[16];
+    unpack_bf16x8(__ldg(up + 2 * block), u);
+    unpack_bf16x8(__ldg(up + 2 * block + 1), u + 8);
+    unpack_bf16x8(__ldg(gate + 2 * block), g);
+    unpack_bf16x8(__ldg(gate + 2 * block + 1), g + 8);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) values[i] = __fmul_rn(gv_gelu_erf(g[i]), u[i]);
+    scale_word |= quantize_block16(values, multiplier, codes[2 * block], codes[2 * block + 1])
+                  << (8 * block);
+  }
+  uint4* out = reinterpret_cast<uint4*>(packed + static_cast<size_t>(route) * (kInter / 2) + quad * 32);
+  out[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+  out[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+  constexpr int groups = kInter / 16;
+  *reinterpret_cast<uint32_t*>(scales + static_cast<size_t>(plan.scale_row_offsets[expert]) * groups +
+                               sf_offset(row, 4 * quad, groups)) = scale_word;
+}
+
+void launch_geglu_quantize(const void* fused_bf16, const float* in_scale_q, const RoutePlan& plan,
+                           int routes, uint8_t* packed, uint8_t* scales, cudaStream_t stream) {
+  geglu_quantize_kernel<<<(routes + kGegluRowsPerBlock - 1) / kGegluRowsPerBlock,
+                          kGegluRowsPerBlock * kQuadsInter, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(fused_bf16), in_scale_q, plan, routes, packed, scales);
+}
+
+// ---------------------------------------------------------------------------
+// Weighted un-permute/reduce.  Reference: reduce_expert_routes,
+// src/nvfp4_cutlass.cu:229-247: fp32 fmaf over the eight routes in route order,
+// one bf16 rounding.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kHidden / 8)
+reduce_routes_kernel(const __nv_bfloat16* __restrict__ routed, const float* __restrict__ route_weights,
+                     const int* __restrict__ inverse_routes, __nv_bfloat16* __restrict__ output) {
+  const int token = blockIdx.x;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+  for (int k = 0; k < kTopK; ++k) {
+    const int index = token * kTopK + k;
+    const int source = inverse_routes[index];
+    const float weight = route_weights[index];
+    float v[8];
+    unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(routed + static_cast<size_t>(source) * kHidden) +
+                        threadIdx.x),
+                  v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = __fmaf_rn(v[i], weight, acc[i]);
+  }
+  uint32_t packed[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 pair = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+    packed[i] = *reinterpret_cast<const uint32_t*>(&pair);
+  }
+  reinterpret_cast<uint4*>(output + static_cast<size_t>(token) * kHidden)[threadIdx.x] =
+      make_uint4(packed[0], packed[1], packed[2], packed[3]);
+}
+
+void launch_reduce_routes(const void* routed_bf16, const float* route_weights,
+                          const int* inverse_routes, int tokens, void* output_bf16,
+                          cudaStream_t stream) {
+  reduce_routes_kernel<<<tokens, kHidden / 8, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(routed_bf16), route_weights, inverse_routes,
+      static_cast<__nv_bfloat16*>(output_bf16));
+}
+
+// ---------------------------------------------------------------------------
+// Synthetic expert packer: fp32 weights -> the sidecar's NVFP4 layout
+// (tensor shapes: src/runtime.cpp:233-252; scale interleave per expert:
+// tools/pack_trtllm_experts.py:59-64).  global = amax/(6*448) per expert matrix.
+// ---------------------------------------------------------------------------
+__global__ void expert_amax_kernel(const float* __restrict__ weights, size_t per_expert,
+                                   unsigned int* __restrict__ amax_bits) {
+  const int expert = blockIdx.y;
+  const float* w = weights + static_cast<size_t>(expert) * per_expert;
+  float maximum = 0.0f;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < per_expert;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x)
+    maximum = fmaxf(maximum, fabsf(w[i]));
+  for (int offset = 16; offset; offset >>= 1)
+    maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, offset));
+  if ((threadIdx.x & 31) == 0) atomicMax(amax_bits + expert, __float_as_uint(maximum));
+}
+
+__global__ void pack_weights_kernel(const float* __restrict__ weights, int n_out, int k_in,
+                                    const unsigned int* __restrict__ amax_bits,
+                                    uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
+                                    float* __restrict__ global_scales) {
+  const int expert = blockIdx.y;
+  const int groups = k_in / 16;
+  const int block_index = blockIdx.x * blockDim.x + threadIdx.x;
+  const float global = __fdiv_rn(__uint_as_float(amax_bits[expert]), __fmul_rn(6.0f, 448.0f));
+  if (block_index == 0) global_scales[expert] = global;
+  if (block_index >= n_out * groups) return;
+  const int n = block_index / groups, g = block_index % groups;
+  const float multiplier = global == 0.0f ? 0.0f : __fdiv_rn(1.0f, global);
+  const float4* src = reinterpret_cast<const float4*>(
+      weights + (static_cast<size_t>(expert) * n_out + n) * k_in + g * 16);
+  float values[16];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float4 v = __ldg(src + i);
+    values[4 * i] = v.x;
+    values[4 * i + 1] = v.y;
+    values[4 * i + 2] = v.z;
+    values[4 * i + 3] = v.w;
+  }
+  uint32_t lo, hi;
+  const uint32_t scale = quantize_block16(values, multiplier, lo, hi);
+  *reinterpret_cast<uint2*>(codes + (static_cast<size_t>(expert) * n_out + n) * (k_in / 2) + g * 8) =
+      make_uint2(lo, hi);
+  scales[static_cast<size_t>(expert) * n_out * groups + sf_offset(n, g, groups)] =
+      static_cast<uint8_t>(scale);
+}
+
+void launch_pack_weights(const float* weights, int experts, int n_out, int k_in, uint8_t* codes,
+                         uint8_t* scales, float* global_scales, cudaStream_t stream) {
+  // Not on the hot path: a stream-ordered temporary holds the per-expert amax bit patterns
+  // (the bits of a non-negative float order like an unsigned integer).
+  unsigned int* accumulator = nullptr;
+  cudaMallocAsync(reinterpret_cast<void**>(&accumulator), sizeof(unsigned int) * experts, stream);
+  cudaMemsetAsync(accumulator, 0, sizeof(unsigned int) * experts, stream);
+  const size_t per_expert = static_cast<size_t>(n_out) * k_in;
+  expert_amax_kernel<<<dim3(64, experts), 256, 0, stream>>>(weights, per_expert, accumulator);
+  const int blocks = n_out * (k_in / 16);
+  pack_weights_kernel<<<dim3((blocks + 255) / 256, experts), 256, 0, stream>>>(
+      weights, n_out, k_in, accumulator, codes, scales, global_scales);
+  cudaFreeAsync(accumulator, stream);
+}
+
+}  // namespace gv

@@ -1,0 +1,154 @@
+/* C ABI of the B200 (sm_100a) Gemma-4 26B-A4B NVFP4 mixture-of-experts path.
+ *
+ * The reference exposes this path as a C++ pimpl class that throws
+ * (gevva::Nvfp4ExpertRunner, include/gevva/gpu.hpp:217-247, implementation
+ * src/nvfp4_cutlass.cu:1680-1938) plus one router kernel launched inline
+ * (route_128_top8_kernel, src/cuda/kernels/routing_sampling.cuh:396-431).  This
+ * header is the plain-C boundary underneath a header-only C++ class of the same
+ * name and methods (include/gevva/nvfp4_expert_runner.hpp), so the reference's
+ * call sites (src/cuda/runtime/prefill.cuh:463-476, :1232-1245,
+ * src/cuda/runtime/verifier.cuh:1020-1034, src/decisions.cpp:139-143) compile
+ * against it unchanged.
+ *
+ * Conventions: every pointer is a DEVICE pointer unless it is an out-parameter
+ * of the call itself; every launch only enqueues work on `stream`; functions
+ * return 0 or a negative gevva_moe_status and never throw.  A runner is used
+ * from one host thread; runners that share scratch must be launched on one
+ * stream (include/gevva/gpu.hpp:222).
+ */
+#ifndef GEVVA_MOE_H_
+#define GEVVA_MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct gevva_moe gevva_moe;          /* opaque runner */
+typedef struct CUstream_st* gevva_stream_t;  /* == cudaStream_t */
+
+enum gevva_moe_status {
+  GEVVA_MOE_OK = 0,
+  GEVVA_MOE_BAD_EXPERT_ID = -1, /* device: an id outside [0,128) reached the route sort */
+  GEVVA_MOE_WAIT_TIMEOUT = -2,  /* device: a bounded wait inside a GEMM kernel expired */
+  GEVVA_MOE_BAD_ARGUMENT = -3,
+  GEVVA_MOE_CUDA_ERROR = -4,
+  GEVVA_MOE_NO_DEVICE = -5,     /* no sm_100 device / driver entry point missing */
+  GEVVA_MOE_TOO_LARGE = -6
+};
+
+/* The eight sidecar tensors of one layer that the reference's constructor resolves
+ * by name (src/nvfp4_cutlass.cu:1792-1802; shapes src/runtime.cpp:233-252):
+ *   w13     u8  [128,1408,1408]  E2M1 pairs, rows 0..703 = up, 704..1407 = gate
+ *   w13_sf  u8  [128,1408,176]   E4M3 block scales, 128x4 interleave per expert
+ *   w2      u8  [128,2816,352]
+ *   w2_sf   u8  [128,2816,44]
+ *   alpha1, alpha2            f32 [128]   g1.alpha, g2.alpha
+ *   in_scale_q1, in_scale_q2  f32 [128]   g1/g2.input_scale_quant
+ * They must stay valid for the life of the runner (pointers are cached). */
+typedef struct {
+  const void* w13;
+  const void* w13_sf;
+  const void* w2;
+  const void* w2_sf;
+  const float* alpha1;
+  const float* alpha2;
+  const float* in_scale_q1;
+  const float* in_scale_q2;
+} gevva_moe_weights;
+
+typedef struct {
+  uint32_t flags; /* reserved, 0 */
+  uint32_t reserved[7];
+} gevva_moe_options;
+
+/* Replaces Nvfp4ExpertRunner::Nvfp4ExpertRunner (src/nvfp4_cutlass.cu:1888-1891,
+ * Impl ctor :1764-1825, ExpertScratch :1680-1736).  Allocates scratch for
+ * `max_tokens` tokens, or shares the scratch of `share_scratch_with` (which must
+ * have the same capacity).  1 <= max_tokens <= 131072 (the reference stops at 4608). */
+int gevva_moe_create(gevva_moe** out, const gevva_moe_weights* weights, int max_tokens,
+                     gevva_moe* share_scratch_with, const gevva_moe_options* options);
+
+void gevva_moe_destroy(gevva_moe* runner);
+
+/* Replaces route_128_top8_kernel<<<rows,128>>> (src/cuda/kernels/routing_sampling.cuh:396-431;
+ * launched at src/cuda/runtime/prefill.cuh:420-422, :1208-1210, verifier.cuh:974-976).
+ * logits bf16 [tokens, ld] (ld >= 128, elements), expert_scale bf16 [128],
+ * weights f32 [tokens,8], ids i32 [tokens,8]; act_scales/w_scale optional (both or none). */
+int gevva_moe_route(const void* logits_bf16, int ld, const void* expert_scale_bf16, float* weights,
+                    int* ids, int tokens, const float* act_scales, const float* w_scale,
+                    gevva_stream_t stream);
+
+/* Replaces Nvfp4ExpertRunner::launch / launch_batch / launch_batch_unreduced
+ * (src/nvfp4_cutlass.cu:1893-1913 -> Impl::launch :1827-1886).
+ * in bf16 [tokens,2816]; ids i32 [tokens,8]; route_weights f32 [tokens,8];
+ * out bf16 [tokens,2816].  out == NULL (then route_weights may be NULL) selects the
+ * unreduced form: results stay in gevva_moe_routed_output(). */
+int gevva_moe_launch(gevva_moe* runner, const void* in, const int* ids, const float* route_weights,
+                     void* out, int tokens, gevva_stream_t stream);
+
+/* Replaces Nvfp4ExpertRunner::routed_output (src/nvfp4_cutlass.cu:1915-1917):
+ * bf16 [8*tokens,2816] in sorted-route order, valid until the next launch. */
+const void* gevva_moe_routed_output(const gevva_moe* runner);
+
+/* Replaces Nvfp4ExpertRunner::inverse_routes (src/nvfp4_cutlass.cu:1919-1921):
+ * i32 [8*tokens], original route 8*t+k -> sorted row. */
+const int* gevva_moe_inverse_routes(const gevva_moe* runner);
+
+/* Reads and clears the device status word (synchronises the device).  The
+ * reference has no counterpart: its kernels cannot report and its host code throws. */
+int gevva_moe_last_status(gevva_moe* runner);
+
+const char* gevva_moe_strerror(int status);
+
+/* ---- stage access, for parity tests and debugging ---------------------------
+ * The reference materialises every intermediate in ExpertScratch
+ * (src/nvfp4_cutlass.cu:1680-1700); these two calls expose the same buffers and
+ * let a test run a sub-range of Impl::launch's stages between edits. */
+enum gevva_moe_stage {
+  GEVVA_MOE_STAGE_SORT = 1,      /* :1851-1867 */
+  GEVVA_MOE_STAGE_QUANTIZE = 2,  /* :1869-1873 */
+  GEVVA_MOE_STAGE_W13 = 4,       /* :1874 */
+  GEVVA_MOE_STAGE_GEGLU = 8,     /* :1875-1879 */
+  GEVVA_MOE_STAGE_W2 = 16,       /* :1880 */
+  GEVVA_MOE_STAGE_REDUCE = 32,   /* :1881-1885 */
+  GEVVA_MOE_STAGE_ALL = 63
+};
+
+int gevva_moe_launch_stages(gevva_moe* runner, const void* in, const int* ids,
+                            const float* route_weights, void* out, int tokens, unsigned stages,
+                            gevva_stream_t stream);
+
+enum gevva_moe_buffer_id {
+  GEVVA_MOE_BUF_INPUT_CODES = 0,   /* u8 [R,1408] */
+  GEVVA_MOE_BUF_INPUT_SF = 1,      /* u8 (R+128*127)*176 */
+  GEVVA_MOE_BUF_W13_OUT = 2,       /* bf16 [R,1408] */
+  GEVVA_MOE_BUF_INTER_CODES = 3,   /* u8 [R,352] */
+  GEVVA_MOE_BUF_INTER_SF = 4,      /* u8 (R+128*127)*44 */
+  GEVVA_MOE_BUF_W2_OUT = 5,        /* bf16 [R,2816] */
+  GEVVA_MOE_BUF_SORTED_EXPERTS = 6,
+  GEVVA_MOE_BUF_SORTED_ROUTES = 7,
+  GEVVA_MOE_BUF_INVERSE_ROUTES = 8,
+  GEVVA_MOE_BUF_EXPERT_OFFSETS = 9,     /* i32 [129] */
+  GEVVA_MOE_BUF_SCALE_ROW_OFFSETS = 10, /* i32 [129] */
+  GEVVA_MOE_BUF_TILE_EXPERT = 11,
+  GEVVA_MOE_BUF_NUM_TILES = 12
+};
+
+int gevva_moe_buffer(const gevva_moe* runner, int buffer_id, void** device_ptr, size_t* bytes);
+
+/* Expert packer for synthetic or freshly quantised weights; stands where
+ * tools/pack_trtllm_experts.py:51-65 stands in the reference (stack experts,
+ * interleave block scales) and also performs the NVFP4 quantisation itself:
+ * fp32 [experts, n_out, k_in] -> codes u8 [experts, n_out, k_in/2], scales u8
+ * [experts, n_out, k_in/16] (interleaved per expert), global f32 [experts]
+ * = amax/(6*448). */
+int gevva_moe_pack_experts(const float* weights, int experts, int n_out, int k_in, void* codes,
+                           void* scales, float* global_scales, gevva_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GEVVA_MOE_H_ */

@@ -1,0 +1,424 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle on a B200.
+
+Bit-exact: top-k ids, router weights, permutation arrays, FP4 codes and E4M3 scale
+bytes (each stage fed the same bytes on both sides).  Tolerance 2e-2 relative L2
+for GEMM outputs and the layer output (accumulation order differs)."""
+import numpy as np
+import pytest
+import torch
+
+from tests import hashgen
+from tests.oracle_api import EXPERTS, HIDDEN, INTER, TOP_K, bf16_to_f32, sf_bytes
+
+pytestmark = pytest.mark.gpu
+
+W13_OUT = 2 * INTER
+REL_L2 = 2e-2
+
+
+def bits(t):
+    return t.detach().contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def from_bits(a, device):
+    return torch.from_numpy(a.view(np.int16).copy()).to(device).view(torch.bfloat16)
+
+
+def rel_l2(got, want):
+    got = got.astype(np.float64)
+    want = want.astype(np.float64)
+    return float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30))
+
+
+def random_ids(tokens, seed):
+    rng = np.random.default_rng(seed)
+    return np.stack([rng.choice(EXPERTS, TOP_K, replace=False) for _ in range(tokens)]).astype(np.int32)
+
+
+def skewed_ids(tokens):
+    """Route 0 always on expert 0, the rest hashed into experts 1..36: few active experts
+    with unequal row counts (the shape of the reference's repeatability test routing,
+    src/nvfp4_cutlass.cu:1962-1974)."""
+    t = np.arange(tokens, dtype=np.uint64)[:, None]
+    k = np.arange(TOP_K, dtype=np.uint64)[None, :]
+    mixed = (t * 2654435761 + k * 2246822519) & 0xFFFFFFFF
+    ids = 1 + ((mixed >> 24) + k * k) % 36
+    ids[:, 0] = 0
+    # a token must not name one expert twice for the layer semantics to make sense; keep
+    # duplicates out by re-drawing deterministically
+    ids = ids.astype(np.int32)
+    for row in ids:
+        seen = set()
+        for j in range(TOP_K):
+            while int(row[j]) in seen:
+                row[j] = 1 + (row[j] + 7) % 36
+            seen.add(int(row[j]))
+    return ids
+
+
+@pytest.fixture(scope="module")
+def gm(cuda_device):
+    import gevva_b200
+    return gevva_b200
+
+
+@pytest.fixture(scope="module")
+def packed(cuda_device, gm):
+    """One layer of hash-generated experts packed on the GPU, plus host copies."""
+    out = {k: [] for k in ("w13", "w13_sf", "g13", "w2", "w2_sf", "g2")}
+    chunk = 16
+    for first in range(0, EXPERTS, chunk):
+        w13 = hashgen.expert_weights_chunk(first, chunk, W13_OUT, HIDDEN, 11, cuda_device)
+        c, s, g = gm.pack_experts(w13)
+        out["w13"].append(c), out["w13_sf"].append(s), out["g13"].append(g)
+        del w13
+        w2 = hashgen.expert_weights_chunk(first, chunk, HIDDEN, INTER, 12, cuda_device)
+        c, s, g = gm.pack_experts(w2)
+        out["w2"].append(c), out["w2_sf"].append(s), out["g2"].append(g)
+        del w2
+    dev = {k: torch.cat(v) for k, v in out.items()}
+    host = {k: v.cpu().numpy() for k, v in dev.items()}
+    return dev, host
+
+
+def make_weights(gm, packed, s1, s2, device):
+    dev, host = packed
+    ones = torch.ones(EXPERTS, dtype=torch.float32, device=device)
+    w = gm.ExpertWeights(dev["w13"], dev["w13_sf"], dev["w2"], dev["w2_sf"],
+                         (dev["g13"] * s1).contiguous(), (dev["g2"] * s2).contiguous(),
+                         (ones / s1).contiguous(), (ones / s2).contiguous())
+    hw = dict(w13=host["w13"], w13_sf=host["w13_sf"], w2=host["w2"], w2_sf=host["w2_sf"],
+              alpha1=w.alpha1.cpu().numpy(), alpha2=w.alpha2.cpu().numpy(),
+              in_scale_q1=w.in_scale_q1.cpu().numpy(), in_scale_q2=w.in_scale_q2.cpu().numpy())
+    return w, hw
+
+
+# Static activation scales amax/(6*448): the hashed activations are bounded by 3.4, and
+# gelu(gate)*up of the w13 output stays below 16 for these weights.
+S1 = np.float32(4.0 / (6.0 * 448.0))
+S2 = np.float32(16.0 / (6.0 * 448.0))
+
+
+@pytest.fixture(scope="module")
+def weights(gm, packed, cuda_device):
+    return make_weights(gm, packed, float(S1), float(S2), cuda_device)
+
+
+# ---------------------------------------------------------------------------------------
+def test_packer_matches_oracle(gm, packed, oracle, cuda_device):
+    dev, host = packed
+    for expert in (0, 77, 127):
+        w13 = hashgen.expert_weights_chunk(expert, 1, W13_OUT, HIDDEN, 11, "cpu")[0].numpy()
+        c, s, g = oracle.pack_weight(w13)
+        assert (host["w13"][expert] == c).all()
+        assert (host["w13_sf"][expert] == s).all()
+        assert host["g13"][expert] == g
+        w2 = hashgen.expert_weights_chunk(expert, 1, HIDDEN, INTER, 12, "cpu")[0].numpy()
+        c, s, g = oracle.pack_weight(w2)
+        assert (host["w2"][expert] == c).all()
+        assert (host["w2_sf"][expert] == s).all()
+        assert host["g2"][expert] == g
+
+
+def test_router_permutation_logits(gm, oracle, cuda_device):
+    rows = 64
+    rank = (np.arange(EXPERTS)[None, :] * 37 + np.arange(rows)[:, None] * 19) & 127
+    logits = torch.tensor((rank - 64) * 0.0625, dtype=torch.float32).to(torch.bfloat16).to(cuda_device)
+    scale = torch.tensor(0.5 + (np.arange(EXPERTS) % 17) * 0.07, dtype=torch.float32).to(
+        torch.bfloat16).to(cuda_device)
+    w, ids = gm.route_128_top8(logits, scale)
+    ow, oids = oracle.route(bits(logits), bits(scale))
+    assert (ids.cpu().numpy() == oids).all()
+    assert (w.cpu().numpy().view(np.uint32) == ow.view(np.uint32)).all()
+
+
+@pytest.mark.parametrize("rows", [1, 3, 4, 5, 257, 4096])
+def test_router_random_with_ties(gm, oracle, cuda_device, rows):
+    gen = torch.Generator(device="cpu").manual_seed(rows)
+    logits = (torch.randn((rows, EXPERTS), generator=gen) * 0.5).to(torch.bfloat16)
+    logits[0, :16] = 0.0
+    logits[0, 1:16:2] = -0.0
+    if rows > 2:
+        logits[2] = logits[2, 0]          # a whole row of ties
+    scale = (0.5 + torch.rand(EXPERTS, generator=gen)).to(torch.bfloat16)
+    w, ids = gm.route_128_top8(logits.to(cuda_device), scale.to(cuda_device))
+    ow, oids = oracle.route(bits(logits), bits(scale))
+    assert (ids.cpu().numpy() == oids).all()
+    assert (w.cpu().numpy().view(np.uint32) == ow.view(np.uint32)).all()
+
+
+def test_router_padded_rows_and_fp8_rescale(gm, oracle, cuda_device):
+    gen = torch.Generator(device="cpu").manual_seed(5)
+    rows = 37
+    padded = torch.randn((48, 160), generator=gen).to(torch.bfloat16)
+    view = padded[:rows, :EXPERTS]
+    act = (0.5 + torch.rand(rows, generator=gen)).float()
+    ws = torch.tensor([0.37], dtype=torch.float32)
+    scale = torch.ones(EXPERTS, dtype=torch.bfloat16)
+    dview = padded.to(cuda_device)[:rows, :EXPERTS]
+    w, ids = gm.route_128_top8(dview, scale.to(cuda_device), act.to(cuda_device), ws.to(cuda_device))
+    ow, oids = oracle.route(bits(view.contiguous()), bits(scale), act.numpy(), ws.numpy())
+    assert (ids.cpu().numpy() == oids).all()
+    assert (w.cpu().numpy().view(np.uint32) == ow.view(np.uint32)).all()
+
+
+def plan_arrays(gm, runner, routes):
+    from gevva_b200 import runtime as rt
+    i32 = torch.int32
+    return dict(
+        sorted_experts=runner.buffer(rt.BUF_SORTED_EXPERTS, i32)[:routes].cpu().numpy(),
+        sorted_routes=runner.buffer(rt.BUF_SORTED_ROUTES, i32)[:routes].cpu().numpy(),
+        inverse=runner.buffer(rt.BUF_INVERSE_ROUTES, i32)[:routes].cpu().numpy(),
+        offsets=runner.buffer(rt.BUF_EXPERT_OFFSETS, i32)[:EXPERTS].cpu().numpy(),
+        scale_rows=runner.buffer(rt.BUF_SCALE_ROW_OFFSETS, i32)[:EXPERTS].cpu().numpy(),
+        num_tiles=int(runner.buffer(rt.BUF_NUM_TILES, i32)[0]),
+        tile_expert=runner.buffer(rt.BUF_TILE_EXPERT, i32).cpu().numpy())
+
+
+@pytest.fixture(scope="module")
+def big_runner(gm, weights):
+    return gm.Nvfp4ExpertRunner(weights[0], 4096)
+
+
+@pytest.mark.parametrize("tokens,kind", [(1, "random"), (2, "random"), (7, "random"), (16, "random"),
+                                         (128, "random"), (129, "random"), (1000, "skewed"),
+                                         (4096, "random"), (4096, "skewed")])
+def test_route_sort_matches_oracle(gm, oracle, big_runner, cuda_device, tokens, kind):
+    from gevva_b200 import runtime as rt
+    ids = random_ids(tokens, tokens) if kind == "random" else skewed_ids(tokens)
+    dev_ids = torch.from_numpy(ids).to(cuda_device)
+    big_runner.launch_stages(rt.STAGE_SORT, tokens, expert_ids=dev_ids)
+    assert big_runner.last_status() == 0
+    got = plan_arrays(gm, big_runner, tokens * TOP_K)
+    want = oracle.sort(ids)
+    for key in ("sorted_experts", "sorted_routes", "inverse", "offsets", "scale_rows"):
+        assert (got[key] == want[key]).all(), key
+    counts = np.bincount(ids.reshape(-1), minlength=EXPERTS)
+    tiles = (counts + 127) // 128
+    assert got["num_tiles"] == tiles.sum()
+    assert (got["tile_expert"][:tiles.sum()] == np.repeat(np.arange(EXPERTS), tiles)).all()
+
+
+def test_bad_expert_id_is_reported(gm, big_runner, cuda_device):
+    from gevva_b200 import runtime as rt
+    for tokens in (4, 300):
+        ids = random_ids(tokens, 1)
+        ids[tokens // 2, 3] = 128
+        big_runner.launch_stages(rt.STAGE_SORT, tokens, expert_ids=torch.from_numpy(ids).to(cuda_device))
+        assert big_runner.last_status() == -1
+        assert big_runner.last_status() == 0  # cleared by the read
+
+
+def test_capacity_and_argument_errors(gm, weights, cuda_device):
+    runner = gm.Nvfp4ExpertRunner(weights[0], 16)
+    x = torch.zeros((17, HIDDEN), dtype=torch.bfloat16, device=cuda_device)
+    ids = torch.zeros((17, TOP_K), dtype=torch.int32, device=cuda_device)
+    with pytest.raises(gm.GevvaMoeError):
+        runner.launch_batch_unreduced(x, ids, 17)
+    with pytest.raises(gm.GevvaMoeError):
+        gm.Nvfp4ExpertRunner(weights[0], 32, shared_scratch=runner)  # capacity mismatch
+    with pytest.raises(gm.GevvaMoeError):
+        gm.Nvfp4ExpertRunner(weights[0], 0)
+
+
+@pytest.mark.parametrize("tokens,kind", [(1, "random"), (16, "random"), (129, "skewed"), (300, "random")])
+def test_input_quantiser_bit_exact(gm, oracle, weights, big_runner, cuda_device, tokens, kind):
+    from gevva_b200 import runtime as rt
+    ids = random_ids(tokens, 7 + tokens) if kind == "random" else skewed_ids(tokens)
+    x = hashgen.activations(tokens, HIDDEN, 3, "cpu")
+    if tokens > 1:
+        x[1, 32:48] = 0          # an all-zero block: scale byte 0, codes 0
+        x[1, 48] = -0.0
+    dev_ids = torch.from_numpy(ids).to(cuda_device)
+    big_runner.launch_stages(rt.STAGE_SORT | rt.STAGE_QUANTIZE, tokens, input=x.to(cuda_device),
+                             expert_ids=dev_ids)
+    assert big_runner.last_status() == 0
+    routes = tokens * TOP_K
+    plan = oracle.sort(ids)
+    want_codes, want_sf = oracle.quantize_sorted(bits(x), weights[1]["in_scale_q1"], plan)
+    got_codes = big_runner.buffer(rt.BUF_INPUT_CODES)[: routes * HIDDEN // 2].cpu().numpy()
+    assert (got_codes.reshape(routes, -1) == want_codes).all()
+    got_sf = big_runner.buffer(rt.BUF_INPUT_SF)[: sf_bytes(routes, HIDDEN)].cpu().numpy()
+    # compare only the bytes this launch owns (padding rows keep earlier contents)
+    groups = HIDDEN // 16
+    for expert in np.unique(ids):
+        rows = int((plan["sorted_experts"] == expert).sum())
+        base = plan["scale_rows"][expert] * groups
+        r = np.arange(rows)[:, None]
+        g = np.arange(groups)[None, :]
+        off = base + (r // 128) * (128 * groups) + (g // 4) * 512 + (r % 32) * 16 + ((r // 32) % 4) * 4 + g % 4
+        assert (got_sf[off] == want_sf[off]).all(), int(expert)
+
+
+def stage_inputs(oracle, weights, tokens, kind, seed):
+    ids = random_ids(tokens, seed) if kind == "random" else skewed_ids(tokens)
+    x = hashgen.activations(tokens, HIDDEN, seed, "cpu")
+    plan = oracle.sort(ids)
+    codes, sf = oracle.quantize_sorted(bits(x), weights[1]["in_scale_q1"], plan)
+    return ids, x, plan, codes, sf
+
+
+def upload(runner, buffer_id, array):
+    flat = torch.from_numpy(np.ascontiguousarray(array).reshape(-1).view(np.uint8))
+    runner.buffer(buffer_id)[: flat.numel()].copy_(flat)
+
+
+@pytest.mark.parametrize("tokens,kind", [(16, "random"), (40, "skewed")])
+def test_w13_gemm_stage(gm, oracle, weights, big_runner, cuda_device, tokens, kind):
+    from gevva_b200 import runtime as rt
+    ids, x, plan, codes, sf = stage_inputs(oracle, weights, tokens, kind, 21)
+    routes = tokens * TOP_K
+    big_runner.launch_stages(rt.STAGE_SORT, tokens, expert_ids=torch.from_numpy(ids).to(cuda_device))
+    upload(big_runner, rt.BUF_INPUT_CODES, codes)
+    upload(big_runner, rt.BUF_INPUT_SF, sf)
+    big_runner.launch_stages(rt.STAGE_W13, tokens)
+    assert big_runner.last_status() == 0
+    got = big_runner.buffer(rt.BUF_W13_OUT, torch.bfloat16)[: routes * W13_OUT].view(routes, W13_OUT)
+    hw = weights[1]
+    want = oracle.grouped_gemm(codes, sf, plan, hw["w13"], hw["w13_sf"], hw["alpha1"], W13_OUT, HIDDEN)
+    err = rel_l2(bf16_to_f32(bits(got)), bf16_to_f32(want))
+    assert err < 5e-3, err
+
+
+@pytest.mark.parametrize("tokens,kind", [(16, "random"), (129, "skewed")])
+def test_geglu_quantiser_bit_exact(gm, oracle, weights, big_runner, cuda_device, tokens, kind):
+    from gevva_b200 import runtime as rt
+    ids = random_ids(tokens, 31) if kind == "random" else skewed_ids(tokens)
+    routes = tokens * TOP_K
+    plan = oracle.sort(ids)
+    fused = hashgen.activations(routes, W13_OUT, 9, "cpu", scale=0.9)
+    fused[0, :16] = 0
+    big_runner.launch_stages(rt.STAGE_SORT, tokens, expert_ids=torch.from_numpy(ids).to(cuda_device))
+    upload(big_runner, rt.BUF_W13_OUT, bits(fused))
+    big_runner.launch_stages(rt.STAGE_GEGLU, tokens)
+    assert big_runner.last_status() == 0
+    want_codes, want_sf = oracle.geglu_quantize(bits(fused), weights[1]["in_scale_q2"], plan)
+    got_codes = big_runner.buffer(rt.BUF_INTER_CODES)[: routes * INTER // 2].cpu().numpy()
+    assert (got_codes.reshape(routes, -1) == want_codes).all()
+    got_sf = big_runner.buffer(rt.BUF_INTER_SF)[: sf_bytes(routes, INTER)].cpu().numpy()
+    groups = INTER // 16
+    for expert in np.unique(ids):
+        rows = int((plan["sorted_experts"] == expert).sum())
+        base = plan["scale_rows"][expert] * groups
+        r = np.arange(rows)[:, None]
+        g = np.arange(groups)[None, :]
+        off = base + (r // 128) * (128 * groups) + (g // 4) * 512 + (r % 32) * 16 + ((r // 32) % 4) * 4 + g % 4
+        assert (got_sf[off] == want_sf[off]).all(), int(expert)
+
+
+def test_w2_gemm_stage(gm, oracle, weights, big_runner, cuda_device):
+    from gevva_b200 import runtime as rt
+    tokens = 24
+    ids = skewed_ids(tokens)
+    routes = tokens * TOP_K
+    plan = oracle.sort(ids)
+    fused = hashgen.activations(routes, W13_OUT, 19, "cpu", scale=0.9)
+    codes, sf = oracle.geglu_quantize(bits(fused), weights[1]["in_scale_q2"], plan)
+    big_runner.launch_stages(rt.STAGE_SORT, tokens, expert_ids=torch.from_numpy(ids).to(cuda_device))
+    upload(big_runner, rt.BUF_INTER_CODES, codes)
+    upload(big_runner, rt.BUF_INTER_SF, sf)
+    big_runner.launch_stages(rt.STAGE_W2, tokens)
+    assert big_runner.last_status() == 0
+    got = big_runner.buffer(rt.BUF_W2_OUT, torch.bfloat16)[: routes * HIDDEN].view(routes, HIDDEN)
+    hw = weights[1]
+    want = oracle.grouped_gemm(codes, sf, plan, hw["w2"], hw["w2_sf"], hw["alpha2"], HIDDEN, INTER)
+    err = rel_l2(bf16_to_f32(bits(got)), bf16_to_f32(want))
+    assert err < 5e-3, err
+
+
+def test_reduce_bit_exact(gm, oracle, big_runner, cuda_device):
+    from gevva_b200 import runtime as rt
+    tokens = 33
+    ids = random_ids(tokens, 2)
+    routes = tokens * TOP_K
+    routed = hashgen.activations(routes, HIDDEN, 29, "cpu")
+    w = torch.rand((tokens, TOP_K), generator=torch.Generator().manual_seed(1)) * 0.3
+    big_runner.launch_stages(rt.STAGE_SORT, tokens, expert_ids=torch.from_numpy(ids).to(cuda_device))
+    upload(big_runner, rt.BUF_W2_OUT, bits(routed))
+    out = torch.empty((tokens, HIDDEN), dtype=torch.bfloat16, device=cuda_device)
+    big_runner.launch_stages(rt.STAGE_REDUCE, tokens, route_weights=w.to(cuda_device), output=out)
+    want = oracle.reduce(bits(routed), w.numpy(), oracle.sort(ids)["inverse"], tokens)
+    assert (bits(out) == want).all()
+
+
+@pytest.mark.parametrize("tokens,kind", [(1, "router"), (16, "router"), (40, "skewed")])
+def test_layer_against_oracle(gm, oracle, weights, cuda_device, tokens, kind):
+    """Config-0 shape (16 tokens) and neighbours: ids exact, output within 2e-2 rel-L2."""
+    w, hw = weights
+    x = hashgen.activations(tokens, HIDDEN, 41, "cpu")
+    dx = x.to(cuda_device)
+    if kind == "router":
+        router_w = (hashgen.hash_uniform(EXPERTS * HIDDEN, 5, "cpu") * 0.0346).view(EXPERTS, HIDDEN)
+        logits = (x.float() @ router_w.t()).to(torch.bfloat16)
+        scale = torch.ones(EXPERTS, dtype=torch.bfloat16)
+        rw, ids = gm.route_128_top8(logits.to(cuda_device), scale.to(cuda_device))
+        orw, oids = oracle.route(bits(logits), bits(scale))
+        assert (ids.cpu().numpy() == oids).all()
+        assert (rw.cpu().numpy().view(np.uint32) == orw.view(np.uint32)).all()
+    else:
+        ids = torch.from_numpy(skewed_ids(tokens)).to(cuda_device)
+        rw = torch.tensor([0.24, 0.19, 0.15, 0.12, 0.10, 0.08, 0.07, 0.05], device=cuda_device).repeat(tokens, 1)
+    runner = gm.Nvfp4ExpertRunner(w, max(tokens, 2))
+    out = torch.empty_like(dx)
+    if tokens == 1:
+        runner.launch(dx, ids, rw, out)
+    else:
+        runner.launch_batch(dx, ids, rw, out, tokens)
+    runner.check()
+    want, want_routed, want_inverse = oracle.moe_layer(bits(x), ids.cpu().numpy(), rw.cpu().numpy(), hw,
+                                                       want_routed=True)
+    err = rel_l2(bf16_to_f32(bits(out)), bf16_to_f32(want))
+    assert err < REL_L2, err
+    assert np.abs(bf16_to_f32(want)).max() > 0
+    # unreduced form on a runner sharing the first one's scratch
+    second = gm.Nvfp4ExpertRunner(w, max(tokens, 2), shared_scratch=runner)
+    second.launch_batch_unreduced(dx, ids, tokens)
+    second.check()
+    assert (second.inverse_routes().cpu().numpy() == want_inverse).all()
+    routed = second.routed_output()
+    assert rel_l2(bf16_to_f32(bits(routed)), bf16_to_f32(want_routed)) < REL_L2
+    # reducing the exposed buffer by hand reproduces launch_batch bit for bit
+    manual = oracle.reduce(bits(routed), rw.cpu().numpy(), want_inverse, tokens)
+    assert (manual == bits(out)).all()
+
+
+def test_full_size_properties(gm, weights, cuda_device):
+    """4096 tokens (the prefill configuration's size): properties that need no oracle."""
+    from gevva_b200 import runtime as rt
+    w, _ = weights
+    tokens = 4096
+    x = hashgen.activations(tokens, HIDDEN, 51, cuda_device)
+    router_w = (hashgen.hash_uniform(EXPERTS * HIDDEN, 5, cuda_device) * 0.0346).view(EXPERTS, HIDDEN)
+    bias = hashgen.hash_uniform(EXPERTS, 6, cuda_device) * 0.9
+    logits = (x.float() @ router_w.t() + bias).to(torch.bfloat16)
+    rw, ids = gm.route_128_top8(logits, torch.ones(EXPERTS, dtype=torch.bfloat16, device=cuda_device))
+    # top-8 really are the eight largest, in order
+    top = torch.gather(logits.float(), 1, ids.long())
+    assert (top[:, :-1] >= top[:, 1:]).all()
+    kth = torch.topk(logits.float(), TOP_K, dim=1).values[:, -1]
+    assert (top[:, -1] == kth).all()
+    assert torch.allclose(rw.sum(1), torch.ones(tokens, device=cuda_device), atol=1e-5)
+    runner = gm.Nvfp4ExpertRunner(w, tokens)
+    out = torch.empty_like(x)
+    runner.launch_batch(x, ids, rw, out, tokens)
+    runner.check()
+    routes = tokens * TOP_K
+    se = runner.buffer(rt.BUF_SORTED_EXPERTS, torch.int32)[:routes]
+    sr = runner.buffer(rt.BUF_SORTED_ROUTES, torch.int32)[:routes].long()
+    inv = runner.inverse_routes().long()
+    assert (se[1:] >= se[:-1]).all()                                   # sortedness
+    assert (inv[sr] == torch.arange(routes, device=cuda_device)).all()  # inverse permutation
+    assert (ids.reshape(-1)[sr] == se).all()
+    same = se[1:] == se[:-1]
+    assert (sr[1:][same] > sr[:-1][same]).all()                        # stability
+    assert torch.isfinite(out.float()).all() and out.float().abs().max() > 0
+    # run-to-run repeatability (the reference's own hot-path test, src/nvfp4_cutlass.cu:1940-2052)
+    out2 = torch.empty_like(x)
+    runner.launch_batch(x, ids, rw, out2, tokens)
+    assert torch.equal(out, out2)
+    # batch invariance: a token's result does not depend on what else is in the batch
+    small = gm.Nvfp4ExpertRunner(w, 16)
+    out3 = torch.empty((16, HIDDEN), dtype=torch.bfloat16, device=cuda_device)
+    small.launch_batch(x[:16].contiguous(), ids[:16].contiguous(), rw[:16].contiguous(), out3, 16)
+    small.check()
+    assert torch.equal(out3, out[:16])

@@ -270,3 +270,34 @@ def pack_experts(weights_fp32, stream=None):
     if status != 0:
         raise GevvaMoeError(status, "pack_experts")
     return codes, scales, global_scales
+
+
+def route_sort_noalloc(expert_ids, stream=None):
+    """Sorts routes without any device allocation inside the library.
+
+    For callers that may not allocate on this path: the library's working memory is a
+    fixed array in its own image (at most 16384 tokens), and every output is a tensor
+    made here by the caller's allocator.  Returns a dict of int32 tensors:
+    sorted_experts, sorted_routes, inverse_routes [8*tokens]; expert_offsets,
+    scale_row_offsets [129]; status [1] (1 if an id was outside [0,128))."""
+    lib = library()
+    vp = ctypes.c_void_p
+    lib.gevva_moe_route_sort_noalloc.argtypes = [vp, ctypes.c_int, vp, vp, vp, vp, vp, vp, vp]
+    lib.gevva_moe_route_sort_noalloc.restype = ctypes.c_int
+    tokens = expert_ids.shape[0]
+    _check(expert_ids, torch.int32, (tokens, TOP_K), "expert_ids")
+    device = expert_ids.device
+    routes = tokens * TOP_K
+    out = {name: torch.empty(routes, dtype=torch.int32, device=device)
+           for name in ("sorted_experts", "sorted_routes", "inverse_routes")}
+    out["expert_offsets"] = torch.empty(EXPERTS + 1, dtype=torch.int32, device=device)
+    out["scale_row_offsets"] = torch.empty(EXPERTS + 1, dtype=torch.int32, device=device)
+    out["status"] = torch.zeros(1, dtype=torch.int32, device=device)
+    with torch.cuda.device(device):
+        status = lib.gevva_moe_route_sort_noalloc(
+            _ptr(expert_ids), tokens, _ptr(out["sorted_experts"]), _ptr(out["sorted_routes"]),
+            _ptr(out["inverse_routes"]), _ptr(out["expert_offsets"]),
+            _ptr(out["scale_row_offsets"]), _ptr(out["status"]), _stream_handle(stream))
+    if status != 0:
+        raise GevvaMoeError(status, "route_sort_noalloc")
+    return out

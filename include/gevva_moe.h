@@ -139,6 +139,24 @@ enum gevva_moe_buffer_id {
 
 int gevva_moe_buffer(const gevva_moe* runner, int buffer_id, void** device_ptr, size_t* bytes);
 
+/* Route sort for callers that cannot allocate device memory on this path: a server
+ * whose arena took all device memory at start-up, a serving loop that may not stall on
+ * cudaMalloc's device-wide synchronisation, a plug-in bound to its host's allocator.  It has
+ * no counterpart in the reference, whose sort always works in ExpertScratch.  Same
+ * results as the sort stage of gevva_moe_launch, but the working memory is a fixed
+ * array inside the library (about 69 KiB per GPU, held until exit) instead of a
+ * runner's scratch, and the caller supplies every output:
+ *   sorted_experts, sorted_routes, inverse_routes  i32 [8*tokens]
+ *   expert_offsets, scale_row_offsets               i32 [129]
+ *   status   i32 [1], zeroed by the caller; set to 1 if an id is outside [0,128)
+ * Limits: 1 <= tokens <= 16384, else GEVVA_MOE_TOO_LARGE.  All calls on a device share
+ * the array, so calls that may overlap on the GPU race; order them on one stream.
+ * The first call on each device resolves the array's address: make it before any
+ * stream capture.  Calls no allocating routine. */
+int gevva_moe_route_sort_noalloc(const int* expert_ids, int tokens, int* sorted_experts,
+                                 int* sorted_routes, int* inverse_routes, int* expert_offsets,
+                                 int* scale_row_offsets, int* status, gevva_stream_t stream);
+
 /* Expert packer for synthetic or freshly quantised weights; stands where
  * tools/pack_trtllm_experts.py:51-65 stands in the reference (stack experts,
  * interleave block scales) and also performs the NVFP4 quantisation itself:

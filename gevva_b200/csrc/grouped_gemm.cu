@@ -33,8 +33,10 @@ constexpr int kStages = 5;
 constexpr int kAccStages = 2;
 constexpr int kGemmThreads = 192;
 constexpr uint32_t kTmemColumns = 512;
-constexpr uint32_t kSfaColumn = kAccStages * kTileN;  // 256
-constexpr uint32_t kSfbColumn = kSfaColumn + 16;      // 272
+// Scale-factor columns are per pipeline stage: a copy for K block k+1 must not wait for
+// the MMAs of K block k to finish reading theirs.
+constexpr uint32_t kSfColumn = kAccStages * kTileN;   // 256; stage s uses [256+32s, 256+32s+32)
+constexpr uint32_t kSfColumnsPerStage = 32;           // 16 for A then 16 for B
 constexpr int kOperandStageBytes = kTileM * kTileKBytes;  // 16 KiB, same for A and B
 
 struct alignas(1024) GemmSmem {
@@ -75,15 +77,20 @@ struct GemmParams {
   int last_mmas;    // MMAs (K = 64 each) in the last K block, 1..4
 };
 
+// Bounded wait on an mbarrier.  The time limit is kept with the SM's cycle counter (a
+// cheap register read); it is consulted only every 1024 failed polls so that a short
+// stall costs nothing but the polls themselves.
+constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s at 2 GHz
+
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, GemmSmem* smem,
                                               int* status) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t start = global_timer_ns();
+  const long long start = clock64();
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 63u) == 0) {
+    if ((spin & 1023u) == 0) {
       if (smem->abort) return false;
-      if (global_timer_ns() - start > 1000000000ull) {
+      if (clock64() - start > kWaitLimitCycles) {
         smem->abort = 1;
         atomicExch(status, static_cast<int>(kWaitTimeout));
         return false;
@@ -91,6 +98,86 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Ge
     }
   }
 }
+
+
+// One K block's worth of tensor-core work issued as a single instruction sequence:
+// kMmas scale-factor atom copies per operand (shared -> tensor memory) followed by kMmas
+// MMAs of K = 64.  Everything is derived from four 32-bit descriptor bases with immediate
+// offsets so the issuing thread spends a handful of integer instructions per MMA; that
+// thread's instruction latency is what bounds the main loop otherwise.
+//   a_lo / b_lo     low words of the operand descriptors of this stage (address >> 4)
+//   sfa_lo / sfb_lo low words of the scale-factor descriptors of this stage
+//   hi_ab / hi_sf   high words (stride, version, swizzle) shared by all stages
+template <int kMmas>
+__device__ __forceinline__ void issue_k_block(uint32_t tmem_acc, uint32_t tmem_sf, uint32_t a_lo,
+                                              uint32_t b_lo, uint32_t sfa_lo, uint32_t sfb_lo,
+                                              uint32_t hi_ab, uint32_t hi_sf, uint32_t accumulate) {
+  static_assert(kMmas >= 1 && kMmas <= 4, "a K block holds one to four MMAs");
+#define GV_SF_COPY(j)                                                      \
+  "add.u32 lo, %4, " #j "*32;\n\t"                                         \
+  "mov.b64 d0, {lo, %7};\n\t"                                              \
+  "add.u32 ta, %1, " #j "*4;\n\t"                                          \
+  "tcgen05.cp.cta_group::1.32x128b.warpx4 [ta], d0;\n\t"                   \
+  "add.u32 lo, %5, " #j "*32;\n\t"                                         \
+  "mov.b64 d0, {lo, %7};\n\t"                                              \
+  "add.u32 ta, %1, 16+" #j "*4;\n\t"                                       \
+  "tcgen05.cp.cta_group::1.32x128b.warpx4 [ta], d0;\n\t"
+#define GV_MMA(j, pred)                                                    \
+  "add.u32 lo, %2, " #j "*2;\n\t"                                          \
+  "mov.b64 d0, {lo, %6};\n\t"                                              \
+  "add.u32 lo, %3, " #j "*2;\n\t"                                          \
+  "mov.b64 d1, {lo, %6};\n\t"                                              \
+  "add.u32 ta, %1, " #j "*4;\n\t"                                          \
+  "add.u32 tb, %1, 16+" #j "*4;\n\t"                                       \
+  "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X"      \
+  " [%0], d0, d1, %8, [ta], [tb], " pred ";\n\t"
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, pt;\n\t"
+      ".reg .b32 lo, ta, tb;\n\t"
+      ".reg .b64 d0, d1;\n\t"
+      "setp.ne.b32 p, %9, 0;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      GV_SF_COPY(0)
+      GV_MMA(0, "p")
+      "}"
+      ::"r"(tmem_acc), "r"(tmem_sf), "r"(a_lo), "r"(b_lo), "r"(sfa_lo), "r"(sfb_lo), "r"(hi_ab),
+        "r"(hi_sf), "r"(kInstrDesc), "r"(accumulate)
+      : "memory");
+  if constexpr (kMmas >= 2)
+    asm volatile("{\n\t.reg .pred pt;\n\t.reg .b32 lo, ta, tb;\n\t.reg .b64 d0, d1;\n\t"
+                 "setp.eq.b32 pt, 0, 0;\n\t" GV_SF_COPY(1) GV_MMA(1, "pt") "}"
+                 ::"r"(tmem_acc), "r"(tmem_sf), "r"(a_lo), "r"(b_lo), "r"(sfa_lo), "r"(sfb_lo),
+                   "r"(hi_ab), "r"(hi_sf), "r"(kInstrDesc), "r"(accumulate)
+                 : "memory");
+  if constexpr (kMmas >= 3)
+    asm volatile("{\n\t.reg .pred pt;\n\t.reg .b32 lo, ta, tb;\n\t.reg .b64 d0, d1;\n\t"
+                 "setp.eq.b32 pt, 0, 0;\n\t" GV_SF_COPY(2) GV_MMA(2, "pt") "}"
+                 ::"r"(tmem_acc), "r"(tmem_sf), "r"(a_lo), "r"(b_lo), "r"(sfa_lo), "r"(sfb_lo),
+                   "r"(hi_ab), "r"(hi_sf), "r"(kInstrDesc), "r"(accumulate)
+                 : "memory");
+  if constexpr (kMmas >= 4)
+    asm volatile("{\n\t.reg .pred pt;\n\t.reg .b32 lo, ta, tb;\n\t.reg .b64 d0, d1;\n\t"
+                 "setp.eq.b32 pt, 0, 0;\n\t" GV_SF_COPY(3) GV_MMA(3, "pt") "}"
+                 ::"r"(tmem_acc), "r"(tmem_sf), "r"(a_lo), "r"(b_lo), "r"(sfa_lo), "r"(sfb_lo),
+                   "r"(hi_ab), "r"(hi_sf), "r"(kInstrDesc), "r"(accumulate)
+                 : "memory");
+#undef GV_SF_COPY
+#undef GV_MMA
+}
+
+#if defined(GV_TRACE)
+// Debug build only: timestamps of CTA 0's roles, read back by gv_trace_read().
+__device__ long long g_trace[3][4096];
+__device__ int g_trace_count[3];
+#define GV_STAMP(role)                                                        \
+  do {                                                                        \
+    if (blockIdx.x == 0 && g_trace_count[role] < 4096)                        \
+      g_trace[role][g_trace_count[role]++] = clock64();                       \
+  } while (0)
+#else
+#define GV_STAMP(role) do {} while (0)
+#endif
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
@@ -146,6 +233,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
             ok = false;
             break;
           }
+          GV_STAMP(0);
           const uint32_t sf_bytes =
               (kb == p.k_blocks - 1 ? p.last_mmas : 4) * static_cast<uint32_t>(kSfAtomBytes);
           mbar_arrive_expect_tx(&smem->full[stage], 2u * kOperandStageBytes + 2u * sf_bytes);
@@ -155,6 +243,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                        &smem->full[stage]);
           bulk_load_1d(smem->sfb[stage], sfb_src + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes,
                        &smem->full[stage]);
+          GV_STAMP(0);
           ++issued;
           if (++stage == kStages) {
             stage = 0;
@@ -172,57 +261,73 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
             s = kStages - 1;
             ph ^= 1u;
           }
-          mbar_wait_bounded(&smem->full[s], ph, 20000000ull);
+          mbar_wait_bounded(&smem->full[s], ph, 40000000ll);
         }
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      int acc_stage = 0;
-      uint32_t acc_phase = 0;
+    // The whole warp walks the loop so that every address below is warp-uniform; one
+    // elected lane (always the same one) issues the tcgen05 instructions, which keeps
+    // their program order.
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc_stage = 0;
+    uint32_t acc_phase = 0;
+    // Descriptor words (sm_100 shared-memory descriptor): low word = address >> 4; high
+    // word = stride >> 4 | version 1 at bit 14 | swizzle mode at bits 29..31.
+    const uint32_t a_lo0 = (smem_u32(smem->a[0]) & 0x3ffffu) >> 4;
+    const uint32_t b_lo0 = (smem_u32(smem->b[0]) & 0x3ffffu) >> 4;
+    const uint32_t sfa_lo0 = (smem_u32(smem->sfa[0]) & 0x3ffffu) >> 4;
+    const uint32_t sfb_lo0 = (smem_u32(smem->sfb[0]) & 0x3ffffu) >> 4;
+    constexpr uint32_t hi_ab = (1024u >> 4) | (1u << 14) | (2u << 29);  // 8 rows x 128 B, 128B swizzle
+    constexpr uint32_t hi_sf = (128u >> 4) | (1u << 14);                // 8 rows x 16 B, no swizzle
+    const bool full_last = p.last_mmas == 4;
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+      if (!__all_sync(0xffffffffu,
+                      wait_or_abort(&smem->acc_empty[acc_stage], acc_phase ^ 1u, smem, p.status)))
+        break;
+      tc_fence_after_sync();
+      const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc_stage * kTileN);
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
-        if (!wait_or_abort(&smem->acc_empty[acc_stage], acc_phase ^ 1u, smem, p.status)) break;
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        ok = __all_sync(0xffffffffu, wait_or_abort(&smem->full[stage], phase, smem, p.status));
+        if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc_stage * kTileN);
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!wait_or_abort(&smem->full[stage], phase, smem, p.status)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after_sync();
-          const int mmas = kb == p.k_blocks - 1 ? p.last_mmas : 4;
-          const uint32_t sfa_addr = smem_u32(smem->sfa[stage]);
-          const uint32_t sfb_addr = smem_u32(smem->sfb[stage]);
-          for (int j = 0; j < mmas; ++j) {
-            tc_copy_sf(tmem_base + kSfaColumn + 4u * j,
-                       make_smem_desc(sfa_addr + j * kSfAtomBytes, 128, 0));
-            tc_copy_sf(tmem_base + kSfbColumn + 4u * j,
-                       make_smem_desc(sfb_addr + j * kSfAtomBytes, 128, 0));
-          }
-          const uint64_t desc_a = make_smem_desc(smem_u32(smem->a[stage]), 1024, 2);
-          const uint64_t desc_b = make_smem_desc(smem_u32(smem->b[stage]), 1024, 2);
-          for (int j = 0; j < mmas; ++j) {
-            // 64 FP4 elements = 32 bytes along K inside the swizzle row: +2 in 16-byte units
-            tc_mma_nvfp4(tmem_acc, desc_a + 2u * j, desc_b + 2u * j, kInstrDesc,
-                         tmem_base + kSfaColumn + 4u * j, tmem_base + kSfbColumn + 4u * j,
-                         (kb | j) != 0 ? 1u : 0u);
+        // Descriptor low words advance by whole stages; the K offset of each MMA (+32 bytes
+        // inside the swizzle row) and each scale atom (+512 bytes) are immediates.
+        const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * (kOperandStageBytes >> 4);
+        const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(stage) * (kOperandStageBytes >> 4);
+        const uint32_t sfa_lo = sfa_lo0 + static_cast<uint32_t>(stage) * (kSfStageBytes >> 4);
+        const uint32_t sfb_lo = sfb_lo0 + static_cast<uint32_t>(stage) * (kSfStageBytes >> 4);
+        const uint32_t tmem_sf = tmem_base + kSfColumn + kSfColumnsPerStage * stage;
+        const uint32_t accumulate = kb != 0 ? 1u : 0u;
+        if (elect_one()) {
+          GV_STAMP(1);
+          if (kb != p.k_blocks - 1 || full_last) {
+            issue_k_block<4>(tmem_acc, tmem_sf, a_lo, b_lo, sfa_lo, sfb_lo, hi_ab, hi_sf, accumulate);
+          } else if (p.last_mmas == 3) {
+            issue_k_block<3>(tmem_acc, tmem_sf, a_lo, b_lo, sfa_lo, sfb_lo, hi_ab, hi_sf, accumulate);
+          } else if (p.last_mmas == 2) {
+            issue_k_block<2>(tmem_acc, tmem_sf, a_lo, b_lo, sfa_lo, sfb_lo, hi_ab, hi_sf, accumulate);
+          } else {
+            issue_k_block<1>(tmem_acc, tmem_sf, a_lo, b_lo, sfa_lo, sfb_lo, hi_ab, hi_sf, accumulate);
           }
           tc_commit(&smem->empty[stage]);  // frees the stage once these MMAs have read it
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
+          GV_STAMP(1);
         }
-        if (!ok) break;
-        tc_commit(&smem->acc_full[acc_stage]);
-        if (++acc_stage == kAccStages) {
-          acc_stage = 0;
-          acc_phase ^= 1u;
+        __syncwarp();
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
         }
+      }
+      if (!ok) break;
+      if (elect_one()) tc_commit(&smem->acc_full[acc_stage]);
+      __syncwarp();
+      if (++acc_stage == kAccStages) {
+        acc_stage = 0;
+        acc_phase ^= 1u;
       }
     }
   } else {
@@ -240,6 +345,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       const float alpha = p.alpha[expert];
       if (!wait_or_abort(&smem->acc_full[acc_stage], acc_phase, smem, p.status)) break;
       tc_fence_after_sync();
+      if (threadIdx.x == 64) GV_STAMP(2);
       const int row_local = quarter * 32 + lane;
       const bool valid = row_local < rows_valid;
       __nv_bfloat16* dst = p.out + static_cast<size_t>(row0 + row_local) * p.n_out + n_tile * kTileN;
@@ -267,6 +373,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       }
       tc_fence_before_sync();
       mbar_arrive(&smem->acc_empty[acc_stage]);
+      if (threadIdx.x == 64) GV_STAMP(2);
       if (++acc_stage == kAccStages) {
         acc_stage = 0;
         acc_phase ^= 1u;
@@ -283,6 +390,15 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
 }
 
 }  // namespace
+
+#if defined(GV_TRACE)
+extern "C" void gv_trace_read(long long* out, int* counts) {
+  cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace));
+  cudaMemcpyFromSymbol(counts, g_trace_count, sizeof(g_trace_count));
+  int zero[3] = {0, 0, 0};
+  cudaMemcpyToSymbol(g_trace_count, zero, sizeof(zero));
+}
+#endif
 
 int prepare_grouped_gemm() {
   return static_cast<int>(cudaFuncSetAttribute(grouped_nvfp4_gemm_kernel,

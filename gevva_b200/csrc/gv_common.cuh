@@ -99,6 +99,20 @@ __device__ __forceinline__ uint32_t smem_u32(const void* ptr) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(ptr));
 }
 
+// True in exactly one lane of a fully active warp (the same lane every time).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t elected;
+  asm volatile(
+      "{\n\t"
+      ".reg .b32 leader;\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync leader|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(elected));
+  return elected != 0;
+}
+
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -133,15 +147,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return done != 0;
 }
 
-// Bounded wait: gives up after `limit_ns` of wall time and reports false.  The
+// Bounded wait: gives up after `limit_cycles` SM clock cycles and reports false.  The
 // caller records the failure in the status word and unwinds; nothing spins forever.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
-                                                  uint64_t limit_ns = 2000000000ull) {
+                                                  long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t start = global_timer_ns();
+  const long long start = clock64();
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 255u) == 0 && global_timer_ns() - start > limit_ns) return false;
+    if ((spin & 255u) == 0 && clock64() - start > limit_cycles) return false;
   }
 }
 

@@ -3,8 +3,8 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 One step = one pass of the layer over one batch: router projection (library GEMM,
-as in the reference), route_128_top8, route sort, NVFP4 quantise, grouped w13 GEMM,
-GeGLU+requantise, grouped w2 GEMM, weighted reduce.  Workload at every N: the
+as in the reference), route_128_top8, route sort, NVFP4 quantise, grouped w13 GEMM with
+GeGLU+requantise in its epilogue, grouped w2 GEMM, weighted reduce.  Workload at every N: the
 prefill configuration, 4096 tokens per GPU with a per-expert router bias ~N(0, 0.5).
 Prints one JSON line (rank 0).
 """
@@ -255,9 +255,8 @@ def run_gpu(args):
         gevva_b200.route_128_top8(logits, layer.expert_scale, weights=weights, ids=ids)
         runner.launch_stages(rt.STAGE_SORT | rt.STAGE_QUANTIZE, TOKENS, input=x, expert_ids=ids)
         g0[i].record()
-        runner.launch_stages(rt.STAGE_W13, TOKENS)
+        runner.launch_stages(rt.STAGE_W13 | rt.STAGE_GEGLU, TOKENS)  # one kernel: GeGLU in the epilogue
         g1[i].record()
-        runner.launch_stages(rt.STAGE_GEGLU, TOKENS)
         h0[i].record()
         runner.launch_stages(rt.STAGE_W2, TOKENS)
         h1[i].record()
@@ -277,7 +276,7 @@ def run_gpu(args):
         achieved = W13_FLOP_PER_TOKEN * TOKENS / (w13_ms * 1e-3) / 1e12
         total_tokens = TOKENS * world * args.steps
         value = total_tokens / (elapsed_ms * 1e-3)
-        launches_per_step = 9  # route, 3 sort kernels, quantise, w13, geglu, w2, reduce
+        launches_per_step = 8  # route, 3 sort kernels, quantise, w13 (+GeGLU), w2, reduce
         line = {
             "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -289,7 +288,7 @@ def run_gpu(args):
                        "parallelism": "single GPU" if world == 1 else f"{world} data-parallel replicas",
                        "l2": "inputs larger than L2: 428 MB of expert weights stream every step"},
             "layer_tflops": FLOP_PER_TOKEN * TOKENS / (elapsed_ms / args.steps * 1e-3) / 1e12,
-            "roofline": {"bound": "tensor", "kernel": "grouped_nvfp4_gemm_kernel (w13)",
+            "roofline": {"bound": "tensor", "kernel": "grouped_nvfp4_gemm_kernel<kGeglu> (w13 + GeGLU + requantise)",
                          "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s",
                          "frac": achieved / fp4_peak, "traffic": None,
                          "peak_source": f"4 x bf16_tflops of MEASURED_PEAKS.json ({peak_kind}); "

@@ -5,20 +5,34 @@
 // Replaces the reference's CUTLASS SM120 grouped GEMM
 // (src/nvfp4_cutlass.cu:81-100 traits, :755-962 plan, :913-930 run):
 //   D_e[r, n] = bf16(alpha[e] * sum_k A[r,k] sfa[r,k/16] B_e[n,k] sfb_e[n,k/16])
-// for the rows r of each expert e, over all 128 experts in one launch.
+// for the rows r of each expert e, over all 128 experts in one launch, and, in its
+// fused form, also the reference's geglu_quantize_sorted_moe (:552-601) applied to
+// the accumulators before anything is written.
 //
 // Mapping.  Tokens (sorted routes) sit on MMA-M, weight rows on MMA-N.  A work
 // item is (128-row tile of one expert) x (128 weight rows).  Row tiles are listed
 // in device memory by the route sort; CTAs are persistent and take items
 // round-robin.  Warp 0 is the TMA producer, warp 1 allocates tensor memory and
-// issues the MMAs, warps 2..5 drain accumulators (two accumulator stages, so the
-// epilogue of one item overlaps the main loop of the next).
+// issues the MMAs, warps 2..17 drain accumulators (two accumulator stages, so the
+// epilogue of one item overlaps the main loop of the next).  Warps 0 and 1 walk
+// their loops as whole warps (warp-uniform addresses) and one elected lane issues.
+//
+// Two epilogues:
+//   kPlain  bf16(alpha*acc), staged through shared memory so that every global
+//           store instruction writes two full 256-byte row segments;
+//   kGeglu  the 128 weight rows of an item are up rows [64j,64j+64) and gate rows
+//           [704+64j, 704+64j+64) of w13, so a thread holds up and gate of the same
+//           64 columns: v = gelu_erf(bf16(gate)) * bf16(up), four 16-value blocks ->
+//           32 code bytes and one 4-byte scale word per row, written straight into the
+//           w2 operand buffers.  The bf16 w13 output never exists in memory.
 //
 // Scale factors.  Both operands keep scales in the 128-row x 4-scale atoms of
 // 512 bytes (row%32)*16 + (row/32)*4 + k that the reference writes
 // (src/nvfp4_cutlass.cu:321-323); one atom is exactly what one MMA (K = 64)
 // consumes and what tcgen05.cp 32x128b.warpx4 moves, so a K block of 256 needs a
-// contiguous 2 KiB per operand, fetched with one untiled bulk copy.
+// contiguous 2 KiB per operand, fetched with one untiled bulk copy.  For kGeglu the
+// weight scales come from a copy re-tiled once at runner creation so that the
+// [64 up | 64 gate] rows of an item form such atoms (retile_w13_scales_kernel below).
 //
 // Every wait is bounded: on expiry the kernel records kWaitTimeout in the status
 // word, all roles leave their loops, tensor memory is released and the CTA exits.
@@ -31,19 +45,26 @@ namespace {
 
 constexpr int kStages = 5;
 constexpr int kAccStages = 2;
-constexpr int kGemmThreads = 192;
+constexpr int kEpilogueWarpsPerQuarter = 4;  // each takes a quarter of a tile's columns
+constexpr int kEpilogueThreads = 4 * kEpilogueWarpsPerQuarter * 32;
+constexpr int kGemmThreads = 64 + kEpilogueThreads;  // producer warp, MMA warp, epilogue warps
 constexpr uint32_t kTmemColumns = 512;
 // Scale-factor columns are per pipeline stage: a copy for K block k+1 must not wait for
 // the MMAs of K block k to finish reading theirs.
 constexpr uint32_t kSfColumn = kAccStages * kTileN;   // 256; stage s uses [256+32s, 256+32s+32)
 constexpr uint32_t kSfColumnsPerStage = 32;           // 16 for A then 16 for B
 constexpr int kOperandStageBytes = kTileM * kTileKBytes;  // 16 KiB, same for A and B
+constexpr int kStageRowBytes = kTileN * 2;                // one bf16 output row of a tile
+constexpr int kStagingBytesPerWarp = 32 * kStageRowBytes; // 8 KiB
+
+enum GemmMode { kPlain = 0, kGeglu = 1 };
 
 struct alignas(1024) GemmSmem {
   uint8_t a[kStages][kOperandStageBytes];
   uint8_t b[kStages][kOperandStageBytes];
   uint8_t sfa[kStages][kSfStageBytes];
   uint8_t sfb[kStages][kSfStageBytes];
+  uint8_t staging[4][kStagingBytesPerWarp];  // kPlain epilogue only
   uint64_t full[kStages];
   uint64_t empty[kStages];
   uint64_t acc_full[kAccStages];
@@ -53,6 +74,7 @@ struct alignas(1024) GemmSmem {
 };
 
 constexpr size_t kGemmSmemBytes = sizeof(GemmSmem) + 1024;  // slack for manual alignment
+static_assert(kGemmSmemBytes <= 232448, "shared memory budget of one sm_100 CTA");
 
 // Instruction descriptor: E2M1 x E2M1 (format 1 in the mxf4 kinds), both K-major,
 // UE4M3 scales (bit 23 clear), N at [17,23) in units of 8, M at [24,29) in units of 16,
@@ -62,16 +84,19 @@ constexpr uint32_t kInstrDesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(
 
 struct GemmParams {
   const uint8_t* a_scales;
-  const uint8_t* b_scales;
+  const uint8_t* b_scales;   // kPlain: sidecar layout; kGeglu: re-tiled copy
   const float* alpha;
-  __nv_bfloat16* out;
+  __nv_bfloat16* out;        // kPlain
+  uint8_t* next_codes;       // kGeglu: w2 operand codes [rows, 352]
+  uint8_t* next_scales;      // kGeglu: w2 operand scale regions
+  const float* next_scale_q; // kGeglu: g2.input_scale_quant [128]
   const int* tile_expert;
   const int* expert_offsets;
   const int* scale_row_offsets;
   const int* num_m_tiles;
   int* status;
   int n_out;
-  int n_tiles;      // n_out / 128
+  int n_tiles;      // work items per row tile
   int groups;       // k_in / 16
   int k_blocks;     // ceil(k_in / 256)
   int last_mmas;    // MMAs (K = 64 each) in the last K block, 1..4
@@ -98,7 +123,6 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Ge
     }
   }
 }
-
 
 // One K block's worth of tensor-core work issued as a single instruction sequence:
 // kMmas scale-factor atom copies per operand (shared -> tensor memory) followed by kMmas
@@ -131,39 +155,20 @@ __device__ __forceinline__ void issue_k_block(uint32_t tmem_acc, uint32_t tmem_s
   "add.u32 tb, %1, 16+" #j "*4;\n\t"                                       \
   "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X"      \
   " [%0], d0, d1, %8, [ta], [tb], " pred ";\n\t"
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p, pt;\n\t"
-      ".reg .b32 lo, ta, tb;\n\t"
-      ".reg .b64 d0, d1;\n\t"
-      "setp.ne.b32 p, %9, 0;\n\t"
-      "setp.eq.b32 pt, 0, 0;\n\t"
-      GV_SF_COPY(0)
-      GV_MMA(0, "p")
-      "}"
-      ::"r"(tmem_acc), "r"(tmem_sf), "r"(a_lo), "r"(b_lo), "r"(sfa_lo), "r"(sfb_lo), "r"(hi_ab),
-        "r"(hi_sf), "r"(kInstrDesc), "r"(accumulate)
-      : "memory");
-  if constexpr (kMmas >= 2)
-    asm volatile("{\n\t.reg .pred pt;\n\t.reg .b32 lo, ta, tb;\n\t.reg .b64 d0, d1;\n\t"
-                 "setp.eq.b32 pt, 0, 0;\n\t" GV_SF_COPY(1) GV_MMA(1, "pt") "}"
-                 ::"r"(tmem_acc), "r"(tmem_sf), "r"(a_lo), "r"(b_lo), "r"(sfa_lo), "r"(sfb_lo),
-                   "r"(hi_ab), "r"(hi_sf), "r"(kInstrDesc), "r"(accumulate)
-                 : "memory");
-  if constexpr (kMmas >= 3)
-    asm volatile("{\n\t.reg .pred pt;\n\t.reg .b32 lo, ta, tb;\n\t.reg .b64 d0, d1;\n\t"
-                 "setp.eq.b32 pt, 0, 0;\n\t" GV_SF_COPY(2) GV_MMA(2, "pt") "}"
-                 ::"r"(tmem_acc), "r"(tmem_sf), "r"(a_lo), "r"(b_lo), "r"(sfa_lo), "r"(sfb_lo),
-                   "r"(hi_ab), "r"(hi_sf), "r"(kInstrDesc), "r"(accumulate)
-                 : "memory");
-  if constexpr (kMmas >= 4)
-    asm volatile("{\n\t.reg .pred pt;\n\t.reg .b32 lo, ta, tb;\n\t.reg .b64 d0, d1;\n\t"
-                 "setp.eq.b32 pt, 0, 0;\n\t" GV_SF_COPY(3) GV_MMA(3, "pt") "}"
-                 ::"r"(tmem_acc), "r"(tmem_sf), "r"(a_lo), "r"(b_lo), "r"(sfa_lo), "r"(sfb_lo),
-                   "r"(hi_ab), "r"(hi_sf), "r"(kInstrDesc), "r"(accumulate)
-                 : "memory");
+#define GV_OPERANDS                                                                            \
+  ::"r"(tmem_acc), "r"(tmem_sf), "r"(a_lo), "r"(b_lo), "r"(sfa_lo), "r"(sfb_lo), "r"(hi_ab),   \
+    "r"(hi_sf), "r"(kInstrDesc), "r"(accumulate)                                               \
+  : "memory"
+#define GV_PROLOGUE "{\n\t.reg .pred p, pt;\n\t.reg .b32 lo, ta, tb;\n\t.reg .b64 d0, d1;\n\t" \
+                    "setp.ne.b32 p, %9, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+  asm volatile(GV_PROLOGUE GV_SF_COPY(0) GV_MMA(0, "p") "}" GV_OPERANDS);
+  if constexpr (kMmas >= 2) asm volatile(GV_PROLOGUE GV_SF_COPY(1) GV_MMA(1, "pt") "}" GV_OPERANDS);
+  if constexpr (kMmas >= 3) asm volatile(GV_PROLOGUE GV_SF_COPY(2) GV_MMA(2, "pt") "}" GV_OPERANDS);
+  if constexpr (kMmas >= 4) asm volatile(GV_PROLOGUE GV_SF_COPY(3) GV_MMA(3, "pt") "}" GV_OPERANDS);
 #undef GV_SF_COPY
 #undef GV_MMA
+#undef GV_OPERANDS
+#undef GV_PROLOGUE
 }
 
 #if defined(GV_TRACE)
@@ -179,6 +184,18 @@ __device__ int g_trace_count[3];
 #define GV_STAMP(role) do {} while (0)
 #endif
 
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&pair);
+}
+
+// bf16 rounding of alpha*acc, returned as float: the value the reference's GEMM
+// epilogue stores and its GeGLU kernel reads back (src/nvfp4_cutlass.cu:582-583).
+__device__ __forceinline__ float round_through_bf16(float alpha, uint32_t acc_bits) {
+  return __bfloat162float(__float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(acc_bits))));
+}
+
+template <int kMode>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                           const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
@@ -195,7 +212,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     }
     for (int s = 0; s < kAccStages; ++s) {
       mbar_init(&smem->acc_full[s], 1);
-      mbar_init(&smem->acc_empty[s], 128);
+      mbar_init(&smem->acc_empty[s], kEpilogueThreads);
     }
     smem->abort = 0;
     fence_barrier_init();
@@ -215,54 +232,67 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      int issued = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
-        const int m_tile = item / p.n_tiles;
-        const int n_tile = item - m_tile * p.n_tiles;
-        const int expert = p.tile_expert[m_tile];
-        const int row0 = p.expert_offsets[expert] + (m_tile * kTileM - p.scale_row_offsets[expert]);
-        const int b_row = expert * p.n_out + n_tile * kTileN;
-        const uint8_t* sfa_src = p.a_scales + static_cast<size_t>(m_tile) * kTileM * p.groups;
-        const uint8_t* sfb_src = p.b_scales + static_cast<size_t>(b_row) * p.groups;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!wait_or_abort(&smem->empty[stage], phase ^ 1u, smem, p.status)) {
-            ok = false;
-            break;
-          }
+    int stage = 0;
+    uint32_t phase = 0;
+    int issued = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+      const int m_tile = item / p.n_tiles;
+      const int n_tile = item - m_tile * p.n_tiles;
+      const int expert = p.tile_expert[m_tile];
+      const int row0 = p.expert_offsets[expert] + (m_tile * kTileM - p.scale_row_offsets[expert]);
+      const uint8_t* sfa_src = p.a_scales + static_cast<size_t>(m_tile) * kTileM * p.groups;
+      int b_row, b_row2 = 0;
+      const uint8_t* sfb_src;
+      if (kMode == kGeglu) {
+        b_row = expert * kW13Out + n_tile * 64;  // up rows; the gate rows lie kInter further on
+        b_row2 = b_row + kInter;
+        sfb_src = p.b_scales + (static_cast<size_t>(expert) * p.n_tiles + n_tile) * kTileN * p.groups;
+      } else {
+        b_row = expert * p.n_out + n_tile * kTileN;
+        sfb_src = p.b_scales + static_cast<size_t>(b_row) * p.groups;
+      }
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        ok = __all_sync(0xffffffffu, wait_or_abort(&smem->empty[stage], phase ^ 1u, smem, p.status));
+        if (!ok) break;
+        if (elect_one()) {
           GV_STAMP(0);
           const uint32_t sf_bytes =
               (kb == p.k_blocks - 1 ? p.last_mmas : 4) * static_cast<uint32_t>(kSfAtomBytes);
           mbar_arrive_expect_tx(&smem->full[stage], 2u * kOperandStageBytes + 2u * sf_bytes);
           tma_load_2d(smem->a[stage], &map_a, &smem->full[stage], kb * kTileKBytes, row0);
-          tma_load_2d(smem->b[stage], &map_b, &smem->full[stage], kb * kTileKBytes, b_row);
+          if (kMode == kGeglu) {
+            tma_load_2d(smem->b[stage], &map_b, &smem->full[stage], kb * kTileKBytes, b_row);
+            tma_load_2d(smem->b[stage] + kOperandStageBytes / 2, &map_b, &smem->full[stage],
+                        kb * kTileKBytes, b_row2);
+          } else {
+            tma_load_2d(smem->b[stage], &map_b, &smem->full[stage], kb * kTileKBytes, b_row);
+          }
           bulk_load_1d(smem->sfa[stage], sfa_src + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes,
                        &smem->full[stage]);
           bulk_load_1d(smem->sfb[stage], sfb_src + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes,
                        &smem->full[stage]);
           GV_STAMP(0);
-          ++issued;
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
+        }
+        __syncwarp();
+        ++issued;
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
         }
       }
-      if (!ok) {
-        // Unwinding: let the copies already issued land before shared memory is given up.
-        const int pending = issued < kStages ? issued : kStages;
-        int s = stage;
-        uint32_t ph = phase;
-        for (int i = 0; i < pending; ++i) {
-          if (--s < 0) {
-            s = kStages - 1;
-            ph ^= 1u;
-          }
-          mbar_wait_bounded(&smem->full[s], ph, 40000000ll);
+    }
+    if (!ok && lane == 0) {
+      // Unwinding: let the copies already issued land before shared memory is given up.
+      const int pending = issued < kStages ? issued : kStages;
+      int s = stage;
+      uint32_t ph = phase;
+      for (int i = 0; i < pending; ++i) {
+        if (--s < 0) {
+          s = kStages - 1;
+          ph ^= 1u;
         }
+        mbar_wait_bounded(&smem->full[s], ph, 40000000ll);
       }
     }
   } else if (warp == 1) {
@@ -331,10 +361,14 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       }
     }
   } else {
-    // ---------------- epilogue: warps 2..5, one 32-lane quarter each ----------------
+    // ---------------- epilogue: 16 warps ----------------
+    // A warp may touch only the tensor-memory lanes 32*(warp%4)..+31, so the four warps
+    // with the same warp%4 share one 32-row quarter of the tile and split its columns.
     const int quarter = warp & 3;
+    const int sub = (warp - 2) >> 2;  // 0..3
     int acc_stage = 0;
     uint32_t acc_phase = 0;
+    uint8_t* staging = smem->staging[quarter];
     for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
       const int m_tile = item / p.n_tiles;
       const int n_tile = item - m_tile * p.n_tiles;
@@ -347,32 +381,74 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       tc_fence_after_sync();
       if (threadIdx.x == 64) GV_STAMP(2);
       const int row_local = quarter * 32 + lane;
-      const bool valid = row_local < rows_valid;
-      __nv_bfloat16* dst = p.out + static_cast<size_t>(row0 + row_local) * p.n_out + n_tile * kTileN;
       const uint32_t tmem_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                 static_cast<uint32_t>(acc_stage * kTileN);
-#pragma unroll 1
-      for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
+      if (kMode == kPlain) {
+        // This warp's 32 rows x 32 columns go to the quarter's staging tile (32 rows x 256
+        // bytes).  16-byte chunk c of row r lives at chunk position c ^ (r & 15), which keeps
+        // the row-wise writes here and the two-rows-per-instruction reads below at the
+        // minimum number of bank passes.
         uint32_t r[32];
-        tmem_load_32x32(tmem_row + chunk * 32, r);
+        tmem_load_32x32(tmem_row + sub * 32, r);
         tmem_load_wait();
-        if (valid) {
-          uint32_t packed[16];
+        tc_fence_before_sync();
+        mbar_arrive(&smem->acc_empty[acc_stage]);  // accumulators are in registers now
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const __nv_bfloat162 pair =
-                __floats2bfloat162_rn(__fmul_rn(alpha, __uint_as_float(r[2 * i])),
-                                      __fmul_rn(alpha, __uint_as_float(r[2 * i + 1])));
-            packed[i] = *reinterpret_cast<const uint32_t*>(&pair);
-          }
-          uint4* out16 = reinterpret_cast<uint4*>(dst + chunk * 32);
+        for (int i = 0; i < 4; ++i) {
+          uint4 v;
+          v.x = pack_bf16x2(__fmul_rn(alpha, __uint_as_float(r[8 * i])),
+                            __fmul_rn(alpha, __uint_as_float(r[8 * i + 1])));
+          v.y = pack_bf16x2(__fmul_rn(alpha, __uint_as_float(r[8 * i + 2])),
+                            __fmul_rn(alpha, __uint_as_float(r[8 * i + 3])));
+          v.z = pack_bf16x2(__fmul_rn(alpha, __uint_as_float(r[8 * i + 4])),
+                            __fmul_rn(alpha, __uint_as_float(r[8 * i + 5])));
+          v.w = pack_bf16x2(__fmul_rn(alpha, __uint_as_float(r[8 * i + 6])),
+                            __fmul_rn(alpha, __uint_as_float(r[8 * i + 7])));
+          const int c = sub * 4 + i;
+          *reinterpret_cast<uint4*>(staging + lane * kStageRowBytes + ((c ^ (lane & 15)) << 4)) = v;
+        }
+        named_barrier(1 + quarter, kEpilogueWarpsPerQuarter * 32);
+        const int c = lane & 15;
+        __nv_bfloat16* dst = p.out + static_cast<size_t>(row0 + quarter * 32) * p.n_out +
+                             n_tile * kTileN + c * 8;
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
-            out16[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+        for (int i = 0; i < 4; ++i) {
+          const int r2 = 2 * (sub * 4 + i) + (lane >> 4);
+          const uint4 v =
+              *reinterpret_cast<const uint4*>(staging + r2 * kStageRowBytes + ((c ^ (r2 & 15)) << 4));
+          if (quarter * 32 + r2 < rows_valid)
+            *reinterpret_cast<uint4*>(dst + static_cast<size_t>(r2) * p.n_out) = v;
+        }
+        named_barrier(1 + quarter, kEpilogueWarpsPerQuarter * 32);  // staging is rewritten next item
+      } else {
+        // Fused GeGLU + NVFP4 requantise.  Accumulator columns [0,64) are up, [64,128) gate,
+        // of intermediate columns [64*n_tile, 64*n_tile+64); this warp owns the 16-column
+        // block `sub` of them.
+        const float multiplier = p.next_scale_q[expert];
+        uint32_t up[16], gate[16];
+        tmem_load_32x16(tmem_row + sub * 16, up);
+        tmem_load_32x16(tmem_row + 64 + sub * 16, gate);
+        tmem_load_wait();
+        tc_fence_before_sync();
+        mbar_arrive(&smem->acc_empty[acc_stage]);
+        float values[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float g = round_through_bf16(alpha, gate[i]);
+          const float u = round_through_bf16(alpha, up[i]);
+          values[i] = __fmul_rn(gv_gelu_erf(g), u);
+        }
+        uint32_t codes_lo, codes_hi;
+        const uint32_t scale = quantize_block16(values, multiplier, codes_lo, codes_hi);
+        if (row_local < rows_valid) {
+          *reinterpret_cast<uint2*>(p.next_codes + static_cast<size_t>(row0 + row_local) * (kInter / 2) +
+                                    n_tile * 32 + sub * 8) = make_uint2(codes_lo, codes_hi);
+          // scale group 4*n_tile+sub of row (128*m_tile + row_local) of the w2 operand
+          constexpr int groups = kInter / 16;
+          p.next_scales[static_cast<size_t>(m_tile) * kTileM * groups +
+                        sf_offset(row_local, 4 * n_tile + sub, groups)] = static_cast<uint8_t>(scale);
         }
       }
-      tc_fence_before_sync();
-      mbar_arrive(&smem->acc_empty[acc_stage]);
       if (threadIdx.x == 64) GV_STAMP(2);
       if (++acc_stage == kAccStages) {
         acc_stage = 0;
@@ -385,8 +461,31 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
+    __syncwarp();
     tmem_dealloc(tmem_base, kTmemColumns);
   }
+}
+
+// Re-tiles the w13 block scales for the fused epilogue: item j of an expert takes up rows
+// [64j, 64j+64) and gate rows [704+64j, 704+64j+64) as its 128 MMA-N rows, so its scale
+// atoms must hold those rows' scales at (n%32)*16 + (n/32)*4 + k.  One thread per byte.
+__global__ void retile_w13_scales_kernel(const uint8_t* __restrict__ sidecar,
+                                         uint8_t* __restrict__ tiled) {
+  constexpr int groups = kHidden / 16;          // 176
+  constexpr int atoms = groups / 4;             // 44
+  constexpr int tiles = kInter / 64;            // 11
+  const size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const size_t total = static_cast<size_t>(kExperts) * tiles * atoms * kSfAtomBytes;
+  if (index >= total) return;
+  const int byte = static_cast<int>(index % kSfAtomBytes);
+  const int atom = static_cast<int>((index / kSfAtomBytes) % atoms);
+  const int tile = static_cast<int>((index / (static_cast<size_t>(kSfAtomBytes) * atoms)) % tiles);
+  const int expert = static_cast<int>(index / (static_cast<size_t>(kSfAtomBytes) * atoms * tiles));
+  const int n = ((byte & 15) >> 2) * 32 + (byte >> 4);  // MMA-N row of this byte
+  const int k = byte & 3;
+  const int source_row = n < 64 ? tile * 64 + n : kInter + tile * 64 + (n - 64);
+  tiled[index] = sidecar[static_cast<size_t>(expert) * kW13Out * groups +
+                         sf_offset(source_row, atom * 4 + k, groups)];
 }
 
 }  // namespace
@@ -401,29 +500,54 @@ extern "C" void gv_trace_read(long long* out, int* counts) {
 #endif
 
 int prepare_grouped_gemm() {
-  return static_cast<int>(cudaFuncSetAttribute(grouped_nvfp4_gemm_kernel,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               static_cast<int>(kGemmSmemBytes)));
+  cudaError_t e = cudaFuncSetAttribute(grouped_nvfp4_gemm_kernel<kPlain>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kGemmSmemBytes));
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(grouped_nvfp4_gemm_kernel<kGeglu>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(kGemmSmemBytes));
+  return static_cast<int>(e);
+}
+
+size_t retiled_w13_scale_bytes() {
+  return static_cast<size_t>(kExperts) * (kInter / 64) * (kHidden / 64) * kSfAtomBytes;
+}
+
+void launch_retile_w13_scales(const uint8_t* sidecar_scales, uint8_t* tiled, cudaStream_t stream) {
+  const size_t total = retiled_w13_scale_bytes();
+  retile_w13_scales_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+      sidecar_scales, tiled);
 }
 
 void launch_grouped_gemm(const GemmOperands& op, const RoutePlan& plan, int sm_count,
                          cudaStream_t stream) {
-  GemmParams p;
+  GemmParams p{};
   p.a_scales = op.a_scales;
   p.b_scales = op.b_scales;
   p.alpha = op.alpha;
   p.out = static_cast<__nv_bfloat16*>(op.out);
+  p.next_codes = op.next_codes;
+  p.next_scales = op.next_scales;
+  p.next_scale_q = op.next_scale_q;
   p.tile_expert = plan.tile_expert;
   p.expert_offsets = plan.expert_offsets;
   p.scale_row_offsets = plan.scale_row_offsets;
   p.num_m_tiles = plan.num_m_tiles;
   p.status = plan.status;
   p.n_out = op.n_out;
-  p.n_tiles = op.n_out / kTileN;
   p.groups = op.k_in / 16;
   p.k_blocks = (op.k_in + kTileK - 1) / kTileK;
   p.last_mmas = (op.k_in - (p.k_blocks - 1) * kTileK) / 64;
-  grouped_nvfp4_gemm_kernel<<<sm_count, kGemmThreads, kGemmSmemBytes, stream>>>(op.map_a, op.map_b, p);
+  if (op.fused_geglu) {
+    p.n_tiles = kInter / 64;
+    grouped_nvfp4_gemm_kernel<kGeglu>
+        <<<sm_count, kGemmThreads, kGemmSmemBytes, stream>>>(op.map_a, op.map_b, p);
+  } else {
+    p.n_tiles = op.n_out / kTileN;
+    grouped_nvfp4_gemm_kernel<kPlain>
+        <<<sm_count, kGemmThreads, kGemmSmemBytes, stream>>>(op.map_a, op.map_b, p);
+  }
 }
 
 }  // namespace gv

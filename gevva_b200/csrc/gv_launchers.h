@@ -52,10 +52,21 @@ struct GemmOperands {
   void* out;                // bf16 [row capacity, N]
   int n_out;                // N: 1408 or 2816
   int k_in;                 // K: 2816 or 704
+  // Fused w13 form (GeGLU + requantise in the epilogue, no bf16 output): map_b then has a
+  // 64-row box, b_scales is the re-tiled copy made by launch_retile_w13_scales, and the
+  // results go to the w2 operand buffers below.
+  bool fused_geglu;
+  uint8_t* next_codes;        // [row capacity, 352]
+  uint8_t* next_scales;       // scale regions of the w2 operand
+  const float* next_scale_q;  // g2.input_scale_quant [128]
 };
 
 void launch_grouped_gemm(const GemmOperands& op, const RoutePlan& plan, int sm_count,
                          cudaStream_t stream);
+
+// w13 block scales [128,1408,176] (sidecar layout) -> per-item atoms for the fused form.
+size_t retiled_w13_scale_bytes();
+void launch_retile_w13_scales(const uint8_t* sidecar_scales, uint8_t* tiled, cudaStream_t stream);
 
 // Must be called once per device before launch_grouped_gemm (sets the dynamic
 // shared-memory limit).  Returns a cudaError_t value.

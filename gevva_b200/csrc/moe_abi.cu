@@ -56,10 +56,11 @@ EncodeTiledFn encode_tiled() {
 
 // Byte matrix [rows, row_bytes] viewed through a 128-row x 128-byte box with the
 // 128-byte swizzle the MMA descriptors expect.  Out-of-range bytes read as zero.
-bool make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes) {
+bool make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                      int box_rows = kTileM) {
   const cuuint64_t dims[2] = {row_bytes, rows};
   const cuuint64_t strides[1] = {row_bytes};
-  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kTileKBytes), static_cast<cuuint32_t>(kTileM)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kTileKBytes), static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t element_strides[2] = {1, 1};
   EncodeTiledFn fn = encode_tiled();
   if (!fn) return false;
@@ -151,8 +152,10 @@ int make_scratch(int tokens, Scratch** out) {
 struct gevva_moe {
   Scratch* scratch = nullptr;
   gevva_moe_weights weights{};
-  gv::GemmOperands w13{};
+  gv::GemmOperands w13{};        // bf16 output (stage access, debugging)
+  gv::GemmOperands w13_fused{};  // GeGLU + requantise in the epilogue (the production path)
   gv::GemmOperands w2{};
+  uint8_t* w13_sf_tiled = nullptr;  // runner-owned re-tiling of weights.w13_sf
   int sm_count = 0;
 };
 
@@ -211,10 +214,26 @@ int gevva_moe_create(gevva_moe** out, const gevva_moe_weights* weights, int max_
   ok = ok && make_operand_map(&m->w2.map_a, s->inter_codes, rows, kInter / 2);
   ok = ok && make_operand_map(&m->w2.map_b, weights->w2, static_cast<uint64_t>(kExperts) * kHidden,
                               kInter / 2);
+  CUtensorMap w13_half_rows;  // same matrix through a 64-row box: up rows and gate rows apart
+  ok = ok && make_operand_map(&w13_half_rows, weights->w13, static_cast<uint64_t>(kExperts) * kW13Out,
+                              kHidden / 2, 64);
   if (!ok) {
     gevva_moe_destroy(m);
     std::snprintf(g_error_text, sizeof(g_error_text), "cuTensorMapEncodeTiled failed");
     return GEVVA_MOE_CUDA_ERROR;
+  }
+  // The fused w13 epilogue pairs up rows with gate rows inside one MMA tile; its weight
+  // scales are a one-off re-tiling of the caller's tensor (the caller's memory is not touched).
+  cudaError_t tiled_error =
+      cudaMalloc(reinterpret_cast<void**>(&m->w13_sf_tiled), gv::retiled_w13_scale_bytes());
+  if (tiled_error == cudaSuccess) {
+    gv::launch_retile_w13_scales(static_cast<const uint8_t*>(weights->w13_sf), m->w13_sf_tiled, nullptr);
+    tiled_error = cudaGetLastError();
+  }
+  if (tiled_error == cudaSuccess) tiled_error = cudaStreamSynchronize(nullptr);
+  if (tiled_error != cudaSuccess) {
+    gevva_moe_destroy(m);
+    return cuda_failure(tiled_error, "w13 scale re-tiling");
   }
   m->w13.a_scales = s->input_sf;
   m->w13.b_scales = static_cast<const uint8_t*>(weights->w13_sf);
@@ -222,6 +241,14 @@ int gevva_moe_create(gevva_moe** out, const gevva_moe_weights* weights, int max_
   m->w13.out = s->w13_out;
   m->w13.n_out = kW13Out;
   m->w13.k_in = kHidden;
+  m->w13_fused = m->w13;
+  m->w13_fused.map_b = w13_half_rows;
+  m->w13_fused.b_scales = m->w13_sf_tiled;
+  m->w13_fused.out = nullptr;
+  m->w13_fused.fused_geglu = true;
+  m->w13_fused.next_codes = s->inter_codes;
+  m->w13_fused.next_scales = s->inter_sf;
+  m->w13_fused.next_scale_q = weights->in_scale_q2;
   m->w2.a_scales = s->inter_sf;
   m->w2.b_scales = static_cast<const uint8_t*>(weights->w2_sf);
   m->w2.alpha = weights->alpha2;
@@ -235,6 +262,7 @@ int gevva_moe_create(gevva_moe** out, const gevva_moe_weights* weights, int max_
 void gevva_moe_destroy(gevva_moe* runner) {
   if (!runner) return;
   if (runner->scratch && --runner->scratch->references == 0) free_scratch(runner->scratch);
+  cudaFree(runner->w13_sf_tiled);
   delete runner;
 }
 
@@ -266,10 +294,17 @@ int gevva_moe_launch_stages(gevva_moe* runner, const void* in, const int* ids,
   if (stages & GEVVA_MOE_STAGE_QUANTIZE)
     gv::launch_quantize_input(in, ids, runner->weights.in_scale_q1, s->plan, tokens, s->input_codes,
                               s->input_sf, stream);
-  if (stages & GEVVA_MOE_STAGE_W13) gv::launch_grouped_gemm(runner->w13, s->plan, runner->sm_count, stream);
-  if (stages & GEVVA_MOE_STAGE_GEGLU)
-    gv::launch_geglu_quantize(s->w13_out, runner->weights.in_scale_q2, s->plan, routes,
-                              s->inter_codes, s->inter_sf, stream);
+  const unsigned both = GEVVA_MOE_STAGE_W13 | GEVVA_MOE_STAGE_GEGLU;
+  if ((stages & both) == both && !(stages & GEVVA_MOE_STAGE_UNFUSED)) {
+    // production path: GeGLU + requantise inside the w13 epilogue, no bf16 w13 output
+    gv::launch_grouped_gemm(runner->w13_fused, s->plan, runner->sm_count, stream);
+  } else {
+    if (stages & GEVVA_MOE_STAGE_W13)
+      gv::launch_grouped_gemm(runner->w13, s->plan, runner->sm_count, stream);
+    if (stages & GEVVA_MOE_STAGE_GEGLU)
+      gv::launch_geglu_quantize(s->w13_out, runner->weights.in_scale_q2, s->plan, routes,
+                                s->inter_codes, s->inter_sf, stream);
+  }
   if (stages & GEVVA_MOE_STAGE_W2) gv::launch_grouped_gemm(runner->w2, s->plan, runner->sm_count, stream);
   if (stages & GEVVA_MOE_STAGE_REDUCE)
     gv::launch_reduce_routes(s->w2_out, route_weights, s->plan.inverse_routes, tokens, out, stream);

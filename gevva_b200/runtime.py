@@ -25,6 +25,7 @@ W13_OUT = 2 * INTER
 
 STAGE_SORT, STAGE_QUANTIZE, STAGE_W13, STAGE_GEGLU, STAGE_W2, STAGE_REDUCE = 1, 2, 4, 8, 16, 32
 STAGE_ALL = 63
+STAGE_UNFUSED = 64  # keep W13 and GEGLU as two kernels (bf16 w13 output materialised)
 
 BUF_INPUT_CODES, BUF_INPUT_SF, BUF_W13_OUT, BUF_INTER_CODES, BUF_INTER_SF, BUF_W2_OUT = range(6)
 (BUF_SORTED_EXPERTS, BUF_SORTED_ROUTES, BUF_INVERSE_ROUTES, BUF_EXPERT_OFFSETS,

@@ -114,7 +114,11 @@ enum gevva_moe_stage {
   GEVVA_MOE_STAGE_GEGLU = 8,     /* :1875-1879 */
   GEVVA_MOE_STAGE_W2 = 16,       /* :1880 */
   GEVVA_MOE_STAGE_REDUCE = 32,   /* :1881-1885 */
-  GEVVA_MOE_STAGE_ALL = 63
+  GEVVA_MOE_STAGE_ALL = 63,
+  /* When W13 and GEGLU are both requested they run as one kernel (GeGLU and requantise in
+   * the GEMM epilogue; the bf16 w13 output is then not materialised).  Adding this flag
+   * keeps them separate, as the reference runs them. */
+  GEVVA_MOE_STAGE_UNFUSED = 64
 };
 
 int gevva_moe_launch_stages(gevva_moe* runner, const void* in, const int* ids,
@@ -124,7 +128,7 @@ int gevva_moe_launch_stages(gevva_moe* runner, const void* in, const int* ids,
 enum gevva_moe_buffer_id {
   GEVVA_MOE_BUF_INPUT_CODES = 0,   /* u8 [R,1408] */
   GEVVA_MOE_BUF_INPUT_SF = 1,      /* u8 (R+128*127)*176 */
-  GEVVA_MOE_BUF_W13_OUT = 2,       /* bf16 [R,1408] */
+  GEVVA_MOE_BUF_W13_OUT = 2,       /* bf16 [R,1408]; written only by the unfused W13 stage */
   GEVVA_MOE_BUF_INTER_CODES = 3,   /* u8 [R,352] */
   GEVVA_MOE_BUF_INTER_SF = 4,      /* u8 (R+128*127)*44 */
   GEVVA_MOE_BUF_W2_OUT = 5,        /* bf16 [R,2816] */

@@ -306,6 +306,31 @@ def test_geglu_quantiser_bit_exact(gm, oracle, weights, big_runner, cuda_device,
         assert (got_sf[off] == want_sf[off]).all(), int(expert)
 
 
+@pytest.mark.parametrize("tokens,kind", [(16, "random"), (300, "skewed"), (4096, "random")])
+def test_fused_w13_epilogue_equals_separate_kernels(gm, weights, big_runner, cuda_device, tokens, kind):
+    """GeGLU + requantise inside the w13 epilogue must give the very bytes that the bf16
+    GEMM followed by the stand-alone GeGLU quantiser gives (same accumulators, same
+    bf16 rounding point, same block quantiser)."""
+    from gevva_b200 import runtime as rt
+    ids = random_ids(tokens, 77) if kind == "random" else skewed_ids(tokens)
+    x = hashgen.activations(tokens, HIDDEN, 61, cuda_device)
+    dev_ids = torch.from_numpy(ids).to(cuda_device)
+    routes = tokens * TOP_K
+    codes = big_runner.buffer(rt.BUF_INTER_CODES)
+    sf = big_runner.buffer(rt.BUF_INTER_SF)
+    big_runner.launch_stages(rt.STAGE_SORT | rt.STAGE_QUANTIZE, tokens, input=x, expert_ids=dev_ids)
+    results = []
+    for extra in (rt.STAGE_UNFUSED, 0):
+        codes.zero_()
+        sf.zero_()
+        big_runner.launch_stages(rt.STAGE_W13 | rt.STAGE_GEGLU | extra, tokens)
+        assert big_runner.last_status() == 0
+        results.append((codes[: routes * INTER // 2].clone(), sf.clone()))
+    assert torch.equal(results[0][0], results[1][0])
+    assert torch.equal(results[0][1], results[1][1])
+    assert results[0][0].any() and results[0][1].any()
+
+
 def test_w2_gemm_stage(gm, oracle, weights, big_runner, cuda_device):
     from gevva_b200 import runtime as rt
     tokens = 24

@@ -108,6 +108,50 @@ def layer_step(layer, x, out, weights, ids):
     layer.runner.launch_batch(x, ids, weights, out, x.shape[0])
 
 
+def decode_sweep(layer, device, steps):
+    """Decode-sized batches (1, 8, 32, 64 tokens, unbiased router): the layer is bound by
+    streaming the routed experts' weights from HBM.  32 different batches are cycled so a
+    step's experts are not the previous steps' (428 MB of weights against 126 MB of L2)."""
+    import torch
+    import gevva_b200
+    from gevva_b200.runtime import Nvfp4ExpertRunner
+    peaks, _ = measured_peaks()
+    runner = Nvfp4ExpertRunner(layer.weights, 64)
+    rows = []
+    for tokens in (1, 8, 32, 64):
+        pool = [layer.inputs(tokens, seed=5000 + 97 * tokens + i) for i in range(32)]
+        out = torch.empty_like(pool[0])
+        weights = torch.empty((tokens, TOP_K), dtype=torch.float32, device=device)
+        ids = torch.empty((tokens, TOP_K), dtype=torch.int32, device=device)
+        distinct = []
+
+        def step(x):
+            logits = torch.matmul(x, layer.router_w.t())
+            gevva_b200.route_128_top8(logits, layer.expert_scale, weights=weights, ids=ids)
+            runner.launch_batch(x, ids, weights, out, tokens)
+
+        for x in pool:
+            step(x)
+            distinct.append(int(torch.unique(ids).numel()))
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(steps):
+            step(pool[i % len(pool)])
+        stop.record()
+        torch.cuda.synchronize()
+        us = start.elapsed_time(stop) * 1e3 / steps
+        d = sum(distinct) / len(distinct)
+        algorithmic = d * 3345408 + 720896 + 2 * tokens * HIDDEN * 2
+        gbs = algorithmic / (us * 1e-6) / 1e9
+        rows.append({"tokens": tokens, "us_per_layer": us, "distinct_experts": d,
+                     "algorithmic_bytes": algorithmic, "hbm_gbs": gbs,
+                     "frac_of_measured_hbm": gbs / float(peaks["hbm_gbs"]),
+                     "frac_of_8000_gbs": gbs / 8000.0, "tokens_per_s": tokens / (us * 1e-6)})
+    runner.check()
+    return rows
+
+
 def oracle_sample(rank_seed, tokens):
     """Synthetic inputs for the CPU legs, generated without a GPU."""
     import numpy as np
@@ -301,6 +345,8 @@ def run_gpu(args):
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }
+        if world == 1:
+            line["decode"] = decode_sweep(layer, device, max(args.steps, 20))
         if world == 1 and not args.no_cpu_baseline:
             sample = 128
             oracle, x_bits, logit_bits, scale_bits, hw = oracle_sample(0, sample)

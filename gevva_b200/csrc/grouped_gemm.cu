@@ -12,8 +12,8 @@
 // Mapping.  Tokens (sorted routes) sit on MMA-M, weight rows on MMA-N.  A work
 // item is (128-row tile of one expert) x (128 weight rows).  Row tiles are listed
 // in device memory by the route sort; CTAs are persistent and take items
-// round-robin.  Warp 0 is the TMA producer, warp 1 allocates tensor memory and
-// issues the MMAs, warps 2..17 drain accumulators (two accumulator stages, so the
+// round-robin.  Warps 0 and 18 are the TMA producers (activation side, weight side),
+// warp 1 allocates tensor memory and issues the MMAs, warps 2..17 drain accumulators (two accumulator stages, so the
 // epilogue of one item overlaps the main loop of the next).  Warps 0 and 1 walk
 // their loops as whole warps (warp-uniform addresses) and one elected lane issues.
 //
@@ -47,7 +47,11 @@ constexpr int kStages = 5;
 constexpr int kAccStages = 2;
 constexpr int kEpilogueWarpsPerQuarter = 4;  // each takes a quarter of a tile's columns
 constexpr int kEpilogueThreads = 4 * kEpilogueWarpsPerQuarter * 32;
-constexpr int kGemmThreads = 64 + kEpilogueThreads;  // producer warp, MMA warp, epilogue warps
+// Warp roles: 0 = producer of the activation side (A + its scales), 1 = MMA issuer,
+// 2..17 = epilogue, 18 = producer of the weight side (B + its scales).  Two producers
+// because one thread cannot issue a K block's copies in the time its MMAs take.
+constexpr int kWeightProducerWarp = 2 + 4 * kEpilogueWarpsPerQuarter;
+constexpr int kGemmThreads = (kWeightProducerWarp + 1) * 32;
 constexpr uint32_t kTmemColumns = 512;
 // Scale-factor columns are per pipeline stage: a copy for K block k+1 must not wait for
 // the MMAs of K block k to finish reading theirs.
@@ -71,6 +75,10 @@ struct alignas(1024) GemmSmem {
   uint64_t acc_empty[kAccStages];
   uint32_t tmem_base;
   volatile int abort;
+#if defined(GV_TRACE)
+  unsigned int trace[3][768];
+  int trace_count[3];
+#endif
 };
 
 constexpr size_t kGemmSmemBytes = sizeof(GemmSmem) + 1024;  // slack for manual alignment
@@ -107,13 +115,18 @@ struct GemmParams {
 // stall costs nothing but the polls themselves.
 constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s at 2 GHz
 
+// kBackoff: sleep between polls.  Warps that wait with slack (producers, epilogue) must not
+// spin, because a spinning warp takes issue slots from the MMA warp on the same scheduler and
+// every instruction of the main loop then costs several times its latency.
+template <bool kBackoff>
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, GemmSmem* smem,
                                               int* status) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
   for (uint32_t spin = 1;; ++spin) {
+    if (kBackoff) __nanosleep(spin < 8 ? 32 : 128);
     if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 1023u) == 0) {
+    if ((spin & (kBackoff ? 63u : 1023u)) == 0) {
       if (smem->abort) return false;
       if (clock64() - start > kWaitLimitCycles) {
         smem->abort = 1;
@@ -172,13 +185,15 @@ __device__ __forceinline__ void issue_k_block(uint32_t tmem_acc, uint32_t tmem_s
 }
 
 #if defined(GV_TRACE)
-// Debug build only: timestamps of CTA 0's roles, read back by gv_trace_read().
-__device__ long long g_trace[3][4096];
+// Debug build only: cycle stamps of CTA 0's roles, kept in shared memory while the kernel
+// runs (a stamp costs one shared store) and copied out at the end; gv_trace_read() reads them.
+constexpr int kTraceDepth = 768;
+__device__ unsigned int g_trace[3][kTraceDepth];
 __device__ int g_trace_count[3];
-#define GV_STAMP(role)                                                        \
-  do {                                                                        \
-    if (blockIdx.x == 0 && g_trace_count[role] < 4096)                        \
-      g_trace[role][g_trace_count[role]++] = clock64();                       \
+#define GV_STAMP(role)                                                              \
+  do {                                                                              \
+    if (blockIdx.x == 0 && smem->trace_count[role] < kTraceDepth)                   \
+      smem->trace[role][smem->trace_count[role]++] = static_cast<unsigned>(clock64()); \
   } while (0)
 #else
 #define GV_STAMP(role) do {} while (0)
@@ -207,7 +222,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&smem->full[s], 1);
+      mbar_init(&smem->full[s], 2);  // one arrival (with its byte count) per producer warp
       mbar_init(&smem->empty[s], 1);
     }
     for (int s = 0; s < kAccStages; ++s) {
@@ -215,6 +230,9 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       mbar_init(&smem->acc_empty[s], kEpilogueThreads);
     }
     smem->abort = 0;
+#if defined(GV_TRACE)
+    smem->trace_count[0] = smem->trace_count[1] = smem->trace_count[2] = 0;
+#endif
     fence_barrier_init();
     prefetch_tensor_map(&map_a);
     prefetch_tensor_map(&map_b);
@@ -230,8 +248,9 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
 
   const int total_items = p.num_m_tiles[0] * p.n_tiles;
 
-  if (warp == 0) {
-    // ---------------- TMA producer ----------------
+  if (warp == 0 || warp == kWeightProducerWarp) {
+    // ---------------- TMA producers ----------------
+    const bool weight_side = warp == kWeightProducerWarp;
     int stage = 0;
     uint32_t phase = 0;
     int issued = 0;
@@ -240,39 +259,43 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       const int m_tile = item / p.n_tiles;
       const int n_tile = item - m_tile * p.n_tiles;
       const int expert = p.tile_expert[m_tile];
-      const int row0 = p.expert_offsets[expert] + (m_tile * kTileM - p.scale_row_offsets[expert]);
-      const uint8_t* sfa_src = p.a_scales + static_cast<size_t>(m_tile) * kTileM * p.groups;
-      int b_row, b_row2 = 0;
-      const uint8_t* sfb_src;
-      if (kMode == kGeglu) {
-        b_row = expert * kW13Out + n_tile * 64;  // up rows; the gate rows lie kInter further on
-        b_row2 = b_row + kInter;
-        sfb_src = p.b_scales + (static_cast<size_t>(expert) * p.n_tiles + n_tile) * kTileN * p.groups;
+      int row = 0, row2 = 0;
+      const uint8_t* sf_src;
+      if (!weight_side) {
+        row = p.expert_offsets[expert] + (m_tile * kTileM - p.scale_row_offsets[expert]);
+        sf_src = p.a_scales + static_cast<size_t>(m_tile) * kTileM * p.groups;
+      } else if (kMode == kGeglu) {
+        row = expert * kW13Out + n_tile * 64;  // up rows; the gate rows lie kInter further on
+        row2 = row + kInter;
+        sf_src = p.b_scales + (static_cast<size_t>(expert) * p.n_tiles + n_tile) * kTileN * p.groups;
       } else {
-        b_row = expert * p.n_out + n_tile * kTileN;
-        sfb_src = p.b_scales + static_cast<size_t>(b_row) * p.groups;
+        row = expert * p.n_out + n_tile * kTileN;
+        sf_src = p.b_scales + static_cast<size_t>(row) * p.groups;
       }
       for (int kb = 0; kb < p.k_blocks; ++kb) {
-        ok = __all_sync(0xffffffffu, wait_or_abort(&smem->empty[stage], phase ^ 1u, smem, p.status));
+        ok = __all_sync(0xffffffffu, wait_or_abort<true>(&smem->empty[stage], phase ^ 1u, smem, p.status));
         if (!ok) break;
         if (elect_one()) {
-          GV_STAMP(0);
+          if (!weight_side) GV_STAMP(0);
           const uint32_t sf_bytes =
               (kb == p.k_blocks - 1 ? p.last_mmas : 4) * static_cast<uint32_t>(kSfAtomBytes);
-          mbar_arrive_expect_tx(&smem->full[stage], 2u * kOperandStageBytes + 2u * sf_bytes);
-          tma_load_2d(smem->a[stage], &map_a, &smem->full[stage], kb * kTileKBytes, row0);
-          if (kMode == kGeglu) {
-            tma_load_2d(smem->b[stage], &map_b, &smem->full[stage], kb * kTileKBytes, b_row);
-            tma_load_2d(smem->b[stage] + kOperandStageBytes / 2, &map_b, &smem->full[stage],
-                        kb * kTileKBytes, b_row2);
+          mbar_arrive_expect_tx(&smem->full[stage], kOperandStageBytes + sf_bytes);
+          if (!weight_side) {
+            tma_load_2d(smem->a[stage], &map_a, &smem->full[stage], kb * kTileKBytes, row);
+            bulk_load_1d(smem->sfa[stage], sf_src + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes,
+                         &smem->full[stage]);
           } else {
-            tma_load_2d(smem->b[stage], &map_b, &smem->full[stage], kb * kTileKBytes, b_row);
+            if (kMode == kGeglu) {
+              tma_load_2d(smem->b[stage], &map_b, &smem->full[stage], kb * kTileKBytes, row);
+              tma_load_2d(smem->b[stage] + kOperandStageBytes / 2, &map_b, &smem->full[stage],
+                          kb * kTileKBytes, row2);
+            } else {
+              tma_load_2d(smem->b[stage], &map_b, &smem->full[stage], kb * kTileKBytes, row);
+            }
+            bulk_load_1d(smem->sfb[stage], sf_src + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes,
+                         &smem->full[stage]);
           }
-          bulk_load_1d(smem->sfa[stage], sfa_src + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes,
-                       &smem->full[stage]);
-          bulk_load_1d(smem->sfb[stage], sfb_src + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes,
-                       &smem->full[stage]);
-          GV_STAMP(0);
+          if (!weight_side) GV_STAMP(0);
         }
         __syncwarp();
         ++issued;
@@ -313,15 +336,15 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     constexpr uint32_t hi_ab = (1024u >> 4) | (1u << 14) | (2u << 29);  // 8 rows x 128 B, 128B swizzle
     constexpr uint32_t hi_sf = (128u >> 4) | (1u << 14);                // 8 rows x 16 B, no swizzle
     const bool full_last = p.last_mmas == 4;
+    const bool leader = elect_one();
     for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
       if (!__all_sync(0xffffffffu,
-                      wait_or_abort(&smem->acc_empty[acc_stage], acc_phase ^ 1u, smem, p.status)))
+                      wait_or_abort<false>(&smem->acc_empty[acc_stage], acc_phase ^ 1u, smem, p.status)))
         break;
-      tc_fence_after_sync();
       const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc_stage * kTileN);
       bool ok = true;
       for (int kb = 0; kb < p.k_blocks; ++kb) {
-        ok = __all_sync(0xffffffffu, wait_or_abort(&smem->full[stage], phase, smem, p.status));
+        ok = __all_sync(0xffffffffu, wait_or_abort<false>(&smem->full[stage], phase, smem, p.status));
         if (!ok) break;
         tc_fence_after_sync();
         // Descriptor low words advance by whole stages; the K offset of each MMA (+32 bytes
@@ -332,7 +355,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         const uint32_t sfb_lo = sfb_lo0 + static_cast<uint32_t>(stage) * (kSfStageBytes >> 4);
         const uint32_t tmem_sf = tmem_base + kSfColumn + kSfColumnsPerStage * stage;
         const uint32_t accumulate = kb != 0 ? 1u : 0u;
-        if (elect_one()) {
+        if (leader) {
           GV_STAMP(1);
           if (kb != p.k_blocks - 1 || full_last) {
             issue_k_block<4>(tmem_acc, tmem_sf, a_lo, b_lo, sfa_lo, sfb_lo, hi_ab, hi_sf, accumulate);
@@ -344,17 +367,15 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
             issue_k_block<1>(tmem_acc, tmem_sf, a_lo, b_lo, sfa_lo, sfb_lo, hi_ab, hi_sf, accumulate);
           }
           tc_commit(&smem->empty[stage]);  // frees the stage once these MMAs have read it
+          if (kb == p.k_blocks - 1) tc_commit(&smem->acc_full[acc_stage]);
           GV_STAMP(1);
         }
-        __syncwarp();
         if (++stage == kStages) {
           stage = 0;
           phase ^= 1u;
         }
       }
       if (!ok) break;
-      if (elect_one()) tc_commit(&smem->acc_full[acc_stage]);
-      __syncwarp();
       if (++acc_stage == kAccStages) {
         acc_stage = 0;
         acc_phase ^= 1u;
@@ -377,7 +398,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       const int row0 = p.expert_offsets[expert] + local0;
       const int rows_valid = p.expert_offsets[expert + 1] - row0;  // may exceed 128
       const float alpha = p.alpha[expert];
-      if (!wait_or_abort(&smem->acc_full[acc_stage], acc_phase, smem, p.status)) break;
+      if (!wait_or_abort<true>(&smem->acc_full[acc_stage], acc_phase, smem, p.status)) break;
       tc_fence_after_sync();
       if (threadIdx.x == 64) GV_STAMP(2);
       const int row_local = quarter * 32 + lane;
@@ -459,6 +480,15 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
 
   tc_fence_before_sync();
   __syncthreads();
+#if defined(GV_TRACE)
+  if (blockIdx.x == 0) {
+    for (int role = 0; role < 3; ++role) {
+      for (int i = threadIdx.x; i < smem->trace_count[role]; i += blockDim.x)
+        g_trace[role][i] = smem->trace[role][i];
+      if (threadIdx.x == 0) g_trace_count[role] = smem->trace_count[role];
+    }
+  }
+#endif
   if (warp == 1) {
     tc_fence_after_sync();
     __syncwarp();
@@ -491,11 +521,9 @@ __global__ void retile_w13_scales_kernel(const uint8_t* __restrict__ sidecar,
 }  // namespace
 
 #if defined(GV_TRACE)
-extern "C" void gv_trace_read(long long* out, int* counts) {
+extern "C" void gv_trace_read(unsigned int* out, int* counts) {
   cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace));
   cudaMemcpyFromSymbol(counts, g_trace_count, sizeof(g_trace_count));
-  int zero[3] = {0, 0, 0};
-  cudaMemcpyToSymbol(g_trace_count, zero, sizeof(zero));
 }
 #endif
 

@@ -280,14 +280,14 @@ void launch_route_sort(const int* expert_ids, int routes, const RoutePlan& plan,
 
 // ---------------------------------------------------------------------------
 // Input quantiser.  Reference: quantize_bf16_sorted_moe, src/nvfp4_cutlass.cu:
-// 290-327 (one CTA per sorted route, 16 scalar loads per thread, byte stores).
-// Here one CTA per token: thread (k, q) quantises 64 consecutive columns of the
-// token for route k and writes 32 code bytes and one 4-byte scale word to the
-// route's sorted row, so the token row is fetched from HBM once and the eight
-// copies come out of L1.
+// 290-327 (one CTA per sorted route, 16 scalar loads per thread, byte stores, the
+// token row fetched eight times).  Here one CTA per token reads the row once with
+// one coalesced 16-byte load per thread; a lane pair owns a 16-value block (amax by
+// one shuffle); then for each of the token's eight routes the block is quantised
+// with that expert's static scale and every warp store covers 128 contiguous bytes
+// of the route's sorted row.  Scale bytes leave as 4-byte words (four blocks each).
 // ---------------------------------------------------------------------------
-constexpr int kQuadsHidden = kHidden / 64;  // 44
-constexpr int kQuadsInter = kInter / 64;    // 11
+constexpr int kQuantizeThreads = kHidden / 8;  // 352: eleven warps of 256 columns each
 
 __device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* out) {
   out[0] = __uint_as_float(raw.x << 16);
@@ -300,43 +300,70 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* out) {
   out[7] = __uint_as_float(raw.w & 0xffff0000u);
 }
 
-__global__ void __launch_bounds__(kTopK * kQuadsHidden)
+__global__ void __launch_bounds__(kQuantizeThreads)
 quantize_input_kernel(const __nv_bfloat16* __restrict__ input, const int* __restrict__ expert_ids,
                       const float* __restrict__ in_scale_q, RoutePlan plan,
                       uint8_t* __restrict__ packed, uint8_t* __restrict__ scales) {
-  const int token = blockIdx.x;
-  const int k = threadIdx.x / kQuadsHidden;
-  const int quad = threadIdx.x % kQuadsHidden;
-  const int route = token * kTopK + k;
-  const int expert = expert_ids[route];
-  if (expert < 0 || expert >= kExperts) return;  // flagged by the route sort
-  const int dst = plan.inverse_routes[route];
-  const int row = dst - plan.expert_offsets[expert];
-  const float multiplier = in_scale_q[expert];
-  const uint4* src =
-      reinterpret_cast<const uint4*>(input + static_cast<size_t>(token) * kHidden + quad * 64);
-  uint32_t codes[8];
-  uint32_t scale_word = 0;
-#pragma unroll
-  for (int block = 0; block < 4; ++block) {
-    float values[16];
-    unpack_bf16x8(__ldg(src + 2 * block), values);
-    unpack_bf16x8(__ldg(src + 2 * block + 1), values + 8);
-    scale_word |= quantize_block16(values, multiplier, codes[2 * block], codes[2 * block + 1])
-                  << (8 * block);
-  }
-  uint4* out = reinterpret_cast<uint4*>(packed + static_cast<size_t>(dst) * (kHidden / 2) + quad * 32);
-  out[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
-  out[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
   constexpr int groups = kHidden / 16;
-  *reinterpret_cast<uint32_t*>(scales + static_cast<size_t>(plan.scale_row_offsets[expert]) * groups +
-                               sf_offset(row, 4 * quad, groups)) = scale_word;
+  __shared__ float route_multiplier[kTopK];
+  __shared__ int route_row[kTopK];            // sorted row, or -1 for a rejected expert id
+  __shared__ unsigned long long route_scale_base[kTopK];
+  const int token = blockIdx.x;
+  if (threadIdx.x < kTopK) {
+    const int route = token * kTopK + threadIdx.x;
+    const int expert = expert_ids[route];
+    if (expert < 0 || expert >= kExperts) {  // flagged by the route sort
+      route_row[threadIdx.x] = -1;
+    } else {
+      const int dst = plan.inverse_routes[route];
+      const int row = dst - plan.expert_offsets[expert];
+      route_row[threadIdx.x] = dst;
+      route_multiplier[threadIdx.x] = in_scale_q[expert];
+      route_scale_base[threadIdx.x] =
+          static_cast<unsigned long long>(plan.scale_row_offsets[expert]) * groups + sf_offset(row, 0, groups);
+    }
+  }
+  const int lane = threadIdx.x & 31;
+  float values[8];
+  unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(input + static_cast<size_t>(token) * kHidden) +
+                      threadIdx.x),
+                values);
+  float maximum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) maximum = fmaxf(maximum, fabsf(values[i]));
+  maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, 1));
+  __syncthreads();
+  const int quad = threadIdx.x >> 3;  // four blocks = one scale word = 64 columns
+#pragma unroll 2
+  for (int k = 0; k < kTopK; ++k) {
+    const int dst = route_row[k];
+    if (dst < 0) continue;
+    const float multiplier = route_multiplier[k];
+    const float unrounded = __fdiv_rn(__fmul_rn(multiplier, maximum), 6.0f);
+    const uint32_t scale = encode_e4m3(unrounded);
+    const float rounded = decode_e4m3(scale);
+    const float inverse = rounded == 0.0f ? 0.0f : __fdiv_rn(multiplier, rounded);
+    uint32_t codes = 0;
+#pragma unroll
+    for (int pair = 0; pair < 4; ++pair)
+      codes |= encode_e2m1x2(__fmul_rn(values[2 * pair], inverse),
+                             __fmul_rn(values[2 * pair + 1], inverse)) << (8 * pair);
+    reinterpret_cast<uint32_t*>(packed + static_cast<size_t>(dst) * (kHidden / 2))[threadIdx.x] = codes;
+    // lanes 8q, 8q+2, 8q+4, 8q+6 hold the four scale bytes of one word
+    const int base_lane = lane & ~7;
+    uint32_t word = __shfl_sync(0xffffffffu, scale, base_lane);
+    word |= __shfl_sync(0xffffffffu, scale, base_lane + 2) << 8;
+    word |= __shfl_sync(0xffffffffu, scale, base_lane + 4) << 16;
+    word |= __shfl_sync(0xffffffffu, scale, base_lane + 6) << 24;
+    if ((lane & 7) == 0)
+      *reinterpret_cast<uint32_t*>(scales + route_scale_base[k] + static_cast<size_t>(quad) * 512) = word;
+  }
 }
 
 void launch_quantize_input(const void* input_bf16, const int* expert_ids, const float* in_scale_q,
                            const RoutePlan& plan, int tokens, uint8_t* packed, uint8_t* scales,
                            cudaStream_t stream) {
-  quantize_input_kernel<<<tokens, kTopK * kQuadsHidden, 0, stream>>>(
+  quantize_input_kernel<<<tokens, kQuantizeThreads, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(input_bf16), expert_ids, in_scale_q, plan, packed, scales);
 }
 
@@ -345,6 +372,7 @@ void launch_quantize_input(const void* input_bf16, const int* expert_ids, const 
 // src/nvfp4_cutlass.cu:552-601: v = gelu_erf(gate) * up from the bf16 GEMM output,
 // columns [0,704) = up and [704,1408) = gate.
 // ---------------------------------------------------------------------------
+constexpr int kQuadsInter = kInter / 64;    // 11
 constexpr int kGegluRowsPerBlock = 32;
 
 __global__ void __launch_bounds__(kGegluRowsPerBlock * kQuadsInter)

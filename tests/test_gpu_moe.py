@@ -407,6 +407,34 @@ def test_layer_against_oracle(gm, oracle, weights, cuda_device, tokens, kind):
     assert (manual == bits(out)).all()
 
 
+def test_against_committed_golden_vectors(gm, packed, weights, cuda_device):
+    """tests/golden/moe_golden.npz: packed weights of all 128 experts (checksums), router,
+    and the 16-token layer output."""
+    import hashlib
+    import os
+    golden = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "moe_golden.npz"))
+
+    def sha(a):
+        return np.frombuffer(hashlib.sha256(np.ascontiguousarray(a).tobytes()).digest(), np.uint8)
+
+    dev, host = packed
+    for key in ("w13", "w13_sf", "w2", "w2_sf"):
+        assert (sha(host[key]) == golden["packed_" + key + "_sha"]).all(), key
+    assert (host["g13"] == golden["packed_g13"]).all() and (host["g2"] == golden["packed_g2"]).all()
+    tokens = 16
+    x = hashgen.activations(tokens, HIDDEN, 41, cuda_device)
+    logits = from_bits(golden["layer_logits"], cuda_device).view(tokens, EXPERTS)
+    rw, ids = gm.route_128_top8(logits, torch.ones(EXPERTS, dtype=torch.bfloat16, device=cuda_device))
+    assert (ids.cpu().numpy() == golden["layer_ids"]).all()
+    assert (rw.cpu().numpy().view(np.uint32) == golden["layer_route_weights"].view(np.uint32)).all()
+    runner = gm.Nvfp4ExpertRunner(weights[0], tokens)
+    out = torch.empty_like(x)
+    runner.launch_batch(x, ids, rw, out, tokens)
+    runner.check()
+    assert (runner.inverse_routes().cpu().numpy() == golden["layer_inverse"]).all()
+    assert rel_l2(bf16_to_f32(bits(out)), bf16_to_f32(golden["layer_out"])) < REL_L2
+
+
 def test_full_size_properties(gm, weights, cuda_device):
     """4096 tokens (the prefill configuration's size): properties that need no oracle."""
     from gevva_b200 import runtime as rt

@@ -33,24 +33,19 @@ def fmt(mono, width):
 
 
 def main():
-    # erf on [0,1): a * p(a^2), p fitted on t=a^2 in [0,1]
-    g = lambda t: np.where(t > 0, erf(np.sqrt(np.maximum(t, 1e-300))) /
-                           np.sqrt(np.maximum(t, 1e-300)), 2 / np.sqrt(np.pi))
-    c, h, m = cheb_mono(g, 0.0, 1.0, 6)
-    a = np.linspace(0, 1, 400001).astype(np.float32)
-    t = (a * a).astype(np.float32)
-    x = ((t - np.float32(c)) * np.float32(1 / h)).astype(np.float32)
-    r = (horner32(m, x).astype(np.float64) * a).astype(np.float32)
-    print(f"// erf small: centre {c} half {h} max abs err "
-          f"{np.abs(r - erf(a.astype(np.float64))).max():.3e}")
-    print("GV_ERF_SMALL =", fmt(m, 7))
-    for lo, hi, deg in ((1, 2, 9), (2, 3, 9), (3, 4, 9)):
-        c, h, m = cheb_mono(erf, lo, hi, deg)
-        a = np.linspace(lo, hi, 400001).astype(np.float32)
-        x = ((a - np.float32(c)) * np.float32(1 / h)).astype(np.float32)
-        e = np.abs(horner32(m, x).astype(np.float64) - erf(a.astype(np.float64))).max()
-        print(f"// erf [{lo},{hi}) centre {c} half {h} max abs err {e:.3e}")
-        print(fmt(m, 10), ",")
+    # erf on [0,4): eight intervals of width 0.5, degree 6 in u = a - centre
+    worst = 0.0
+    print("#define GV_ERF_TABLE_INIT {\\")
+    for i in range(8):
+        lo, hi = 0.5 * i, 0.5 * (i + 1)
+        c, h, m = cheb_mono(erf, lo, hi, 6)
+        m = m / (h ** np.arange(len(m)))  # monomial in (a - c)
+        a = np.linspace(lo, hi, 100001)[:-1].astype(np.float32)
+        u = (a - np.float32(c)).astype(np.float32)
+        worst = max(worst, np.abs(horner32(m, u).astype(np.float64) - erf(a.astype(np.float64))).max())
+        print("  " + fmt(m, 7)[:-1] + ", 0.0f},\\")
+    print("}")
+    print(f"// erf table max abs err {worst:.3e}")
     # exp on [-ln2/2, ln2/2]
     half = np.log(2.0) / 2
     c, h, m = cheb_mono(np.exp, -half, half, 6)

@@ -75,6 +75,7 @@ struct alignas(1024) GemmSmem {
   uint64_t acc_empty[kAccStages];
   uint32_t tmem_base;
   volatile int abort;
+  float erf_table[GV_ERF_TABLE_FLOATS];
 #if defined(GV_TRACE)
   unsigned int trace[3][768];
   int trace_count[3];
@@ -241,6 +242,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     tmem_alloc(&smem->tmem_base, kTmemColumns);
     tmem_relinquish();
   }
+  if (kMode == kGeglu) load_erf_table(smem->erf_table);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -457,7 +459,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         for (int i = 0; i < 16; ++i) {
           const float g = round_through_bf16(alpha, gate[i]);
           const float u = round_through_bf16(alpha, up[i]);
-          values[i] = __fmul_rn(gv_gelu_erf(g), u);
+          values[i] = __fmul_rn(gv_gelu_erf(g, smem->erf_table), u);
         }
         uint32_t codes_lo, codes_hi;
         const uint32_t scale = quantize_block16(values, multiplier, codes_lo, codes_hi);

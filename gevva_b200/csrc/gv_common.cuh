@@ -36,6 +36,14 @@ constexpr int kTileK = 2 * kTileKBytes;
 constexpr int kSfAtomBytes = 512;              // 128 rows x 4 scale bytes (K = 64)
 constexpr int kSfStageBytes = 4 * kSfAtomBytes;
 
+// erf coefficient table; kernels copy it to shared memory once (load_erf_table) because
+// lanes read different rows of it.
+static __constant__ float g_erf_table[8][8] = GV_ERF_TABLE_INIT;
+
+__device__ __forceinline__ void load_erf_table(float* shared_table) {
+  if (threadIdx.x < GV_ERF_TABLE_FLOATS) shared_table[threadIdx.x] = g_erf_table[threadIdx.x >> 3][threadIdx.x & 7];
+}
+
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) {
   return __uint_as_float(bits16 << 16);
 }

@@ -55,66 +55,50 @@ GV_HD uint32_t gv_float_to_bits(float value) {
 #endif
 }
 
-// erf(x), max abs error 9e-8 over the reals.
-GV_HD float gv_erff(float x) {
+// erf as eight half-unit intervals of |x| in [0,4), each a degree-6 polynomial in
+// u = |x| - centre; 1 beyond.  Branch-free apart from the NaN test, so sixteen values can
+// be evaluated interleaved.  Row i of the table holds c0..c6 (and a pad) of interval i;
+// max abs error 8e-8.  Coefficients from fit_transcendentals.py.
+#define GV_ERF_TABLE_INIT {\
+  {2.763263881e-01f, 1.060013652e+00f, -2.650032640e-01f, -3.091164231e-01f, 1.269483566e-01f, 7.830715179e-02f, -3.948784247e-02f, 0.0f},\
+  {7.111556530e-01f, 6.429315209e-01f, -4.821982384e-01f, 2.672714554e-02f, 1.506790370e-01f, -5.125992000e-02f, -2.661922388e-02f, 0.0f},\
+  {9.229001403e-01f, 2.365212291e-01f, -2.956515551e-01f, 1.675231010e-01f, -6.140203681e-03f, -4.677713290e-02f, 2.068483829e-02f, 0.0f},\
+  {9.866716862e-01f, 5.277483538e-02f, -9.235622734e-02f, 9.017768502e-02f, -4.810455441e-02f, 5.969322287e-03f, 9.039151482e-03f, 0.0f},\
+  {9.985373020e-01f, 7.142300252e-03f, -1.607019082e-02f, 2.172697149e-02f, -1.908679493e-02f, 1.058122981e-02f, -2.795148641e-03f, 0.0f},\
+  {9.998993874e-01f, 5.862942780e-04f, -1.612264663e-03f, 2.758205635e-03f, -3.257828532e-03f, 2.825851319e-03f, -1.666593715e-03f, 0.0f},\
+  {9.999957085e-01f, 2.919363942e-05f, -9.486651834e-05f, 1.952197636e-04f, -2.862895199e-04f, 3.326097503e-04f, -2.724775113e-04f, 0.0f},\
+  {9.999998808e-01f, 8.818848301e-07f, -3.305675591e-06f, 7.911847206e-06f, -1.380229787e-05f, 2.020373722e-05f, -2.051217416e-05f, 0.0f},\
+}
+#define GV_ERF_TABLE_FLOATS 64
+
+#if !defined(__CUDA_ARCH__)
+static const float gv_erf_table_host[8][8] = GV_ERF_TABLE_INIT;
+#endif
+
+// `table` points at the 64 floats above: gv_erf_table_host on the CPU, a shared-memory
+// copy inside kernels (lanes index it with different rows).
+GV_HD float gv_erff(float x, const float* table) {
   const float a = fabsf(x);
-  float r;
-  if (a < 1.0f) {
-    // erf(a) = a * p(2*a^2 - 1)
-    const float t = GV_FMA(GV_MUL(a, a), 2.0f, -1.0f);
-    float p = 1.230605449e-06f;
-    p = GV_FMA(p, t, -1.766906826e-05f);
-    p = GV_FMA(p, t, 2.175135451e-04f);
-    p = GV_FMA(p, t, -2.285419498e-03f);
-    p = GV_FMA(p, t, 1.985249668e-02f);
-    p = GV_FMA(p, t, -1.405360997e-01f);
-    p = GV_FMA(p, t, 9.654687643e-01f);
-    r = GV_MUL(a, p);
-  } else if (a < 4.0f) {
-    // Three unit intervals, each a degree-9 polynomial in u = 2*(a - centre).
-    float c0, c1, c2, c3, c4, c5, c6, c7, c8, c9, centre;
-    if (a < 2.0f) {
-      centre = 1.5f;
-      c0 = 9.661051631e-01f; c1 = 5.946514383e-02f; c2 = -4.459885508e-02f;
-      c3 = 1.734401286e-02f; c4 = -2.787466859e-03f; c5 = -4.646643938e-04f;
-      c6 = 3.020868462e-04f; c7 = -3.679370275e-05f; c8 = -9.383547876e-06f;
-      c9 = 3.037872602e-06f;
-    } else if (a < 3.0f) {
-      centre = 2.5f;
-      c0 = 9.995930195e-01f; c1 = 1.089142170e-03f; c2 = -1.361434348e-03f;
-      c3 = 1.043760800e-03f; c4 = -5.388446734e-04f; c5 = 1.911700965e-04f;
-      c6 = -4.387873560e-05f; c7 = 4.229543720e-06f; c8 = 1.196742119e-06f;
-      c9 = -4.803476372e-07f;
-    } else {
-      centre = 3.5f;
-      c0 = 9.999992847e-01f; c1 = 2.699713605e-06f; c2 = -4.724084192e-06f;
-      c3 = 5.286926353e-06f; c4 = -4.235686902e-06f; c5 = 2.566234798e-06f;
-      c6 = -1.205385843e-06f; c7 = 4.543294381e-07f; c8 = -1.446854156e-07f;
-      c9 = 3.033540352e-08f;
-    }
-    const float u = GV_MUL(GV_SUB(a, centre), 2.0f);
-    float p = c9;
-    p = GV_FMA(p, u, c8);
-    p = GV_FMA(p, u, c7);
-    p = GV_FMA(p, u, c6);
-    p = GV_FMA(p, u, c5);
-    p = GV_FMA(p, u, c4);
-    p = GV_FMA(p, u, c3);
-    p = GV_FMA(p, u, c2);
-    p = GV_FMA(p, u, c1);
-    p = GV_FMA(p, u, c0);
-    r = p;
-  } else {
-    r = 1.0f;  // also NaN-free for +-inf; NaN input compares false above and lands here
-  }
-  if (a != a) return x;  // propagate NaN
-  return x < 0.0f ? -r : r;
+  if (a != a) return x;  // NaN
+  const float clamped = fminf(a, 3.99999976f);
+  const float index = truncf(GV_MUL(clamped, 2.0f));
+  const float u = GV_SUB(GV_FMA(index, -0.5f, clamped), 0.25f);
+  const float* c = table + 8 * (int)index;
+  float p = c[6];
+  p = GV_FMA(p, u, c[5]);
+  p = GV_FMA(p, u, c[4]);
+  p = GV_FMA(p, u, c[3]);
+  p = GV_FMA(p, u, c[2]);
+  p = GV_FMA(p, u, c[1]);
+  p = GV_FMA(p, u, c[0]);
+  const float r = a >= 4.0f ? 1.0f : p;
+  return copysignf(r, x);
 }
 
 // erf-GELU exactly as the reference writes it (src/nvfp4_cutlass.cu:175-177):
 // 0.5F * value * (1.0F + erff(value * 0.7071067811865475F)), left to right.
-GV_HD float gv_gelu_erf(float value) {
-  const float e = gv_erff(GV_MUL(value, 0.7071067811865475f));
+GV_HD float gv_gelu_erf(float value, const float* table) {
+  const float e = gv_erff(GV_MUL(value, 0.7071067811865475f), table);
   return GV_MUL(GV_MUL(0.5f, value), GV_ADD(1.0f, e));
 }
 

@@ -379,6 +379,9 @@ __global__ void __launch_bounds__(kGegluRowsPerBlock * kQuadsInter)
 geglu_quantize_kernel(const __nv_bfloat16* __restrict__ fused, const float* __restrict__ in_scale_q,
                       RoutePlan plan, int routes, uint8_t* __restrict__ packed,
                       uint8_t* __restrict__ scales) {
+  __shared__ float erf_table[GV_ERF_TABLE_FLOATS];
+  load_erf_table(erf_table);
+  __syncthreads();
   const int route = blockIdx.x * kGegluRowsPerBlock + threadIdx.x / kQuadsInter;
   const int quad = threadIdx.x % kQuadsInter;
   if (route >= routes) return;
@@ -397,7 +400,7 @@ geglu_quantize_kernel(const __nv_bfloat16* __restrict__ fused, const float* __re
     unpack_bf16x8(__ldg(gate + 2 * block), g);
     unpack_bf16x8(__ldg(gate + 2 * block + 1), g + 8);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) values[i] = __fmul_rn(gv_gelu_erf(g[i]), u[i]);
+    for (int i = 0; i < 16; ++i) values[i] = __fmul_rn(gv_gelu_erf(g[i], erf_table), u[i]);
     scale_word |= quantize_block16(values, multiplier, codes[2 * block], codes[2 * block + 1])
                   << (8 * block);
   }

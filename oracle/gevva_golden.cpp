@@ -172,9 +172,9 @@ uint8_t gvo_encode_e2m1(float v) { return encode_e2m1(v); }
 float gvo_decode_e2m1(unsigned c) { return decode_e2m1(c); }
 uint16_t gvo_float_to_bf16(float v) { return float_to_bf16(v); }
 float gvo_bf16_to_float(uint16_t v) { return bf16_to_float(v); }
-float gvo_erff(float v) { return gv_erff(v); }
+float gvo_erff(float v) { return gv_erff(v, &gv_erf_table_host[0][0]); }
 float gvo_expf(float v) { return gv_expf(v); }
-float gvo_gelu(float v) { return gv_gelu_erf(v); }
+float gvo_gelu(float v) { return gv_gelu_erf(v, &gv_erf_table_host[0][0]); }
 size_t gvo_sf_offset(int row, int group, int groups) { return sf_offset(row, group, groups); }
 
 // ---- a2: router, src/cuda/kernels/routing_sampling.cuh:396-431 ---------------
@@ -282,7 +282,8 @@ void gvo_geglu_quantize(const uint16_t* fused, const float* input_scale_quant,
       float values[16];
       for (int i = 0; i < 16; ++i) {
         const int column = group * 16 + i;
-        values[i] = gv_gelu_erf(bf16_to_float(row[width + column])) * bf16_to_float(row[column]);
+        values[i] = gv_gelu_erf(bf16_to_float(row[width + column]), &gv_erf_table_host[0][0]) *
+                    bf16_to_float(row[column]);
       }
       const uint8_t scale = quantize_block16(
           values, multiplier, packed + static_cast<size_t>(route) * (width / 2) + group * 8);

@@ -358,7 +358,7 @@ def run_gpu(args):
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }
-        if world == 1:
+        if world == 1 and not args.no_decode:
             line["decode"] = decode_sweep(layer, device, max(args.steps, 20))
         if world == 1 and not args.no_cpu_baseline:
             sample = 128
@@ -380,6 +380,7 @@ def main():
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-decode", action="store_true", help="skip the decode-size sweep")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)

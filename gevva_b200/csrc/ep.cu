@@ -1,0 +1,436 @@
+// Expert-parallel form of the MoE layer: experts sharded over the GPUs of one
+// node, tokens data-parallel, rows exchanged by stores into peer memory over NVLink.
+// The reference is single-GPU and has no counterpart.
+//
+// Placement.  Expert e lives on rank e % world as local expert e / world; the
+// "virtual" id v = (e % world) * EL + e / world (EL = 128 / world) orders experts by
+// owning rank, so a sender's sorted routes are contiguous per destination.
+//
+// One step, on every rank (the caller places a cross-rank barrier where marked):
+//   1. route_sort   sort local routes by v; store this rank's 128 counts into
+//                   every peer's count matrix                       -- barrier --
+//   2. dispatch     from the full count matrix compute, for every v, where this
+//                   rank's rows land in the owner's receive buffer; quantise each
+//                   route with its expert's static scale and store codes and scale
+//                   bytes straight into the owner's w13 operand buffers
+//                   (1584 B per route instead of 5632 B of bf16)     -- barrier --
+//   3. compute      build the group geometry of the local experts from the same
+//                   matrix; w13 (+GeGLU+requantise) and w2 grouped GEMMs; copy
+//                   every result row back into its source rank's combine buffer
+//                   at the source's own sorted position              -- barrier --
+//   4. reduce       the source's usual weighted reduce over its eight routes.
+// Receive order is fixed by (local expert, source rank, source order), so results do
+// not depend on timing.  All peer traffic is plain global stores through mapped
+// peer pointers; nothing here waits on a peer inside a kernel (the barriers are the
+// caller's collectives), and no TMA load touches peer memory: the GEMMs read only
+// this GPU's own receive buffers.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <new>
+
+#include "../../include/gevva_moe.h"
+#include "gv_common.cuh"
+#include "gv_launchers.h"
+#include "gv_plan.cuh"
+
+namespace gv {
+
+namespace {
+
+constexpr int kMaxWorld = 8;
+
+struct EpDevice {            // device-visible description, passed to kernels by value
+  int rank, world, local_experts;
+  uint8_t* peer_codes[kMaxWorld];   // each rank's w13 operand codes [capacity, 1408]
+  uint8_t* peer_scales[kMaxWorld];  // each rank's w13 operand scale regions
+  __nv_bfloat16* peer_combine[kMaxWorld];  // each rank's combine buffer [8*T_local, 2816]
+  int* peer_counts[kMaxWorld];      // each rank's count matrix [world][128]
+  int* counts;                      // == peer_counts[rank]
+  int* send_row_base;               // [128] by v
+  int* send_src_prefix;             // [128] by v
+  int* send_scale_rows;             // [128] by v
+  int* source_offsets;              // [world][EL]: sorted position of (source, local expert) on the source
+  const int* remap;                 // [128] e -> v
+};
+
+// ---- 1: publish this rank's per-expert counts into every peer's matrix -------------
+__global__ void __launch_bounds__(kExperts)
+ep_publish_counts_kernel(EpDevice ep, RoutePlan plan) {
+  const int v = threadIdx.x;
+  const int count = plan.expert_offsets[v + 1] - plan.expert_offsets[v];
+  for (int d = 0; d < ep.world; ++d) ep.peer_counts[d][ep.rank * kExperts + v] = count;
+}
+
+// ---- 2a: where this rank's rows land on their owners ------------------------------
+__global__ void __launch_bounds__(kExperts) ep_send_bases_kernel(EpDevice ep) {
+  const int v = threadIdx.x;
+  const int el = ep.local_experts;
+  const int owner_first = (v / el) * el;
+  int expert_base = 0, scale_rows = 0, src_prefix = 0;
+  for (int u = owner_first; u < v; ++u) {
+    int total = 0;
+    for (int s = 0; s < ep.world; ++s) total += ep.counts[s * kExperts + u];
+    expert_base += total;
+    scale_rows += (total + kTileM - 1) / kTileM * kTileM;
+  }
+  for (int s = 0; s < ep.rank; ++s) src_prefix += ep.counts[s * kExperts + v];
+  ep.send_row_base[v] = expert_base + src_prefix;
+  ep.send_src_prefix[v] = src_prefix;
+  ep.send_scale_rows[v] = scale_rows;
+}
+
+// ---- 2b: quantise and store into the owners' operand buffers -----------------------
+// Same arithmetic and thread mapping as quantize_input_kernel (one CTA per token, the row
+// read once); only the destination differs.
+constexpr int kQuantizeThreads = kHidden / 8;
+
+__global__ void __launch_bounds__(kQuantizeThreads)
+ep_dispatch_kernel(const __nv_bfloat16* __restrict__ input, const int* __restrict__ expert_ids,
+                   const float* __restrict__ in_scale_q_global, EpDevice ep, RoutePlan plan) {
+  constexpr int groups = kHidden / 16;
+  __shared__ float route_multiplier[kTopK];
+  __shared__ uint8_t* route_codes[kTopK];
+  __shared__ uint8_t* route_scales[kTopK];
+  const int token = blockIdx.x;
+  if (threadIdx.x < kTopK) {
+    const int route = token * kTopK + threadIdx.x;
+    const int expert = expert_ids[route];
+    if (expert < 0 || expert >= kExperts) {
+      route_codes[threadIdx.x] = nullptr;
+    } else {
+      const int v = ep.remap[expert];
+      const int owner = v / ep.local_experts;
+      const int j = plan.inverse_routes[route] - plan.expert_offsets[v];
+      const int row = ep.send_row_base[v] + j;
+      const int row_in_expert = ep.send_src_prefix[v] + j;
+      route_multiplier[threadIdx.x] = in_scale_q_global[expert];
+      route_codes[threadIdx.x] = ep.peer_codes[owner] + static_cast<size_t>(row) * (kHidden / 2);
+      route_scales[threadIdx.x] = ep.peer_scales[owner] +
+                                  static_cast<size_t>(ep.send_scale_rows[v]) * groups +
+                                  sf_offset(row_in_expert, 0, groups);
+    }
+  }
+  const int lane = threadIdx.x & 31;
+  const uint4 raw = __ldg(reinterpret_cast<const uint4*>(input + static_cast<size_t>(token) * kHidden) +
+                          threadIdx.x);
+  float values[8];
+  values[0] = __uint_as_float(raw.x << 16);
+  values[1] = __uint_as_float(raw.x & 0xffff0000u);
+  values[2] = __uint_as_float(raw.y << 16);
+  values[3] = __uint_as_float(raw.y & 0xffff0000u);
+  values[4] = __uint_as_float(raw.z << 16);
+  values[5] = __uint_as_float(raw.z & 0xffff0000u);
+  values[6] = __uint_as_float(raw.w << 16);
+  values[7] = __uint_as_float(raw.w & 0xffff0000u);
+  float maximum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) maximum = fmaxf(maximum, fabsf(values[i]));
+  maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, 1));
+  __syncthreads();
+  const int quad = threadIdx.x >> 3;
+#pragma unroll 2
+  for (int k = 0; k < kTopK; ++k) {
+    uint8_t* codes_row = route_codes[k];
+    if (!codes_row) continue;
+    const float multiplier = route_multiplier[k];
+    const float unrounded = __fdiv_rn(__fmul_rn(multiplier, maximum), 6.0f);
+    const uint32_t scale = encode_e4m3(unrounded);
+    const float rounded = decode_e4m3(scale);
+    const float inverse = rounded == 0.0f ? 0.0f : __fdiv_rn(multiplier, rounded);
+    uint32_t codes = 0;
+#pragma unroll
+    for (int pair = 0; pair < 4; ++pair)
+      codes |= encode_e2m1x2(__fmul_rn(values[2 * pair], inverse),
+                             __fmul_rn(values[2 * pair + 1], inverse)) << (8 * pair);
+    reinterpret_cast<uint32_t*>(codes_row)[threadIdx.x] = codes;
+    const int base_lane = lane & ~7;
+    uint32_t word = __shfl_sync(0xffffffffu, scale, base_lane);
+    word |= __shfl_sync(0xffffffffu, scale, base_lane + 2) << 8;
+    word |= __shfl_sync(0xffffffffu, scale, base_lane + 4) << 16;
+    word |= __shfl_sync(0xffffffffu, scale, base_lane + 6) << 24;
+    if ((lane & 7) == 0)
+      *reinterpret_cast<uint32_t*>(route_scales[k] + static_cast<size_t>(quad) * 512) = word;
+  }
+}
+
+// ---- 3a: group geometry of the local experts ---------------------------------------
+__global__ void __launch_bounds__(kExperts) ep_receive_plan_kernel(EpDevice ep, RoutePlan plan) {
+  __shared__ int scan_scratch[16];
+  const int le = threadIdx.x;
+  const int el = ep.local_experts;
+  int count = 0;
+  if (le < el) {
+    const int v = ep.rank * el + le;
+    for (int s = 0; s < ep.world; ++s) count += ep.counts[s * kExperts + v];
+  }
+  publish_groups(count, 0, plan, scan_scratch);
+  // sorted position, on source rank s, of the first row it sent to local expert le
+  for (int index = threadIdx.x; index < ep.world * el; index += kExperts) {
+    const int s = index / el, e = index % el;
+    const int v = ep.rank * el + e;
+    int offset = 0;
+    for (int u = 0; u < v; ++u) offset += ep.counts[s * kExperts + u];
+    ep.source_offsets[index] = offset;
+  }
+}
+
+// ---- 3b: return result rows to their sources ---------------------------------------
+__global__ void __launch_bounds__(kHidden / 8)
+ep_combine_kernel(const __nv_bfloat16* __restrict__ routed, EpDevice ep, RoutePlan plan) {
+  const int el = ep.local_experts;
+  const int total = plan.expert_offsets[kExperts];
+  for (int row = blockIdx.x; row < total; row += gridDim.x) {
+    // local expert of this row: the last le with expert_offsets[le] <= row
+    int lo = 0, hi = el - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (plan.expert_offsets[mid] <= row) lo = mid; else hi = mid - 1;
+    }
+    const int le = lo;
+    int within = row - plan.expert_offsets[le];
+    const int v = ep.rank * el + le;
+    int s = 0;
+    for (; s < ep.world - 1; ++s) {
+      const int c = ep.counts[s * kExperts + v];
+      if (within < c) break;
+      within -= c;
+    }
+    const int dst_row = ep.source_offsets[s * el + le] + within;
+    const uint4 value = reinterpret_cast<const uint4*>(routed + static_cast<size_t>(row) * kHidden)[threadIdx.x];
+    reinterpret_cast<uint4*>(ep.peer_combine[s] + static_cast<size_t>(dst_row) * kHidden)[threadIdx.x] = value;
+  }
+}
+
+}  // namespace
+
+}  // namespace gv
+
+// ------------------------------------------------------------------------------------
+// C ABI
+// ------------------------------------------------------------------------------------
+namespace {
+
+using namespace gv;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, int box_rows) {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {row_bytes, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kTileKBytes), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t element_strides[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+            element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+struct gevva_moe_ep {
+  gv::EpDevice dev{};
+  gv::RoutePlan send_plan{};     // this rank's own routes, sorted by v
+  gv::RoutePlan receive_plan{};  // rows received for the local experts
+  gv::GemmOperands w13{}, w2{};
+  const float* in_scale_q1_global = nullptr;
+  int max_tokens = 0;
+  size_t capacity_rows = 0;
+  int sm_count = 0;
+  // owned device memory
+  int* ints = nullptr;
+  uint8_t* inter_codes = nullptr;
+  uint8_t* inter_sf = nullptr;
+  void* w2_out = nullptr;
+  uint8_t* w13_sf_tiled = nullptr;
+};
+
+extern "C" {
+
+void gevva_moe_ep_destroy(gevva_moe_ep* ep) {
+  if (!ep) return;
+  cudaFree(ep->ints);
+  cudaFree(ep->inter_codes);
+  cudaFree(ep->inter_sf);
+  cudaFree(ep->w2_out);
+  cudaFree(ep->w13_sf_tiled);
+  delete ep;
+}
+
+int gevva_moe_ep_create(gevva_moe_ep** out, const gevva_moe_weights* local_weights,
+                        const float* in_scale_q1_global, const gevva_moe_ep_config* config) {
+  if (!out || !local_weights || !in_scale_q1_global || !config) return GEVVA_MOE_BAD_ARGUMENT;
+  const int world = config->world, rank = config->rank;
+  if (world < 1 || world > gv::kMaxWorld || kExperts % world != 0 || rank < 0 || rank >= world ||
+      config->max_tokens < 1)
+    return GEVVA_MOE_BAD_ARGUMENT;
+  if (gv::prepare_grouped_gemm() != 0) return GEVVA_MOE_CUDA_ERROR;
+  cudaDeviceProp prop;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess)
+    return GEVVA_MOE_CUDA_ERROR;
+  if (prop.major != 10) return GEVVA_MOE_NO_DEVICE;
+  gevva_moe_ep* ep = new (std::nothrow) gevva_moe_ep;
+  if (!ep) return GEVVA_MOE_CUDA_ERROR;
+  const int el = kExperts / world;
+  ep->sm_count = prop.multiProcessorCount;
+  ep->max_tokens = config->max_tokens;
+  ep->capacity_rows = config->recv_capacity_rows;
+  ep->in_scale_q1_global = in_scale_q1_global;
+  ep->dev.rank = rank;
+  ep->dev.world = world;
+  ep->dev.local_experts = el;
+  for (int d = 0; d < world; ++d) {
+    ep->dev.peer_codes[d] = static_cast<uint8_t*>(config->peer_recv_codes[d]);
+    ep->dev.peer_scales[d] = static_cast<uint8_t*>(config->peer_recv_sf[d]);
+    ep->dev.peer_combine[d] = static_cast<__nv_bfloat16*>(config->peer_combine[d]);
+    ep->dev.peer_counts[d] = config->peer_counts[d];
+  }
+  ep->dev.counts = ep->dev.peer_counts[rank];
+
+  const size_t local_routes = static_cast<size_t>(config->max_tokens) * kTopK;
+  const size_t cap = ep->capacity_rows;
+  const size_t send_tiles = local_routes / kTileM + kExperts + 1;
+  const size_t recv_tiles = cap / kTileM + kExperts + 1;
+  const size_t chunks = (local_routes + 1023) / 1024;
+  const size_t int_count = 3 * local_routes + 2 * (kExperts + 1) + send_tiles + 1 + chunks * kExperts + 1 +
+                           2 * (kExperts + 1) + recv_tiles + 1 + 1 +   // receive plan
+                           4 * kExperts + kExperts + 64;                // tables + remap
+  const size_t padded = cap + static_cast<size_t>(kExperts) * 127;
+  cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&ep->ints), int_count * sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(ep->ints, 0, int_count * sizeof(int));
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&ep->inter_codes), cap * (kInter / 2));
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&ep->inter_sf), padded * (kInter / 16));
+  if (e == cudaSuccess) e = cudaMemset(ep->inter_sf, 0, padded * (kInter / 16));
+  if (e == cudaSuccess) e = cudaMalloc(&ep->w2_out, cap * kHidden * 2);
+  if (e == cudaSuccess)
+    e = cudaMalloc(reinterpret_cast<void**>(&ep->w13_sf_tiled), gv::retiled_w13_scale_bytes(el));
+  if (e != cudaSuccess) {
+    gevva_moe_ep_destroy(ep);
+    return GEVVA_MOE_CUDA_ERROR;
+  }
+  int* cursor = ep->ints;
+  auto carve = [&](size_t n) { int* p = cursor; cursor += n; return p; };
+  gv::RoutePlan& sp = ep->send_plan;
+  sp.sorted_experts = carve(local_routes);
+  sp.sorted_routes = carve(local_routes);
+  sp.inverse_routes = carve(local_routes);
+  sp.expert_offsets = carve(kExperts + 1);
+  sp.scale_row_offsets = carve(kExperts + 1);
+  sp.tile_expert = carve(send_tiles);
+  sp.num_m_tiles = carve(1);
+  sp.chunk_hist = carve(chunks * kExperts);
+  sp.status = carve(1);
+  gv::RoutePlan& rp = ep->receive_plan;
+  rp.expert_offsets = carve(kExperts + 1);
+  rp.scale_row_offsets = carve(kExperts + 1);
+  rp.tile_expert = carve(recv_tiles);
+  rp.num_m_tiles = carve(1);
+  rp.status = sp.status;
+  ep->dev.send_row_base = carve(kExperts);
+  ep->dev.send_src_prefix = carve(kExperts);
+  ep->dev.send_scale_rows = carve(kExperts);
+  ep->dev.source_offsets = carve(kExperts);
+  int* remap = carve(kExperts);
+  int host_remap[kExperts];
+  for (int x = 0; x < kExperts; ++x) host_remap[x] = (x % world) * el + x / world;
+  e = cudaMemcpy(remap, host_remap, sizeof(host_remap), cudaMemcpyHostToDevice);
+  ep->dev.remap = remap;
+  sp.remap = remap;
+
+  gv::launch_retile_w13_scales(static_cast<const uint8_t*>(local_weights->w13_sf), ep->w13_sf_tiled, el,
+                               nullptr);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaStreamSynchronize(nullptr);
+  bool ok = e == cudaSuccess;
+  ok = ok && make_map(&ep->w13.map_a, ep->dev.peer_codes[rank], cap, kHidden / 2, kTileM);
+  ok = ok && make_map(&ep->w13.map_b, local_weights->w13, static_cast<uint64_t>(el) * kW13Out,
+                      kHidden / 2, 64);
+  ok = ok && make_map(&ep->w2.map_a, ep->inter_codes, cap, kInter / 2, kTileM);
+  ok = ok && make_map(&ep->w2.map_b, local_weights->w2, static_cast<uint64_t>(el) * kHidden, kInter / 2,
+                      kTileM);
+  if (!ok) {
+    gevva_moe_ep_destroy(ep);
+    return GEVVA_MOE_CUDA_ERROR;
+  }
+  ep->w13.a_scales = ep->dev.peer_scales[rank];
+  ep->w13.b_scales = ep->w13_sf_tiled;
+  ep->w13.alpha = local_weights->alpha1;
+  ep->w13.out = nullptr;
+  ep->w13.n_out = kW13Out;
+  ep->w13.k_in = kHidden;
+  ep->w13.fused_geglu = true;
+  ep->w13.next_codes = ep->inter_codes;
+  ep->w13.next_scales = ep->inter_sf;
+  ep->w13.next_scale_q = local_weights->in_scale_q2;
+  ep->w2.a_scales = ep->inter_sf;
+  ep->w2.b_scales = static_cast<const uint8_t*>(local_weights->w2_sf);
+  ep->w2.alpha = local_weights->alpha2;
+  ep->w2.out = ep->w2_out;
+  ep->w2.n_out = kHidden;
+  ep->w2.k_in = kInter;
+  ep->w2.fused_geglu = false;
+  *out = ep;
+  return GEVVA_MOE_OK;
+}
+
+int gevva_moe_ep_route_sort(gevva_moe_ep* ep, const int* ids, int tokens, gevva_stream_t stream) {
+  if (!ep || !ids || tokens < 1 || tokens > ep->max_tokens) return GEVVA_MOE_BAD_ARGUMENT;
+  gv::launch_route_sort(ids, tokens * kTopK, ep->send_plan, stream);
+  gv::ep_publish_counts_kernel<<<1, kExperts, 0, stream>>>(ep->dev, ep->send_plan);
+  return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;
+}
+
+int gevva_moe_ep_dispatch(gevva_moe_ep* ep, const void* in, const int* ids, int tokens,
+                          gevva_stream_t stream) {
+  if (!ep || !in || !ids || tokens < 1 || tokens > ep->max_tokens) return GEVVA_MOE_BAD_ARGUMENT;
+  gv::ep_send_bases_kernel<<<1, kExperts, 0, stream>>>(ep->dev);
+  gv::ep_dispatch_kernel<<<tokens, gv::kQuantizeThreads, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(in), ids, ep->in_scale_q1_global, ep->dev, ep->send_plan);
+  return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;
+}
+
+int gevva_moe_ep_compute(gevva_moe_ep* ep, gevva_stream_t stream) {
+  if (!ep) return GEVVA_MOE_BAD_ARGUMENT;
+  gv::ep_receive_plan_kernel<<<1, kExperts, 0, stream>>>(ep->dev, ep->receive_plan);
+  gv::launch_grouped_gemm(ep->w13, ep->receive_plan, ep->sm_count, stream);
+  gv::launch_grouped_gemm(ep->w2, ep->receive_plan, ep->sm_count, stream);
+  gv::ep_combine_kernel<<<ep->sm_count * 8, kHidden / 8, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(ep->w2_out), ep->dev, ep->receive_plan);
+  return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;
+}
+
+int gevva_moe_ep_reduce(gevva_moe_ep* ep, const float* route_weights, void* out, int tokens,
+                        gevva_stream_t stream) {
+  if (!ep || !route_weights || !out || tokens < 1 || tokens > ep->max_tokens) return GEVVA_MOE_BAD_ARGUMENT;
+  gv::launch_reduce_routes(ep->dev.peer_combine[ep->dev.rank], route_weights,
+                           ep->send_plan.inverse_routes, tokens, out, stream);
+  return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;
+}
+
+int gevva_moe_ep_status(gevva_moe_ep* ep, int* received_rows) {
+  if (!ep) return GEVVA_MOE_BAD_ARGUMENT;
+  int status = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return GEVVA_MOE_CUDA_ERROR;
+  if (cudaMemcpy(&status, ep->send_plan.status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
+    return GEVVA_MOE_CUDA_ERROR;
+  if (status) cudaMemset(ep->send_plan.status, 0, sizeof(int));
+  if (received_rows)
+    cudaMemcpy(received_rows, ep->receive_plan.expert_offsets + kExperts, sizeof(int),
+               cudaMemcpyDeviceToHost);
+  return -status;
+}
+
+}  // extern "C"

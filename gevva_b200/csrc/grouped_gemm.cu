@@ -502,12 +502,12 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
 // [64j, 64j+64) and gate rows [704+64j, 704+64j+64) as its 128 MMA-N rows, so its scale
 // atoms must hold those rows' scales at (n%32)*16 + (n/32)*4 + k.  One thread per byte.
 __global__ void retile_w13_scales_kernel(const uint8_t* __restrict__ sidecar,
-                                         uint8_t* __restrict__ tiled) {
+                                         uint8_t* __restrict__ tiled, int experts) {
   constexpr int groups = kHidden / 16;          // 176
   constexpr int atoms = groups / 4;             // 44
   constexpr int tiles = kInter / 64;            // 11
   const size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const size_t total = static_cast<size_t>(kExperts) * tiles * atoms * kSfAtomBytes;
+  const size_t total = static_cast<size_t>(experts) * tiles * atoms * kSfAtomBytes;
   if (index >= total) return;
   const int byte = static_cast<int>(index % kSfAtomBytes);
   const int atom = static_cast<int>((index / kSfAtomBytes) % atoms);
@@ -540,14 +540,15 @@ int prepare_grouped_gemm() {
   return static_cast<int>(e);
 }
 
-size_t retiled_w13_scale_bytes() {
-  return static_cast<size_t>(kExperts) * (kInter / 64) * (kHidden / 64) * kSfAtomBytes;
+size_t retiled_w13_scale_bytes(int experts) {
+  return static_cast<size_t>(experts) * (kInter / 64) * (kHidden / 64) * kSfAtomBytes;
 }
 
-void launch_retile_w13_scales(const uint8_t* sidecar_scales, uint8_t* tiled, cudaStream_t stream) {
-  const size_t total = retiled_w13_scale_bytes();
+void launch_retile_w13_scales(const uint8_t* sidecar_scales, uint8_t* tiled, int experts,
+                              cudaStream_t stream) {
+  const size_t total = retiled_w13_scale_bytes(experts);
   retile_w13_scales_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
-      sidecar_scales, tiled);
+      sidecar_scales, tiled, experts);
 }
 
 void launch_grouped_gemm(const GemmOperands& op, const RoutePlan& plan, int sm_count,

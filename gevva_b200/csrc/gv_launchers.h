@@ -20,6 +20,7 @@ struct RoutePlan {
   int* num_m_tiles;        // [1]
   int* chunk_hist;         // [ceil(R/1024) * 128] scratch of the multi-block sort
   int* status;             // [1]   device status word (gv::Status)
+  const int* remap;        // optional [128]: sort key = remap[expert id] (expert-parallel placement)
 };
 
 void launch_route(const void* logits_bf16, int ld, const void* expert_scale_bf16, float* weights,
@@ -65,8 +66,9 @@ void launch_grouped_gemm(const GemmOperands& op, const RoutePlan& plan, int sm_c
                          cudaStream_t stream);
 
 // w13 block scales [128,1408,176] (sidecar layout) -> per-item atoms for the fused form.
-size_t retiled_w13_scale_bytes();
-void launch_retile_w13_scales(const uint8_t* sidecar_scales, uint8_t* tiled, cudaStream_t stream);
+size_t retiled_w13_scale_bytes(int experts);
+void launch_retile_w13_scales(const uint8_t* sidecar_scales, uint8_t* tiled, int experts,
+                              cudaStream_t stream);
 
 // Must be called once per device before launch_grouped_gemm (sets the dynamic
 // shared-memory limit).  Returns a cudaError_t value.

@@ -225,9 +225,10 @@ int gevva_moe_create(gevva_moe** out, const gevva_moe_weights* weights, int max_
   // The fused w13 epilogue pairs up rows with gate rows inside one MMA tile; its weight
   // scales are a one-off re-tiling of the caller's tensor (the caller's memory is not touched).
   cudaError_t tiled_error =
-      cudaMalloc(reinterpret_cast<void**>(&m->w13_sf_tiled), gv::retiled_w13_scale_bytes());
+      cudaMalloc(reinterpret_cast<void**>(&m->w13_sf_tiled), gv::retiled_w13_scale_bytes(kExperts));
   if (tiled_error == cudaSuccess) {
-    gv::launch_retile_w13_scales(static_cast<const uint8_t*>(weights->w13_sf), m->w13_sf_tiled, nullptr);
+    gv::launch_retile_w13_scales(static_cast<const uint8_t*>(weights->w13_sf), m->w13_sf_tiled, kExperts,
+                                 nullptr);
     tiled_error = cudaGetLastError();
   }
   if (tiled_error == cudaSuccess) tiled_error = cudaStreamSynchronize(nullptr);

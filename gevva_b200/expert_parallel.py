@@ -1,0 +1,128 @@
+"""Expert-parallel MoE layer over the GPUs of one node (one process per GPU).
+
+torch.distributed supplies the process group, the symmetric (peer-mapped) buffers and the
+barriers; rows move by stores from the kernels in csrc/ep.cu into peer memory.  The
+reference is single-GPU and has no counterpart."""
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from .runtime import (EXPERTS, HIDDEN, INTER, TOP_K, W13_OUT, ExpertWeights, GevvaMoeError, _Weights,
+                      _check, _ptr, _stream_handle, library)
+
+
+class _EpConfig(ctypes.Structure):
+    _fields_ = [("rank", ctypes.c_int), ("world", ctypes.c_int), ("max_tokens", ctypes.c_int),
+                ("recv_capacity_rows", ctypes.c_size_t),
+                ("peer_recv_codes", ctypes.POINTER(ctypes.c_void_p)),
+                ("peer_recv_sf", ctypes.POINTER(ctypes.c_void_p)),
+                ("peer_combine", ctypes.POINTER(ctypes.c_void_p)),
+                ("peer_counts", ctypes.POINTER(ctypes.c_void_p))]
+
+
+def local_expert_weights(full: ExpertWeights, rank: int, world: int) -> ExpertWeights:
+    """This rank's shard: experts rank, rank+world, ... (local index e // world)."""
+    pick = lambda t: t[rank::world].contiguous()
+    return ExpertWeights(pick(full.w13), pick(full.w13_sf), pick(full.w2), pick(full.w2_sf),
+                         pick(full.alpha1), pick(full.alpha2), pick(full.in_scale_q1),
+                         pick(full.in_scale_q2))
+
+
+class ExpertParallelRunner:
+    def __init__(self, local_weights: ExpertWeights, in_scale_q1_global: torch.Tensor, max_tokens: int,
+                 group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group or dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.group = group
+        self.device = local_weights.w13.device
+        self.max_tokens = max_tokens
+        el = EXPERTS // self.world
+        _check(local_weights.w13, torch.uint8, (el, W13_OUT, HIDDEN // 2), "w13.weight")
+        _check(local_weights.w2, torch.uint8, (el, HIDDEN, INTER // 2), "w2.weight")
+        _check(in_scale_q1_global, torch.float32, (EXPERTS,), "g1.input_scale_quant (all experts)")
+        self._weights, self._scale_q1 = local_weights, in_scale_q1_global
+        routes = max_tokens * TOP_K
+        cap = self.world * routes
+        align = lambda n: (n + 255) // 256 * 256
+        sizes = [align(self.world * EXPERTS * 4), align(cap * (HIDDEN // 2)),
+                 align((cap + EXPERTS * 127) * (HIDDEN // 16)), align(routes * HIDDEN * 2)]
+        offsets = [0]
+        for size in sizes:
+            offsets.append(offsets[-1] + size)
+        self._buffer = symm_mem.empty(offsets[-1], dtype=torch.uint8, device=self.device)
+        self._buffer.zero_()
+        self._handle_symm = symm_mem.rendezvous(self._buffer, group.group_name)
+        bases = [int(p) for p in self._handle_symm.buffer_ptrs]
+        arrays = []
+        for region in range(4):
+            arr = (ctypes.c_void_p * self.world)(*[b + offsets[region] for b in bases])
+            arrays.append(arr)
+        self._arrays = arrays
+        config = _EpConfig(self.rank, self.world, max_tokens, cap,
+                           ctypes.cast(arrays[1], ctypes.POINTER(ctypes.c_void_p)),
+                           ctypes.cast(arrays[2], ctypes.POINTER(ctypes.c_void_p)),
+                           ctypes.cast(arrays[3], ctypes.POINTER(ctypes.c_void_p)),
+                           ctypes.cast(arrays[0], ctypes.POINTER(ctypes.c_void_p)))
+        lib = library()
+        vp = ctypes.c_void_p
+        lib.gevva_moe_ep_create.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(_Weights), vp,
+                                            ctypes.POINTER(_EpConfig)]
+        lib.gevva_moe_ep_destroy.argtypes = [vp]
+        lib.gevva_moe_ep_destroy.restype = None
+        lib.gevva_moe_ep_route_sort.argtypes = [vp, vp, ctypes.c_int, vp]
+        lib.gevva_moe_ep_dispatch.argtypes = [vp, vp, vp, ctypes.c_int, vp]
+        lib.gevva_moe_ep_compute.argtypes = [vp, vp]
+        lib.gevva_moe_ep_reduce.argtypes = [vp, vp, vp, ctypes.c_int, vp]
+        lib.gevva_moe_ep_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int)]
+        w = local_weights
+        packed = _Weights(*[t.data_ptr() for t in (w.w13, w.w13_sf, w.w2, w.w2_sf, w.alpha1, w.alpha2,
+                                                   w.in_scale_q1, w.in_scale_q2)])
+        handle = vp()
+        with torch.cuda.device(self.device):
+            status = lib.gevva_moe_ep_create(ctypes.byref(handle), ctypes.byref(packed),
+                                             _ptr(in_scale_q1_global), ctypes.byref(config))
+        if status != 0:
+            raise GevvaMoeError(status, "ExpertParallelRunner")
+        self._handle = handle
+        self._flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        dist.barrier(group)
+
+    def __del__(self):
+        handle = getattr(self, "_handle", None)
+        if handle:
+            library().gevva_moe_ep_destroy(handle)
+            self._handle = None
+
+    def _barrier(self):
+        # a stream-ordered collective: no rank's next phase starts before every rank's
+        # previous phase (and its stores into peer memory) has finished
+        dist.all_reduce(self._flag, group=self.group)
+
+    def _call(self, name, *args):
+        with torch.cuda.device(self.device):
+            status = getattr(library(), name)(self._handle, *args)
+        if status != 0:
+            raise GevvaMoeError(status, name)
+
+    def launch_batch(self, input, expert_ids, route_weights, output, tokens, stream=None):
+        """Same contract as Nvfp4ExpertRunner.launch_batch, for this rank's tokens."""
+        _check(input, torch.bfloat16, (tokens, HIDDEN), "input")
+        _check(expert_ids, torch.int32, (tokens, TOP_K), "expert_ids")
+        _check(route_weights, torch.float32, (tokens, TOP_K), "route_weights")
+        _check(output, torch.bfloat16, (tokens, HIDDEN), "output")
+        s = _stream_handle(stream)
+        self._call("gevva_moe_ep_route_sort", _ptr(expert_ids), tokens, s)
+        self._barrier()
+        self._call("gevva_moe_ep_dispatch", _ptr(input), _ptr(expert_ids), tokens, s)
+        self._barrier()
+        self._call("gevva_moe_ep_compute", s)
+        self._barrier()
+        self._call("gevva_moe_ep_reduce", _ptr(route_weights), _ptr(output), tokens, s)
+
+    def status(self):
+        rows = ctypes.c_int(0)
+        with torch.cuda.device(self.device):
+            status = library().gevva_moe_ep_status(self._handle, ctypes.byref(rows))
+        return status, rows.value

@@ -161,6 +161,49 @@ int gevva_moe_route_sort_noalloc(const int* expert_ids, int tokens, int* sorted_
                                  int* sorted_routes, int* inverse_routes, int* expert_offsets,
                                  int* scale_row_offsets, int* status, gevva_stream_t stream);
 
+/* ---- expert-parallel form (no counterpart in the reference, which is single-GPU) ----
+ * Experts are sharded over the `world` GPUs of one node (expert e on rank e % world, local
+ * index e / world); each rank routes its own tokens, stores the quantised rows straight
+ * into the owning rank's operand buffers over NVLink, runs the two grouped GEMMs for its
+ * experts and stores result rows back into the source rank's combine buffer.  One step is
+ * four calls with a cross-rank barrier (any stream-ordered collective) between them:
+ *   gevva_moe_ep_route_sort | barrier | gevva_moe_ep_dispatch | barrier |
+ *   gevva_moe_ep_compute    | barrier | gevva_moe_ep_reduce
+ * The peer-writable buffers are allocated by the caller (e.g. symmetric memory) with the
+ * same sizes on every rank and passed as host arrays of `world` device pointers:
+ *   peer_counts      i32 [world*128]
+ *   peer_recv_codes  u8  [recv_capacity_rows, 1408]
+ *   peer_recv_sf     u8  (recv_capacity_rows + 128*127) * 176
+ *   peer_combine     bf16 [8*max_tokens, 2816]
+ * recv_capacity_rows >= world * 8 * max_tokens covers the worst case.  local_weights holds
+ * this rank's 128/world experts in the sidecar layout with [128/world] scale vectors;
+ * in_scale_q1_global is g1.input_scale_quant of all 128 experts (the sender quantises). */
+typedef struct gevva_moe_ep gevva_moe_ep;
+
+typedef struct {
+  int rank;
+  int world;      /* 1, 2, 4 or 8 */
+  int max_tokens; /* tokens of this rank per step */
+  size_t recv_capacity_rows;
+  void* const* peer_recv_codes;
+  void* const* peer_recv_sf;
+  void* const* peer_combine;
+  int* const* peer_counts;
+} gevva_moe_ep_config;
+
+int gevva_moe_ep_create(gevva_moe_ep** out, const gevva_moe_weights* local_weights,
+                        const float* in_scale_q1_global, const gevva_moe_ep_config* config);
+void gevva_moe_ep_destroy(gevva_moe_ep* ep);
+int gevva_moe_ep_route_sort(gevva_moe_ep* ep, const int* ids, int tokens, gevva_stream_t stream);
+int gevva_moe_ep_dispatch(gevva_moe_ep* ep, const void* in, const int* ids, int tokens,
+                          gevva_stream_t stream);
+int gevva_moe_ep_compute(gevva_moe_ep* ep, gevva_stream_t stream);
+int gevva_moe_ep_reduce(gevva_moe_ep* ep, const float* route_weights, void* out, int tokens,
+                        gevva_stream_t stream);
+/* Synchronises; returns and clears the device status word; optionally reports how many rows
+ * this rank received in the last step. */
+int gevva_moe_ep_status(gevva_moe_ep* ep, int* received_rows);
+
 /* Expert packer for synthetic or freshly quantised weights; stands where
  * tools/pack_trtllm_experts.py:51-65 stands in the reference (stack experts,
  * interleave block scales) and also performs the NVFP4 quantisation itself:

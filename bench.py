@@ -90,22 +90,25 @@ class ClockSampler:
 
 
 def build_layer(device, rank):
+    """Same experts, router and static scales on every rank (seed 0, calibrated on one fixed
+    batch); each rank then gets its own input batch."""
     import torch
     from gevva_b200.synthetic import SyntheticLayer
-    layer = SyntheticLayer(seed=rank, max_tokens=TOKENS, device=device, bias_std=0.5)
-    x = layer.inputs(TOKENS, seed=1000 + rank)
-    layer.calibrate(x)
+    layer = SyntheticLayer(seed=0, max_tokens=TOKENS, device=device, bias_std=0.5)
+    layer.calibrate(layer.inputs(TOKENS, seed=1000))
     layer.bias_row = layer.bias.to(torch.bfloat16)
-    return layer, x
+    return layer, layer.inputs(TOKENS, seed=1000 + rank)
 
 
 def layer_step(layer, x, out, weights, ids):
-    """The timed unit: router projection with bias (one library GEMM) + our kernels."""
+    """The timed unit: router projection with bias (one library GEMM) + our kernels.  With more
+    than one GPU the experts are sharded and `layer.ep` exchanges rows over NVLink."""
     import torch
     import gevva_b200
     logits = torch.addmm(layer.bias_row, x, layer.router_w.t())
     gevva_b200.route_128_top8(logits, layer.expert_scale, weights=weights, ids=ids)
-    layer.runner.launch_batch(x, ids, weights, out, x.shape[0])
+    runner = layer.ep if getattr(layer, "ep", None) is not None else layer.runner
+    runner.launch_batch(x, ids, weights, out, x.shape[0])
 
 
 def decode_sweep(layer, device, steps):
@@ -260,13 +263,25 @@ def run_gpu(args):
         torch.cuda.synchronize()
 
     layer, x = build_layer(device, rank)
+    layer.ep = None
+    if world > 1:
+        from gevva_b200.expert_parallel import ExpertParallelRunner, local_expert_weights
+        layer.ep = ExpertParallelRunner(local_expert_weights(layer.weights, rank, world),
+                                        layer.weights.in_scale_q1, TOKENS)
     out = torch.empty_like(x)
     weights = torch.empty((TOKENS, TOP_K), dtype=torch.float32, device=device)
     ids = torch.empty((TOKENS, TOP_K), dtype=torch.int32, device=device)
 
+    def check():
+        if layer.ep is not None:
+            status, _ = layer.ep.status()
+            if status != 0:
+                raise RuntimeError(f"expert-parallel device status {status}")
+        layer.runner.check()
+
     for _ in range(max(args.warmup, 3)):
         layer_step(layer, x, out, weights, ids)
-    layer.runner.check()
+    check()
 
     # ---- device-resident throughput ("value") -----------------------------------
     sampler = ClockSampler(local_rank)
@@ -280,7 +295,7 @@ def run_gpu(args):
     barrier()
     clocks = sampler.stop()
     elapsed_ms = start.elapsed_time(stop)
-    layer.runner.check()
+    check()
 
     # ---- end to end through host buffers ("e2e") -------------------------------
     host_in = x.cpu().pin_memory()
@@ -322,6 +337,11 @@ def run_gpu(args):
     w13_ms = sum(a.elapsed_time(b) for a, b in zip(g0, g1)) / args.steps
     w2_ms = sum(a.elapsed_time(b) for a, b in zip(h0, h1)) / args.steps
 
+    ep_phases = None
+    if layer.ep is not None:
+        samples = [layer.ep.timed_step(x, ids, weights, out, TOKENS) for _ in range(5)]
+        ep_phases = {k: sum(s[k] for s in samples[1:]) / (len(samples) - 1) for k in samples[0]}
+
     times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -333,7 +353,9 @@ def run_gpu(args):
         achieved = W13_FLOP_PER_TOKEN * TOKENS / (w13_ms * 1e-3) / 1e12
         total_tokens = TOKENS * world * args.steps
         value = total_tokens / (elapsed_ms * 1e-3)
-        launches_per_step = 8  # route, 3 sort kernels, quantise, w13 (+GeGLU), w2, reduce
+        # single GPU: route, 3 sort kernels, quantise, w13 (+GeGLU), w2, reduce; expert parallel:
+        # route, 3 sort, publish, send-bases, dispatch, receive-plan, w13, w2, combine, reduce
+        launches_per_step = 8 if world == 1 else 12
         line = {
             "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -342,7 +364,9 @@ def run_gpu(args):
             "data": "synthetic",
             "config": {"workload": WORKLOAD, "tokens_per_gpu": TOKENS, "experts": EXPERTS,
                        "top_k": TOP_K, "hidden": HIDDEN, "expert_width": INTER,
-                       "parallelism": "single GPU" if world == 1 else f"{world} data-parallel replicas",
+                       "parallelism": "single GPU" if world == 1 else
+                       f"expert parallel x{world}: 128/{world} experts per GPU, tokens data-parallel, "
+                       "dispatch/combine by stores into peer memory over NVLink",
                        "l2": "inputs larger than L2: 428 MB of expert weights stream every step"},
             "layer_tflops": FLOP_PER_TOKEN * TOKENS / (elapsed_ms / args.steps * 1e-3) / 1e12,
             "roofline": {"bound": "tensor", "kernel": "grouped_nvfp4_gemm_kernel<kGeglu> (w13 + GeGLU + requantise)",
@@ -351,6 +375,7 @@ def run_gpu(args):
                          "peak_source": f"4 x bf16_tflops of MEASURED_PEAKS.json ({peak_kind}); "
                                         "no FP4 entry exists",
                          "frac_of_nominal_9000": achieved / NOMINAL_FP4_TFLOPS,
+                         "measured_on": "this GPU's own 4096-token batch through the single-GPU stages",
                          "kernel_ms": w13_ms, "w2_kernel_ms": w2_ms,
                          "w2_tflops": (FLOP_PER_TOKEN - W13_FLOP_PER_TOKEN) * TOKENS / (w2_ms * 1e-3) / 1e12},
             "e2e": {"value": total_tokens / (e2e_ms * 1e-3), "unit": "tokens/s",
@@ -358,6 +383,8 @@ def run_gpu(args):
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }
+        if ep_phases is not None:
+            line["ep_phases_us_rank0"] = ep_phases
         if world == 1 and not args.no_decode:
             line["decode"] = decode_sweep(layer, device, max(args.steps, 20))
         if world == 1 and not args.no_cpu_baseline:

@@ -12,12 +12,13 @@
 //   2. dispatch     from the full count matrix compute, for every v, where this
 //                   rank's rows land in the owner's receive buffer; quantise each
 //                   route with its expert's static scale and store codes and scale
-//                   bytes straight into the owner's w13 operand buffers
+//                   rows straight into the owner's receive buffers
 //                   (1584 B per route instead of 5632 B of bf16)     -- barrier --
 //   3. compute      build the group geometry of the local experts from the same
-//                   matrix; w13 (+GeGLU+requantise) and w2 grouped GEMMs; copy
-//                   every result row back into its source rank's combine buffer
-//                   at the source's own sorted position              -- barrier --
+//                   matrix; w13 (+GeGLU+requantise) and w2 grouped GEMMs; the w2
+//                   epilogue stores every result row straight into its source
+//                   rank's combine buffer at the source's own sorted position
+//                                                                    -- barrier --
 //   4. reduce       the source's usual weighted reduce over its eight routes.
 // Receive order is fixed by (local expert, source rank, source order), so results do
 // not depend on timing.  All peer traffic is plain global stores through mapped
@@ -44,9 +45,10 @@ constexpr int kMaxWorld = 8;
 struct EpDevice {            // device-visible description, passed to kernels by value
   int rank, world, local_experts;
   uint8_t* peer_codes[kMaxWorld];   // each rank's w13 operand codes [capacity, 1408]
-  uint8_t* peer_scales[kMaxWorld];  // each rank's w13 operand scale regions
+  uint8_t* peer_scales[kMaxWorld];  // each rank's scale staging, row-major [capacity, 176]
   __nv_bfloat16* peer_combine[kMaxWorld];  // each rank's combine buffer [8*T_local, 2816]
   int* peer_counts[kMaxWorld];      // each rank's count matrix [world][128]
+  int* peer_flags[kMaxWorld];       // each rank's barrier flags [world]
   int* counts;                      // == peer_counts[rank]
   int* send_row_base;               // [128] by v
   int* send_src_prefix;             // [128] by v
@@ -54,6 +56,32 @@ struct EpDevice {            // device-visible description, passed to kernels by
   int* source_offsets;              // [world][EL]: sorted position of (source, local expert) on the source
   const int* remap;                 // [128] e -> v
 };
+
+// ---- barrier across ranks -----------------------------------------------------------
+// Rank r stores `epoch` into flag r of every peer, then waits until all of its own flags
+// have reached `epoch`.  The stores of earlier kernels of this stream are complete when this
+// kernel starts; the fence orders the flag behind them at system scope.  The wait is bounded:
+// on expiry the status word gets kWaitTimeout and the kernel returns.
+__global__ void __launch_bounds__(32) ep_barrier_kernel(EpDevice ep, int epoch, int* status) {
+  const int lane = threadIdx.x;
+  if (lane < ep.world) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(ep.peer_flags[lane] + ep.rank), "r"(epoch)
+                 : "memory");
+    const int* mine = ep.peer_flags[ep.rank] + lane;
+    const long long start = clock64();
+    for (;;) {
+      int seen;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+      if (seen - epoch >= 0) break;
+      if (clock64() - start > 4000000000ll) {
+        atomicExch(status, static_cast<int>(kWaitTimeout));
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+}
 
 // ---- 1: publish this rank's per-expert counts into every peer's matrix -------------
 __global__ void __launch_bounds__(kExperts)
@@ -93,6 +121,7 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ input, const int* __restric
   __shared__ float route_multiplier[kTopK];
   __shared__ uint8_t* route_codes[kTopK];
   __shared__ uint8_t* route_scales[kTopK];
+  __shared__ __align__(16) uint32_t scale_words[kTopK][groups / 4];  // one 176-byte row per route
   const int token = blockIdx.x;
   if (threadIdx.x < kTopK) {
     const int route = token * kTopK + threadIdx.x;
@@ -104,12 +133,9 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ input, const int* __restric
       const int owner = v / ep.local_experts;
       const int j = plan.inverse_routes[route] - plan.expert_offsets[v];
       const int row = ep.send_row_base[v] + j;
-      const int row_in_expert = ep.send_src_prefix[v] + j;
       route_multiplier[threadIdx.x] = in_scale_q_global[expert];
       route_codes[threadIdx.x] = ep.peer_codes[owner] + static_cast<size_t>(row) * (kHidden / 2);
-      route_scales[threadIdx.x] = ep.peer_scales[owner] +
-                                  static_cast<size_t>(ep.send_scale_rows[v]) * groups +
-                                  sf_offset(row_in_expert, 0, groups);
+      route_scales[threadIdx.x] = ep.peer_scales[owner] + static_cast<size_t>(row) * groups;
     }
   }
   const int lane = threadIdx.x & 31;
@@ -150,9 +176,14 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ input, const int* __restric
     word |= __shfl_sync(0xffffffffu, scale, base_lane + 2) << 8;
     word |= __shfl_sync(0xffffffffu, scale, base_lane + 4) << 16;
     word |= __shfl_sync(0xffffffffu, scale, base_lane + 6) << 24;
-    if ((lane & 7) == 0)
-      *reinterpret_cast<uint32_t*>(route_scales[k] + static_cast<size_t>(quad) * 512) = word;
+    if ((lane & 7) == 0) scale_words[k][quad] = word;
   }
+  // Scale bytes cross NVLink as one contiguous 176-byte row per route (eleven 16-byte
+  // stores by one warp); the owner puts them into the MMA's interleaved layout itself.
+  __syncthreads();
+  const int k = threadIdx.x >> 5;
+  if (k < kTopK && lane < groups / 16 && route_codes[k])
+    reinterpret_cast<uint4*>(route_scales[k])[lane] = reinterpret_cast<const uint4*>(scale_words[k])[lane];
 }
 
 // ---- 3a: group geometry of the local experts ---------------------------------------
@@ -176,12 +207,40 @@ __global__ void __launch_bounds__(kExperts) ep_receive_plan_kernel(EpDevice ep, 
   }
 }
 
-// ---- 3b: return result rows to their sources ---------------------------------------
-__global__ void __launch_bounds__(kHidden / 8)
-ep_combine_kernel(const __nv_bfloat16* __restrict__ routed, EpDevice ep, RoutePlan plan) {
+// ---- 3a': received scale rows -> the interleaved layout of the w13 operand -------------
+__global__ void __launch_bounds__(256)
+ep_swizzle_scales_kernel(const uint8_t* __restrict__ staged, EpDevice ep, RoutePlan plan,
+                         uint8_t* __restrict__ scales) {
+  constexpr int groups = kHidden / 16;
+  constexpr int words = groups / 4;  // 44 per row
   const int el = ep.local_experts;
   const int total = plan.expert_offsets[kExperts];
-  for (int row = blockIdx.x; row < total; row += gridDim.x) {
+  const long long items = static_cast<long long>(total) * words;
+  for (long long index = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; index < items;
+       index += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int row = static_cast<int>(index / words);
+    const int word = static_cast<int>(index % words);
+    int lo = 0, hi = el - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (plan.expert_offsets[mid] <= row) lo = mid; else hi = mid - 1;
+    }
+    const int row_in_expert = row - plan.expert_offsets[lo];
+    const uint32_t value = reinterpret_cast<const uint32_t*>(staged + static_cast<size_t>(row) * groups)[word];
+    *reinterpret_cast<uint32_t*>(scales + static_cast<size_t>(plan.scale_row_offsets[lo]) * groups +
+                                 sf_offset(row_in_expert, 4 * word, groups)) = value;
+  }
+}
+
+// ---- 3b: where every received row's result goes ------------------------------------
+// One 64-bit address per receive row: the row of the source rank's combine buffer at the
+// source's own sorted position.  The w2 GEMM epilogue stores through these addresses, so
+// results cross NVLink while the GEMM is still running and never touch local memory.
+__global__ void __launch_bounds__(256)
+ep_row_destinations_kernel(EpDevice ep, RoutePlan plan, unsigned long long* __restrict__ row_dest) {
+  const int el = ep.local_experts;
+  const int total = plan.expert_offsets[kExperts];
+  for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < total; row += gridDim.x * blockDim.x) {
     // local expert of this row: the last le with expert_offsets[le] <= row
     int lo = 0, hi = el - 1;
     while (lo < hi) {
@@ -198,8 +257,8 @@ ep_combine_kernel(const __nv_bfloat16* __restrict__ routed, EpDevice ep, RoutePl
       within -= c;
     }
     const int dst_row = ep.source_offsets[s * el + le] + within;
-    const uint4 value = reinterpret_cast<const uint4*>(routed + static_cast<size_t>(row) * kHidden)[threadIdx.x];
-    reinterpret_cast<uint4*>(ep.peer_combine[s] + static_cast<size_t>(dst_row) * kHidden)[threadIdx.x] = value;
+    row_dest[row] = reinterpret_cast<unsigned long long>(ep.peer_combine[s] +
+                                                         static_cast<size_t>(dst_row) * kHidden);
   }
 }
 
@@ -249,11 +308,13 @@ struct gevva_moe_ep {
   int max_tokens = 0;
   size_t capacity_rows = 0;
   int sm_count = 0;
+  int epoch = 0;
   // owned device memory
   int* ints = nullptr;
+  uint8_t* input_sf = nullptr;
   uint8_t* inter_codes = nullptr;
   uint8_t* inter_sf = nullptr;
-  void* w2_out = nullptr;
+  unsigned long long* row_dest = nullptr;
   uint8_t* w13_sf_tiled = nullptr;
 };
 
@@ -262,9 +323,10 @@ extern "C" {
 void gevva_moe_ep_destroy(gevva_moe_ep* ep) {
   if (!ep) return;
   cudaFree(ep->ints);
+  cudaFree(ep->input_sf);
   cudaFree(ep->inter_codes);
   cudaFree(ep->inter_sf);
-  cudaFree(ep->w2_out);
+  cudaFree(ep->row_dest);
   cudaFree(ep->w13_sf_tiled);
   delete ep;
 }
@@ -297,6 +359,7 @@ int gevva_moe_ep_create(gevva_moe_ep** out, const gevva_moe_weights* local_weigh
     ep->dev.peer_scales[d] = static_cast<uint8_t*>(config->peer_recv_sf[d]);
     ep->dev.peer_combine[d] = static_cast<__nv_bfloat16*>(config->peer_combine[d]);
     ep->dev.peer_counts[d] = config->peer_counts[d];
+    ep->dev.peer_flags[d] = config->peer_flags[d];
   }
   ep->dev.counts = ep->dev.peer_counts[rank];
 
@@ -311,10 +374,12 @@ int gevva_moe_ep_create(gevva_moe_ep** out, const gevva_moe_weights* local_weigh
   const size_t padded = cap + static_cast<size_t>(kExperts) * 127;
   cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&ep->ints), int_count * sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(ep->ints, 0, int_count * sizeof(int));
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&ep->input_sf), padded * (kHidden / 16));
+  if (e == cudaSuccess) e = cudaMemset(ep->input_sf, 0, padded * (kHidden / 16));
   if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&ep->inter_codes), cap * (kInter / 2));
   if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&ep->inter_sf), padded * (kInter / 16));
   if (e == cudaSuccess) e = cudaMemset(ep->inter_sf, 0, padded * (kInter / 16));
-  if (e == cudaSuccess) e = cudaMalloc(&ep->w2_out, cap * kHidden * 2);
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&ep->row_dest), cap * sizeof(unsigned long long));
   if (e == cudaSuccess)
     e = cudaMalloc(reinterpret_cast<void**>(&ep->w13_sf_tiled), gv::retiled_w13_scale_bytes(el));
   if (e != cudaSuccess) {
@@ -365,7 +430,7 @@ int gevva_moe_ep_create(gevva_moe_ep** out, const gevva_moe_weights* local_weigh
     gevva_moe_ep_destroy(ep);
     return GEVVA_MOE_CUDA_ERROR;
   }
-  ep->w13.a_scales = ep->dev.peer_scales[rank];
+  ep->w13.a_scales = ep->input_sf;
   ep->w13.b_scales = ep->w13_sf_tiled;
   ep->w13.alpha = local_weights->alpha1;
   ep->w13.out = nullptr;
@@ -378,12 +443,19 @@ int gevva_moe_ep_create(gevva_moe_ep** out, const gevva_moe_weights* local_weigh
   ep->w2.a_scales = ep->inter_sf;
   ep->w2.b_scales = static_cast<const uint8_t*>(local_weights->w2_sf);
   ep->w2.alpha = local_weights->alpha2;
-  ep->w2.out = ep->w2_out;
+  ep->w2.out = nullptr;
+  ep->w2.row_dest = ep->row_dest;
   ep->w2.n_out = kHidden;
   ep->w2.k_in = kInter;
   ep->w2.fused_geglu = false;
   *out = ep;
   return GEVVA_MOE_OK;
+}
+
+int gevva_moe_ep_barrier(gevva_moe_ep* ep, gevva_stream_t stream) {
+  if (!ep) return GEVVA_MOE_BAD_ARGUMENT;
+  gv::ep_barrier_kernel<<<1, 32, 0, stream>>>(ep->dev, ++ep->epoch, ep->send_plan.status);
+  return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;
 }
 
 int gevva_moe_ep_route_sort(gevva_moe_ep* ep, const int* ids, int tokens, gevva_stream_t stream) {
@@ -405,10 +477,12 @@ int gevva_moe_ep_dispatch(gevva_moe_ep* ep, const void* in, const int* ids, int 
 int gevva_moe_ep_compute(gevva_moe_ep* ep, gevva_stream_t stream) {
   if (!ep) return GEVVA_MOE_BAD_ARGUMENT;
   gv::ep_receive_plan_kernel<<<1, kExperts, 0, stream>>>(ep->dev, ep->receive_plan);
+  gv::ep_swizzle_scales_kernel<<<ep->sm_count * 4, 256, 0, stream>>>(
+      ep->dev.peer_scales[ep->dev.rank], ep->dev, ep->receive_plan, ep->input_sf);
+  gv::ep_row_destinations_kernel<<<ep->sm_count * 2, 256, 0, stream>>>(ep->dev, ep->receive_plan,
+                                                                        ep->row_dest);
   gv::launch_grouped_gemm(ep->w13, ep->receive_plan, ep->sm_count, stream);
   gv::launch_grouped_gemm(ep->w2, ep->receive_plan, ep->sm_count, stream);
-  gv::ep_combine_kernel<<<ep->sm_count * 8, kHidden / 8, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(ep->w2_out), ep->dev, ep->receive_plan);
   return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;
 }
 

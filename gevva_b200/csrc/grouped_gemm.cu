@@ -96,6 +96,7 @@ struct GemmParams {
   const uint8_t* b_scales;   // kPlain: sidecar layout; kGeglu: re-tiled copy
   const float* alpha;
   __nv_bfloat16* out;        // kPlain
+  const unsigned long long* row_dest;  // kPlain, optional: address of each output row (may be peer memory)
   uint8_t* next_codes;       // kGeglu: w2 operand codes [rows, 352]
   uint8_t* next_scales;      // kGeglu: w2 operand scale regions
   const float* next_scale_q; // kGeglu: g2.input_scale_quant [128]
@@ -439,8 +440,15 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           const int r2 = 2 * (sub * 4 + i) + (lane >> 4);
           const uint4 v =
               *reinterpret_cast<const uint4*>(staging + r2 * kStageRowBytes + ((c ^ (r2 & 15)) << 4));
-          if (quarter * 32 + r2 < rows_valid)
-            *reinterpret_cast<uint4*>(dst + static_cast<size_t>(r2) * p.n_out) = v;
+          if (quarter * 32 + r2 < rows_valid) {
+            if (p.row_dest) {
+              // expert-parallel combine: the row goes straight to its source rank's buffer
+              __nv_bfloat16* remote = reinterpret_cast<__nv_bfloat16*>(p.row_dest[row0 + quarter * 32 + r2]);
+              *reinterpret_cast<uint4*>(remote + n_tile * kTileN + c * 8) = v;
+            } else {
+              *reinterpret_cast<uint4*>(dst + static_cast<size_t>(r2) * p.n_out) = v;
+            }
+          }
         }
         named_barrier(1 + quarter, kEpilogueWarpsPerQuarter * 32);  // staging is rewritten next item
       } else {
@@ -558,6 +566,7 @@ void launch_grouped_gemm(const GemmOperands& op, const RoutePlan& plan, int sm_c
   p.b_scales = op.b_scales;
   p.alpha = op.alpha;
   p.out = static_cast<__nv_bfloat16*>(op.out);
+  p.row_dest = op.row_dest;
   p.next_codes = op.next_codes;
   p.next_scales = op.next_scales;
   p.next_scale_q = op.next_scale_q;

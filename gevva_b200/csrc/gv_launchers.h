@@ -51,6 +51,7 @@ struct GemmOperands {
   const uint8_t* b_scales;  // [128, N, K/16] swizzled per expert
   const float* alpha;       // [128]
   void* out;                // bf16 [row capacity, N]
+  const unsigned long long* row_dest;  // optional: per-row output address instead of `out`
   int n_out;                // N: 1408 or 2816
   int k_in;                 // K: 2816 or 704
   // Fused w13 form (GeGLU + requantise in the epilogue, no bf16 output): map_b then has a

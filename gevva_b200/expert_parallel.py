@@ -18,7 +18,8 @@ class _EpConfig(ctypes.Structure):
                 ("peer_recv_codes", ctypes.POINTER(ctypes.c_void_p)),
                 ("peer_recv_sf", ctypes.POINTER(ctypes.c_void_p)),
                 ("peer_combine", ctypes.POINTER(ctypes.c_void_p)),
-                ("peer_counts", ctypes.POINTER(ctypes.c_void_p))]
+                ("peer_counts", ctypes.POINTER(ctypes.c_void_p)),
+                ("peer_flags", ctypes.POINTER(ctypes.c_void_p))]
 
 
 def local_expert_weights(full: ExpertWeights, rank: int, world: int) -> ExpertWeights:
@@ -47,7 +48,7 @@ class ExpertParallelRunner:
         cap = self.world * routes
         align = lambda n: (n + 255) // 256 * 256
         sizes = [align(self.world * EXPERTS * 4), align(cap * (HIDDEN // 2)),
-                 align((cap + EXPERTS * 127) * (HIDDEN // 16)), align(routes * HIDDEN * 2)]
+                 align(cap * (HIDDEN // 16)), align(routes * HIDDEN * 2), 256]
         offsets = [0]
         for size in sizes:
             offsets.append(offsets[-1] + size)
@@ -56,7 +57,7 @@ class ExpertParallelRunner:
         self._handle_symm = symm_mem.rendezvous(self._buffer, group.group_name)
         bases = [int(p) for p in self._handle_symm.buffer_ptrs]
         arrays = []
-        for region in range(4):
+        for region in range(5):
             arr = (ctypes.c_void_p * self.world)(*[b + offsets[region] for b in bases])
             arrays.append(arr)
         self._arrays = arrays
@@ -64,13 +65,15 @@ class ExpertParallelRunner:
                            ctypes.cast(arrays[1], ctypes.POINTER(ctypes.c_void_p)),
                            ctypes.cast(arrays[2], ctypes.POINTER(ctypes.c_void_p)),
                            ctypes.cast(arrays[3], ctypes.POINTER(ctypes.c_void_p)),
-                           ctypes.cast(arrays[0], ctypes.POINTER(ctypes.c_void_p)))
+                           ctypes.cast(arrays[0], ctypes.POINTER(ctypes.c_void_p)),
+                           ctypes.cast(arrays[4], ctypes.POINTER(ctypes.c_void_p)))
         lib = library()
         vp = ctypes.c_void_p
         lib.gevva_moe_ep_create.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(_Weights), vp,
                                             ctypes.POINTER(_EpConfig)]
         lib.gevva_moe_ep_destroy.argtypes = [vp]
         lib.gevva_moe_ep_destroy.restype = None
+        lib.gevva_moe_ep_barrier.argtypes = [vp, vp]
         lib.gevva_moe_ep_route_sort.argtypes = [vp, vp, ctypes.c_int, vp]
         lib.gevva_moe_ep_dispatch.argtypes = [vp, vp, vp, ctypes.c_int, vp]
         lib.gevva_moe_ep_compute.argtypes = [vp, vp]
@@ -87,6 +90,9 @@ class ExpertParallelRunner:
             raise GevvaMoeError(status, "ExpertParallelRunner")
         self._handle = handle
         self._flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # GEVVA_EP_NCCL_BARRIER=1 swaps the flag barrier of csrc/ep.cu for an NCCL all-reduce
+        import os
+        self._nccl_barrier = os.environ.get("GEVVA_EP_NCCL_BARRIER", "0") == "1"
         dist.barrier(group)
 
     def __del__(self):
@@ -98,7 +104,10 @@ class ExpertParallelRunner:
     def _barrier(self):
         # a stream-ordered collective: no rank's next phase starts before every rank's
         # previous phase (and its stores into peer memory) has finished
-        dist.all_reduce(self._flag, group=self.group)
+        if self._nccl_barrier:
+            dist.all_reduce(self._flag, group=self.group)
+        else:
+            self._call("gevva_moe_ep_barrier", _stream_handle(None))
 
     def _call(self, name, *args):
         with torch.cuda.device(self.device):
@@ -120,6 +129,30 @@ class ExpertParallelRunner:
         self._call("gevva_moe_ep_compute", s)
         self._barrier()
         self._call("gevva_moe_ep_reduce", _ptr(route_weights), _ptr(output), tokens, s)
+
+    def timed_step(self, input, expert_ids, route_weights, output, tokens):
+        """One step with CUDA events between the phases; returns microseconds per phase
+        (barriers include waiting for the slowest rank)."""
+        names = ["route_sort", "barrier1", "dispatch", "barrier2", "compute", "barrier3", "reduce"]
+        events = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
+        s = _stream_handle(None)
+        events[0].record()
+        self._call("gevva_moe_ep_route_sort", _ptr(expert_ids), tokens, s)
+        events[1].record()
+        self._barrier()
+        events[2].record()
+        self._call("gevva_moe_ep_dispatch", _ptr(input), _ptr(expert_ids), tokens, s)
+        events[3].record()
+        self._barrier()
+        events[4].record()
+        self._call("gevva_moe_ep_compute", s)
+        events[5].record()
+        self._barrier()
+        events[6].record()
+        self._call("gevva_moe_ep_reduce", _ptr(route_weights), _ptr(output), tokens, s)
+        events[7].record()
+        torch.cuda.synchronize()
+        return {n: events[i].elapsed_time(events[i + 1]) * 1e3 for i, n in enumerate(names)}
 
     def status(self):
         rows = ctypes.c_int(0)

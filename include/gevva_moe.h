@@ -172,8 +172,9 @@ int gevva_moe_route_sort_noalloc(const int* expert_ids, int tokens, int* sorted_
  * The peer-writable buffers are allocated by the caller (e.g. symmetric memory) with the
  * same sizes on every rank and passed as host arrays of `world` device pointers:
  *   peer_counts      i32 [world*128]
+ *   peer_flags       i32 [world], zero-initialised
  *   peer_recv_codes  u8  [recv_capacity_rows, 1408]
- *   peer_recv_sf     u8  (recv_capacity_rows + 128*127) * 176
+ *   peer_recv_sf     u8  [recv_capacity_rows, 176]   (row-major scale bytes as received)
  *   peer_combine     bf16 [8*max_tokens, 2816]
  * recv_capacity_rows >= world * 8 * max_tokens covers the worst case.  local_weights holds
  * this rank's 128/world experts in the sidecar layout with [128/world] scale vectors;
@@ -189,11 +190,16 @@ typedef struct {
   void* const* peer_recv_sf;
   void* const* peer_combine;
   int* const* peer_counts;
+  int* const* peer_flags; /* i32 [world] per rank, zero-initialised: flags of gevva_moe_ep_barrier */
 } gevva_moe_ep_config;
 
 int gevva_moe_ep_create(gevva_moe_ep** out, const gevva_moe_weights* local_weights,
                         const float* in_scale_q1_global, const gevva_moe_ep_config* config);
 void gevva_moe_ep_destroy(gevva_moe_ep* ep);
+/* A barrier across the ranks, enqueued on `stream`: flags in peer memory, a bounded wait
+ * (expiry sets GEVVA_MOE_WAIT_TIMEOUT in the status word).  Every rank must call it the same
+ * number of times.  Any other stream-ordered collective may be used instead. */
+int gevva_moe_ep_barrier(gevva_moe_ep* ep, gevva_stream_t stream);
 int gevva_moe_ep_route_sort(gevva_moe_ep* ep, const int* ids, int tokens, gevva_stream_t stream);
 int gevva_moe_ep_dispatch(gevva_moe_ep* ep, const void* in, const int* ids, int tokens,
                           gevva_stream_t stream);

@@ -43,7 +43,6 @@ namespace gv {
 
 namespace {
 
-constexpr int kStages = 5;
 constexpr int kAccStages = 2;
 constexpr int kEpilogueWarpsPerQuarter = 4;  // each takes a quarter of a tile's columns
 constexpr int kEpilogueThreads = 4 * kEpilogueWarpsPerQuarter * 32;
@@ -53,22 +52,35 @@ constexpr int kEpilogueThreads = 4 * kEpilogueWarpsPerQuarter * 32;
 constexpr int kWeightProducerWarp = 2 + 4 * kEpilogueWarpsPerQuarter;
 constexpr int kGemmThreads = (kWeightProducerWarp + 1) * 32;
 constexpr uint32_t kTmemColumns = 512;
-// Scale-factor columns are per pipeline stage: a copy for K block k+1 must not wait for
-// the MMAs of K block k to finish reading theirs.
-constexpr uint32_t kSfColumn = kAccStages * kTileN;   // 256; stage s uses [256+32s, 256+32s+32)
-constexpr uint32_t kSfColumnsPerStage = 32;           // 16 for A then 16 for B
+// Scale-factor columns are per pipeline stage and K atom: a copy for the next K block must
+// not wait for the MMAs of the previous one to finish reading theirs.
+constexpr uint32_t kSfColumn = kAccStages * kTileN;   // 256
+constexpr uint32_t kSfColumnsPerAtom = 32;            // 16 for A then 16 for B
 constexpr int kOperandStageBytes = kTileM * kTileKBytes;  // 16 KiB, same for A and B
 constexpr int kStageRowBytes = kTileN * 2;                // one bf16 output row of a tile
 constexpr int kStagingBytesPerWarp = 32 * kStageRowBytes; // 8 KiB
 
 enum GemmMode { kPlain = 0, kGeglu = 1 };
 
+// A pipeline stage holds kAtoms K blocks of 256 elements (one 128-byte swizzle row each).
+// The barrier round trip of a stage (wait, fence, commit, loop) costs the issuing warp about
+// as many cycles as one K block's MMAs take on the tensor pipe, so the long-K GEMM (w13,
+// eleven K blocks) moves two K blocks per stage; the short-K one (w2, 2.75 K blocks) keeps
+// one per stage and spends the shared memory on the store staging instead.
+template <int kMode> struct StageShape {
+  static constexpr int kAtoms = kMode == kGeglu ? 2 : 1;
+  static constexpr int kStages = kMode == kGeglu ? 3 : 5;
+};
+
+template <int kMode>
 struct alignas(1024) GemmSmem {
-  uint8_t a[kStages][kOperandStageBytes];
-  uint8_t b[kStages][kOperandStageBytes];
-  uint8_t sfa[kStages][kSfStageBytes];
-  uint8_t sfb[kStages][kSfStageBytes];
-  uint8_t staging[4][kStagingBytesPerWarp];  // kPlain epilogue only
+  static constexpr int kAtoms = StageShape<kMode>::kAtoms;
+  static constexpr int kStages = StageShape<kMode>::kStages;
+  uint8_t a[kStages][kAtoms * kOperandStageBytes];
+  uint8_t b[kStages][kAtoms * kOperandStageBytes];
+  uint8_t sfa[kStages][kAtoms * kSfStageBytes];
+  uint8_t sfb[kStages][kAtoms * kSfStageBytes];
+  uint8_t staging[4][kMode == kPlain ? kStagingBytesPerWarp : 16];  // kPlain epilogue only
   uint64_t full[kStages];
   uint64_t empty[kStages];
   uint64_t acc_full[kAccStages];
@@ -82,8 +94,12 @@ struct alignas(1024) GemmSmem {
 #endif
 };
 
-constexpr size_t kGemmSmemBytes = sizeof(GemmSmem) + 1024;  // slack for manual alignment
-static_assert(kGemmSmemBytes <= 232448, "shared memory budget of one sm_100 CTA");
+template <int kMode> constexpr size_t gemm_smem_bytes() { return sizeof(GemmSmem<kMode>) + 1024; }
+static_assert(gemm_smem_bytes<kPlain>() <= 232448 && gemm_smem_bytes<kGeglu>() <= 232448,
+              "shared memory budget of one sm_100 CTA");
+static_assert(kSfColumn + kSfColumnsPerAtom * 2 * 3 <= kTmemColumns &&
+                  kSfColumn + kSfColumnsPerAtom * 5 <= kTmemColumns,
+              "tensor memory budget");
 
 // Instruction descriptor: E2M1 x E2M1 (format 1 in the mxf4 kinds), both K-major,
 // UE4M3 scales (bit 23 clear), N at [17,23) in units of 8, M at [24,29) in units of 16,
@@ -120,8 +136,8 @@ constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s at 2 GHz
 // kBackoff: sleep between polls.  Warps that wait with slack (producers, epilogue) must not
 // spin, because a spinning warp takes issue slots from the MMA warp on the same scheduler and
 // every instruction of the main loop then costs several times its latency.
-template <bool kBackoff>
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, GemmSmem* smem,
+template <bool kBackoff, class Smem>
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Smem* smem,
                                               int* status) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
@@ -216,8 +232,11 @@ template <int kMode>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                           const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+  using Smem = GemmSmem<kMode>;
+  constexpr int kStages = Smem::kStages;
+  constexpr int kAtoms = Smem::kAtoms;
   extern __shared__ uint8_t smem_raw[];
-  GemmSmem* smem = reinterpret_cast<GemmSmem*>(
+  Smem* smem = reinterpret_cast<Smem*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -275,29 +294,32 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         row = expert * p.n_out + n_tile * kTileN;
         sf_src = p.b_scales + static_cast<size_t>(row) * p.groups;
       }
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
+      for (int kb = 0; kb < p.k_blocks; kb += kAtoms) {
         ok = __all_sync(0xffffffffu, wait_or_abort<true>(&smem->empty[stage], phase ^ 1u, smem, p.status));
         if (!ok) break;
         if (elect_one()) {
           if (!weight_side) GV_STAMP(0);
+          const int atoms = p.k_blocks - kb < kAtoms ? p.k_blocks - kb : kAtoms;
+          const bool has_last = kb + atoms == p.k_blocks;
           const uint32_t sf_bytes =
-              (kb == p.k_blocks - 1 ? p.last_mmas : 4) * static_cast<uint32_t>(kSfAtomBytes);
-          mbar_arrive_expect_tx(&smem->full[stage], kOperandStageBytes + sf_bytes);
-          if (!weight_side) {
-            tma_load_2d(smem->a[stage], &map_a, &smem->full[stage], kb * kTileKBytes, row);
-            bulk_load_1d(smem->sfa[stage], sf_src + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes,
-                         &smem->full[stage]);
-          } else {
-            if (kMode == kGeglu) {
-              tma_load_2d(smem->b[stage], &map_b, &smem->full[stage], kb * kTileKBytes, row);
-              tma_load_2d(smem->b[stage] + kOperandStageBytes / 2, &map_b, &smem->full[stage],
-                          kb * kTileKBytes, row2);
+              static_cast<uint32_t>((atoms - 1) * 4 + (has_last ? p.last_mmas : 4)) * kSfAtomBytes;
+          mbar_arrive_expect_tx(&smem->full[stage], atoms * kOperandStageBytes + sf_bytes);
+#pragma unroll
+          for (int atom = 0; atom < kAtoms; ++atom) {
+            if (atom >= atoms) break;
+            const int x = (kb + atom) * kTileKBytes;
+            if (!weight_side) {
+              tma_load_2d(smem->a[stage] + atom * kOperandStageBytes, &map_a, &smem->full[stage], x, row);
+            } else if (kMode == kGeglu) {
+              tma_load_2d(smem->b[stage] + atom * kOperandStageBytes, &map_b, &smem->full[stage], x, row);
+              tma_load_2d(smem->b[stage] + atom * kOperandStageBytes + kOperandStageBytes / 2, &map_b,
+                          &smem->full[stage], x, row2);
             } else {
-              tma_load_2d(smem->b[stage], &map_b, &smem->full[stage], kb * kTileKBytes, row);
+              tma_load_2d(smem->b[stage] + atom * kOperandStageBytes, &map_b, &smem->full[stage], x, row);
             }
-            bulk_load_1d(smem->sfb[stage], sf_src + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes,
-                         &smem->full[stage]);
           }
+          bulk_load_1d(weight_side ? smem->sfb[stage] : smem->sfa[stage],
+                       sf_src + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes, &smem->full[stage]);
           if (!weight_side) GV_STAMP(0);
         }
         __syncwarp();
@@ -346,31 +368,41 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         break;
       const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc_stage * kTileN);
       bool ok = true;
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
+      for (int kb = 0; kb < p.k_blocks; kb += kAtoms) {
         ok = __all_sync(0xffffffffu, wait_or_abort<false>(&smem->full[stage], phase, smem, p.status));
         if (!ok) break;
         tc_fence_after_sync();
-        // Descriptor low words advance by whole stages; the K offset of each MMA (+32 bytes
-        // inside the swizzle row) and each scale atom (+512 bytes) are immediates.
-        const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * (kOperandStageBytes >> 4);
-        const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(stage) * (kOperandStageBytes >> 4);
-        const uint32_t sfa_lo = sfa_lo0 + static_cast<uint32_t>(stage) * (kSfStageBytes >> 4);
-        const uint32_t sfb_lo = sfb_lo0 + static_cast<uint32_t>(stage) * (kSfStageBytes >> 4);
-        const uint32_t tmem_sf = tmem_base + kSfColumn + kSfColumnsPerStage * stage;
-        const uint32_t accumulate = kb != 0 ? 1u : 0u;
+        // Descriptor low words advance by whole stages and K atoms; the K offset of each MMA
+        // (+32 bytes inside the swizzle row) and each scale atom (+512 bytes) are immediates.
+        const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * (kAtoms * kOperandStageBytes >> 4);
+        const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(stage) * (kAtoms * kOperandStageBytes >> 4);
+        const uint32_t sfa_lo = sfa_lo0 + static_cast<uint32_t>(stage) * (kAtoms * kSfStageBytes >> 4);
+        const uint32_t sfb_lo = sfb_lo0 + static_cast<uint32_t>(stage) * (kAtoms * kSfStageBytes >> 4);
+        const uint32_t tmem_sf = tmem_base + kSfColumn + kSfColumnsPerAtom * kAtoms * stage;
         if (leader) {
           GV_STAMP(1);
-          if (kb != p.k_blocks - 1 || full_last) {
-            issue_k_block<4>(tmem_acc, tmem_sf, a_lo, b_lo, sfa_lo, sfb_lo, hi_ab, hi_sf, accumulate);
-          } else if (p.last_mmas == 3) {
-            issue_k_block<3>(tmem_acc, tmem_sf, a_lo, b_lo, sfa_lo, sfb_lo, hi_ab, hi_sf, accumulate);
-          } else if (p.last_mmas == 2) {
-            issue_k_block<2>(tmem_acc, tmem_sf, a_lo, b_lo, sfa_lo, sfb_lo, hi_ab, hi_sf, accumulate);
-          } else {
-            issue_k_block<1>(tmem_acc, tmem_sf, a_lo, b_lo, sfa_lo, sfb_lo, hi_ab, hi_sf, accumulate);
+#pragma unroll
+          for (int atom = 0; atom < kAtoms; ++atom) {
+            const int k = kb + atom;
+            if (k >= p.k_blocks) break;
+            const uint32_t accumulate = k != 0 ? 1u : 0u;
+            const uint32_t aa = a_lo + atom * (kOperandStageBytes >> 4);
+            const uint32_t bb = b_lo + atom * (kOperandStageBytes >> 4);
+            const uint32_t sa = sfa_lo + atom * (kSfStageBytes >> 4);
+            const uint32_t sb = sfb_lo + atom * (kSfStageBytes >> 4);
+            const uint32_t ts = tmem_sf + atom * kSfColumnsPerAtom;
+            if (k != p.k_blocks - 1 || full_last) {
+              issue_k_block<4>(tmem_acc, ts, aa, bb, sa, sb, hi_ab, hi_sf, accumulate);
+            } else if (p.last_mmas == 3) {
+              issue_k_block<3>(tmem_acc, ts, aa, bb, sa, sb, hi_ab, hi_sf, accumulate);
+            } else if (p.last_mmas == 2) {
+              issue_k_block<2>(tmem_acc, ts, aa, bb, sa, sb, hi_ab, hi_sf, accumulate);
+            } else {
+              issue_k_block<1>(tmem_acc, ts, aa, bb, sa, sb, hi_ab, hi_sf, accumulate);
+            }
           }
           tc_commit(&smem->empty[stage]);  // frees the stage once these MMAs have read it
-          if (kb == p.k_blocks - 1) tc_commit(&smem->acc_full[acc_stage]);
+          if (kb + kAtoms >= p.k_blocks) tc_commit(&smem->acc_full[acc_stage]);
           GV_STAMP(1);
         }
         if (++stage == kStages) {
@@ -540,11 +572,11 @@ extern "C" void gv_trace_read(unsigned int* out, int* counts) {
 int prepare_grouped_gemm() {
   cudaError_t e = cudaFuncSetAttribute(grouped_nvfp4_gemm_kernel<kPlain>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(kGemmSmemBytes));
+                                       static_cast<int>(gemm_smem_bytes<kPlain>()));
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(grouped_nvfp4_gemm_kernel<kGeglu>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(kGemmSmemBytes));
+                             static_cast<int>(gemm_smem_bytes<kGeglu>()));
   return static_cast<int>(e);
 }
 
@@ -582,11 +614,11 @@ void launch_grouped_gemm(const GemmOperands& op, const RoutePlan& plan, int sm_c
   if (op.fused_geglu) {
     p.n_tiles = kInter / 64;
     grouped_nvfp4_gemm_kernel<kGeglu>
-        <<<sm_count, kGemmThreads, kGemmSmemBytes, stream>>>(op.map_a, op.map_b, p);
+        <<<sm_count, kGemmThreads, gemm_smem_bytes<kGeglu>(), stream>>>(op.map_a, op.map_b, p);
   } else {
     p.n_tiles = op.n_out / kTileN;
     grouped_nvfp4_gemm_kernel<kPlain>
-        <<<sm_count, kGemmThreads, kGemmSmemBytes, stream>>>(op.map_a, op.map_b, p);
+        <<<sm_count, kGemmThreads, gemm_smem_bytes<kPlain>(), stream>>>(op.map_a, op.map_b, p);
   }
 }
 

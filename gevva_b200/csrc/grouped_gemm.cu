@@ -60,7 +60,7 @@ constexpr int kOperandStageBytes = kTileM * kTileKBytes;  // 16 KiB, same for A 
 constexpr int kStageRowBytes = kTileN * 2;                // one bf16 output row of a tile
 constexpr int kStagingBytesPerWarp = 32 * kStageRowBytes; // 8 KiB
 
-enum GemmMode { kPlain = 0, kGeglu = 1 };
+enum GemmMode { kPlain = 0, kGeglu = 1, kFp8 = 2 };  // kFp8: dense E4M3 operands, plain epilogue
 
 // A pipeline stage holds kAtoms K blocks of 256 elements (one 128-byte swizzle row each).
 // The barrier round trip of a stage (wait, fence, commit, loop) costs the issuing warp about
@@ -80,7 +80,7 @@ struct alignas(1024) GemmSmem {
   uint8_t b[kStages][kAtoms * kOperandStageBytes];
   uint8_t sfa[kStages][kAtoms * kSfStageBytes];
   uint8_t sfb[kStages][kAtoms * kSfStageBytes];
-  uint8_t staging[4][kMode == kPlain ? kStagingBytesPerWarp : 16];  // kPlain epilogue only
+  uint8_t staging[4][kMode != kGeglu ? kStagingBytesPerWarp : 16];  // plain epilogue only
   uint64_t full[kStages];
   uint64_t empty[kStages];
   uint64_t acc_full[kAccStages];
@@ -95,7 +95,8 @@ struct alignas(1024) GemmSmem {
 };
 
 template <int kMode> constexpr size_t gemm_smem_bytes() { return sizeof(GemmSmem<kMode>) + 1024; }
-static_assert(gemm_smem_bytes<kPlain>() <= 232448 && gemm_smem_bytes<kGeglu>() <= 232448,
+static_assert(gemm_smem_bytes<kPlain>() <= 232448 && gemm_smem_bytes<kGeglu>() <= 232448 &&
+                  gemm_smem_bytes<kFp8>() <= 232448,
               "shared memory budget of one sm_100 CTA");
 static_assert(kSfColumn + kSfColumnsPerAtom * 2 * 3 <= kTmemColumns &&
                   kSfColumn + kSfColumnsPerAtom * 5 <= kTmemColumns,
@@ -202,6 +203,33 @@ __device__ __forceinline__ void issue_k_block(uint32_t tmem_acc, uint32_t tmem_s
 #undef GV_PROLOGUE
 }
 
+// Dense FP8 form of the same: kMmas MMAs of K = 32 E4M3 elements (32 bytes, the same
+// descriptor step), no scale factors.  Instruction descriptor: fp32 accumulate (bit 4),
+// E4M3 x E4M3 (format 0), both K-major, N and M as above.
+constexpr uint32_t kInstrDescFp8 = (1u << 4) | (static_cast<uint32_t>(kTileN >> 3) << 17) |
+                                   (static_cast<uint32_t>(kTileM >> 4) << 24);
+
+template <int kMmas>
+__device__ __forceinline__ void issue_k_block_fp8(uint32_t tmem_acc, uint32_t a_lo, uint32_t b_lo,
+                                                  uint32_t hi_ab, uint32_t accumulate) {
+#define GV_MMA8(j, pred)                                                   \
+  "add.u32 lo, %1, " #j "*2;\n\t"                                          \
+  "mov.b64 d0, {lo, %3};\n\t"                                              \
+  "add.u32 lo, %2, " #j "*2;\n\t"                                          \
+  "mov.b64 d1, {lo, %3};\n\t"                                              \
+  "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], d0, d1, %4, " pred ";\n\t"
+#define GV_OPERANDS8 ::"r"(tmem_acc), "r"(a_lo), "r"(b_lo), "r"(hi_ab), "r"(kInstrDescFp8), "r"(accumulate) : "memory"
+#define GV_PROLOGUE8 "{\n\t.reg .pred p, pt;\n\t.reg .b32 lo;\n\t.reg .b64 d0, d1;\n\t" \
+                     "setp.ne.b32 p, %5, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+  asm volatile(GV_PROLOGUE8 GV_MMA8(0, "p") "}" GV_OPERANDS8);
+  if constexpr (kMmas >= 2) asm volatile(GV_PROLOGUE8 GV_MMA8(1, "pt") "}" GV_OPERANDS8);
+  if constexpr (kMmas >= 3) asm volatile(GV_PROLOGUE8 GV_MMA8(2, "pt") "}" GV_OPERANDS8);
+  if constexpr (kMmas >= 4) asm volatile(GV_PROLOGUE8 GV_MMA8(3, "pt") "}" GV_OPERANDS8);
+#undef GV_MMA8
+#undef GV_OPERANDS8
+#undef GV_PROLOGUE8
+}
+
 #if defined(GV_TRACE)
 // Debug build only: cycle stamps of CTA 0's roles, kept in shared memory while the kernel
 // runs (a stamp costs one shared store) and copied out at the end; gv_trace_read() reads them.
@@ -302,7 +330,8 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           const int atoms = p.k_blocks - kb < kAtoms ? p.k_blocks - kb : kAtoms;
           const bool has_last = kb + atoms == p.k_blocks;
           const uint32_t sf_bytes =
-              static_cast<uint32_t>((atoms - 1) * 4 + (has_last ? p.last_mmas : 4)) * kSfAtomBytes;
+              kMode == kFp8 ? 0u
+                            : static_cast<uint32_t>((atoms - 1) * 4 + (has_last ? p.last_mmas : 4)) * kSfAtomBytes;
           mbar_arrive_expect_tx(&smem->full[stage], atoms * kOperandStageBytes + sf_bytes);
 #pragma unroll
           for (int atom = 0; atom < kAtoms; ++atom) {
@@ -318,8 +347,9 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
               tma_load_2d(smem->b[stage] + atom * kOperandStageBytes, &map_b, &smem->full[stage], x, row);
             }
           }
-          bulk_load_1d(weight_side ? smem->sfb[stage] : smem->sfa[stage],
-                       sf_src + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes, &smem->full[stage]);
+          if (kMode != kFp8)
+            bulk_load_1d(weight_side ? smem->sfb[stage] : smem->sfa[stage],
+                         sf_src + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes, &smem->full[stage]);
           if (!weight_side) GV_STAMP(0);
         }
         __syncwarp();
@@ -391,7 +421,12 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
             const uint32_t sa = sfa_lo + atom * (kSfStageBytes >> 4);
             const uint32_t sb = sfb_lo + atom * (kSfStageBytes >> 4);
             const uint32_t ts = tmem_sf + atom * kSfColumnsPerAtom;
-            if (k != p.k_blocks - 1 || full_last) {
+            if (kMode == kFp8) {
+              if (k != p.k_blocks - 1 || full_last) issue_k_block_fp8<4>(tmem_acc, aa, bb, hi_ab, accumulate);
+              else if (p.last_mmas == 3) issue_k_block_fp8<3>(tmem_acc, aa, bb, hi_ab, accumulate);
+              else if (p.last_mmas == 2) issue_k_block_fp8<2>(tmem_acc, aa, bb, hi_ab, accumulate);
+              else issue_k_block_fp8<1>(tmem_acc, aa, bb, hi_ab, accumulate);
+            } else if (k != p.k_blocks - 1 || full_last) {
               issue_k_block<4>(tmem_acc, ts, aa, bb, sa, sb, hi_ab, hi_sf, accumulate);
             } else if (p.last_mmas == 3) {
               issue_k_block<3>(tmem_acc, ts, aa, bb, sa, sb, hi_ab, hi_sf, accumulate);
@@ -439,7 +474,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       const int row_local = quarter * 32 + lane;
       const uint32_t tmem_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                 static_cast<uint32_t>(acc_stage * kTileN);
-      if (kMode == kPlain) {
+      if (kMode != kGeglu) {
         // This warp's 32 rows x 32 columns go to the quarter's staging tile (32 rows x 256
         // bytes).  16-byte chunk c of row r lives at chunk position c ^ (r & 15), which keeps
         // the row-wise writes here and the two-rows-per-instruction reads below at the
@@ -577,6 +612,9 @@ int prepare_grouped_gemm() {
     e = cudaFuncSetAttribute(grouped_nvfp4_gemm_kernel<kGeglu>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(gemm_smem_bytes<kGeglu>()));
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(grouped_nvfp4_gemm_kernel<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(gemm_smem_bytes<kFp8>()));
   return static_cast<int>(e);
 }
 
@@ -608,10 +646,15 @@ void launch_grouped_gemm(const GemmOperands& op, const RoutePlan& plan, int sm_c
   p.num_m_tiles = plan.num_m_tiles;
   p.status = plan.status;
   p.n_out = op.n_out;
+  const int k_bytes = op.fp8 ? op.k_in : op.k_in / 2;
   p.groups = op.k_in / 16;
-  p.k_blocks = (op.k_in + kTileK - 1) / kTileK;
-  p.last_mmas = (op.k_in - (p.k_blocks - 1) * kTileK) / 64;
-  if (op.fused_geglu) {
+  p.k_blocks = (k_bytes + kTileKBytes - 1) / kTileKBytes;
+  p.last_mmas = (k_bytes - (p.k_blocks - 1) * kTileKBytes) / 32;
+  if (op.fp8) {
+    p.n_tiles = op.n_out / kTileN;
+    grouped_nvfp4_gemm_kernel<kFp8>
+        <<<sm_count, kGemmThreads, gemm_smem_bytes<kFp8>(), stream>>>(op.map_a, op.map_b, p);
+  } else if (op.fused_geglu) {
     p.n_tiles = kInter / 64;
     grouped_nvfp4_gemm_kernel<kGeglu>
         <<<sm_count, kGemmThreads, gemm_smem_bytes<kGeglu>(), stream>>>(op.map_a, op.map_b, p);

@@ -58,6 +58,7 @@ struct GemmOperands {
   // 64-row box, b_scales is the re-tiled copy made by launch_retile_w13_scales, and the
   // results go to the w2 operand buffers below.
   bool fused_geglu;
+  bool fp8;                   // dense E4M3 x E4M3 (no block scales); k_in counts bytes = elements
   uint8_t* next_codes;        // [row capacity, 352]
   uint8_t* next_scales;       // scale regions of the w2 operand
   const float* next_scale_q;  // g2.input_scale_quant [128]
@@ -71,6 +72,11 @@ size_t retiled_w13_scale_bytes(int experts);
 void launch_retile_w13_scales(const uint8_t* sidecar_scales, uint8_t* tiled, int experts,
                               cudaStream_t stream);
 
+// Byte matrix [rows, row_bytes] seen through a box of box_rows x 128 bytes with the 128-byte
+// swizzle; bytes out of range read as zero.  False if the driver entry point is missing.
+bool make_operand_tensor_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                             int box_rows);
+
 // Must be called once per device before launch_grouped_gemm (sets the dynamic
 // shared-memory limit).  Returns a cudaError_t value.
 int prepare_grouped_gemm();
@@ -79,5 +85,22 @@ int prepare_grouped_gemm();
 // bytes and the per-expert global scale amax/(6*448).
 void launch_pack_weights(const float* weights, int experts, int n_out, int k_in, uint8_t* codes,
                          uint8_t* scales, float* global_scales, cudaStream_t stream);
+
+// ---- feed-forward steps around the expert path and the dense FP8 MLP (dense_ff.cu) ------
+void launch_ff_prepare(const void* input, const void* dense_weight, const void* expert_weight,
+                       const void* router_scale, void* dense_out, void* expert_out, void* router_out,
+                       int rows, cudaStream_t stream);
+void launch_fp8_quantize_rows(const void* input, uint8_t* out, float* scales, int rows,
+                              cudaStream_t stream);
+void launch_gelu_quantize_fp8(const void* gate_up, const float* activation_scales, float gate_w_scale,
+                              float up_w_scale, uint8_t* out, float* scales, int rows,
+                              cudaStream_t stream);
+void launch_ff_finalize(const void* dense, const void* dense_weight, const void* expert_routes,
+                        const float* route_weights, const int* inverse_routes, const void* expert_weight,
+                        const void* combined_weight, const void* residual, const void* layer_scalar,
+                        void* output, int rows, const float* dense_activation_scales,
+                        float dense_projection_scale, cudaStream_t stream);
+void launch_dense_plan(int rows, const RoutePlan& plan, cudaStream_t stream);
+void launch_pack_fp8(const float* w, size_t count, uint8_t* out, float* scale_out, cudaStream_t stream);
 
 }  // namespace gv

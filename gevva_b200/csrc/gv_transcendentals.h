@@ -124,3 +124,27 @@ GV_HD float gv_expf(float x) {
   const float s2 = gv_bits_to_float((uint32_t)(n2 + 127) << 23);
   return GV_MUL(GV_MUL(p, s1), s2);
 }
+
+// tanh through gv_expf: 1 - 2/(exp(2y)+1).  Absolute error below 3e-7, which is what the
+// GELU needs; the reference's dense-MLP GELU (src/cuda/kernels/fp8.cuh:299-306) calls tanhf.
+GV_HD float gv_tanhf(float y) {
+  const float e = gv_expf(GV_MUL(2.0f, y));
+  return GV_SUB(1.0f, GV_DIV(2.0f, GV_ADD(e, 1.0f)));
+}
+
+// tanh-GELU times up, rounded to bf16 by the caller: 0.5*x*(1+tanh(k*(x+0.044715*x^3))),
+// operations in the order the reference writes them.
+GV_HD float gv_gelu_tanh(float x) {
+  const float cube = GV_MUL(GV_MUL(GV_MUL(0.044715f, x), x), x);
+  const float inner = GV_MUL(0.7978845608028654f, GV_ADD(x, cube));
+  return GV_MUL(GV_MUL(0.5f, x), GV_ADD(1.0f, gv_tanhf(inner)));
+}
+
+// 1/sqrt(x) with IEEE square root and division (the reference calls the approximate rsqrtf).
+GV_HD float gv_rsqrtf(float x) {
+#if defined(__CUDA_ARCH__)
+  return __fdiv_rn(1.0f, __fsqrt_rn(x));
+#else
+  return 1.0f / sqrtf(x);
+#endif
+}

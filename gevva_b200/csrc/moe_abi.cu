@@ -149,6 +149,13 @@ int make_scratch(int tokens, Scratch** out) {
 
 }  // namespace
 
+namespace gv {
+bool make_operand_tensor_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
+                             int box_rows) {
+  return make_operand_map(map, base, rows, row_bytes, box_rows);
+}
+}  // namespace gv
+
 struct gevva_moe {
   Scratch* scratch = nullptr;
   gevva_moe_weights weights{};

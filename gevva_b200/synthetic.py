@@ -134,3 +134,49 @@ class SyntheticLayer:
             out = torch.empty_like(x)
         self.runner.launch_batch(x, ids, weights, out, tokens)
         return out
+
+
+class SyntheticStack:
+    """Random-init FFN stack in the shape of Gemma-4 26B-A4B with attention replaced by
+    identity: per layer the MoE above plus a dense FP8 GeGLU MLP of width 2112 (weights
+    ~N(0, 0.02), per-tensor scale amax/448), norm weights 1, layer scalar 1.  With
+    `distinct_experts=False` every layer shares one packed expert set (tests)."""
+
+    def __init__(self, layers, max_tokens, device="cuda:0", seed=0, distinct_experts=True, s1=None, s2=None):
+        from .feedforward import DENSE, DenseMlp, FeedForwardLayer, pack_fp8
+        self.device = torch.device(device)
+        gen = torch.Generator(device=self.device)
+        gen.manual_seed(seed + 4242)
+        ones = torch.ones(HIDDEN, dtype=torch.bfloat16, device=self.device)
+        self.layers = []
+        first_runner = None
+        packed = None
+        for index in range(layers):
+            if packed is None or distinct_experts:
+                packed = make_packed_experts(seed + index, self.device)
+            base = SyntheticLayer(seed + index, max_tokens, self.device, shared_scratch=first_runner,
+                                  packed=packed)
+            if s1 is None:
+                calib = base.inputs(min(max_tokens, 256), seed + 17)
+                s1, s2 = base.calibrate(calib)
+            base.set_scales(s1, s2)
+            first_runner = first_runner or base.runner
+            gate = _randn((DENSE, HIDDEN), 0.02, gen, self.device)
+            up = _randn((DENSE, HIDDEN), 0.02, gen, self.device)
+            down = _randn((HIDDEN, DENSE), 0.02, gen, self.device)
+            gq, gs = pack_fp8(gate)
+            uq, us = pack_fp8(up)
+            dq, ds = pack_fp8(down)
+            dense = DenseMlp(torch.cat([gq, uq]).contiguous(), dq, gs, us, ds, max_tokens)
+            self.layers.append(FeedForwardLayer(
+                dense_pre=ones, expert_pre=ones, router_scale=ones, router_w=base.router_w,
+                expert_scale=base.expert_scale, dense_post=ones, expert_post=ones, combined_post=ones,
+                layer_scalar=torch.ones(1, dtype=torch.bfloat16, device=self.device),
+                experts=base.runner, dense=dense))
+            self._keep = getattr(self, "_keep", []) + [base]
+        self.aux = torch.cuda.Stream(device=self.device)
+
+    def forward(self, hidden, concurrent=True):
+        for layer in self.layers:
+            hidden = layer.forward(hidden, self.aux if concurrent else None)
+        return hidden

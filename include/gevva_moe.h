@@ -210,6 +210,52 @@ int gevva_moe_ep_reduce(gevva_moe_ep* ep, const float* route_weights, void* out,
  * this rank received in the last step. */
 int gevva_moe_ep_status(gevva_moe_ep* ep, int* received_rows);
 
+/* ---- feed-forward steps around the expert path, and the dense FP8 GeGLU MLP -----------
+ * (the 30-layer FFN stack).  Every tensor is bf16 unless noted; rows are 2816 wide.
+ *
+ * gevva_ff_prepare replaces dual_rmsnorm_router_2816_kernel
+ * (src/cuda/kernels/normalization.cuh:83-123, launched at src/cuda/runtime/prefill.cuh:1200-1202):
+ * one RMS statistic, three outputs (dense-MLP input, expert input, router input).
+ *
+ * gevva_ff_finalize replaces finalize_feedforward_routes_2816_kernel (normalization.cuh:249-377,
+ * launched at prefill.cuh:1238-1245): weighted reduce of the eight routed rows (read through
+ * inverse_routes from gevva_moe_routed_output), RMSNorm of the dense and expert branches, their
+ * sum, a third RMSNorm, residual add and the layer scalar.  dense_activation_scales /
+ * dense_projection_scale rescale an unscaled FP8 GEMM output (NULL / unused otherwise). */
+int gevva_ff_prepare(const void* input, const void* dense_weight, const void* expert_weight,
+                     const void* router_scale, void* dense_out, void* expert_out, void* router_out,
+                     int rows, gevva_stream_t stream);
+int gevva_ff_finalize(const void* dense, const void* dense_weight, const void* expert_routes,
+                      const float* route_weights, const int* inverse_routes, const void* expert_weight,
+                      const void* combined_weight, const void* residual, const void* layer_scalar,
+                      void* output, int rows, const float* dense_activation_scales,
+                      float dense_projection_scale, gevva_stream_t stream);
+
+/* Dense GeGLU MLP of width 2112 in FP8 E4M3 with per-tensor weight scales
+ * (tools/pack_fp8_dense.py:52-71) and per-row dynamic activation scales.  Replaces the
+ * reference's sequence quantize_fp8_rows -> gate and up projections (cuBLASLt, unit scales)
+ * -> gelu_quantize_fp8_2112 -> down projection (src/cuda/runtime/prefill.cuh:1211-1230,
+ * src/cuda/kernels/fp8.cuh:2-26, :299-364).  gate_up is the gate matrix [2112,2816] followed by
+ * the up matrix [2112,2816]; down is [2816,2112].  The output is the UNSCALED bf16 down
+ * projection; gevva_dense_output_scales gives the per-row activation scale that, times
+ * down_scale, gevva_ff_finalize applies. */
+typedef struct gevva_dense gevva_dense;
+typedef struct {
+  const void* gate_up; /* e4m3 [4224,2816] */
+  const void* down;    /* e4m3 [2816,2112] */
+  float gate_scale, up_scale, down_scale;
+} gevva_dense_weights;
+int gevva_dense_create(gevva_dense** out, const gevva_dense_weights* weights, int max_tokens);
+void gevva_dense_destroy(gevva_dense* dense);
+int gevva_dense_launch(gevva_dense* dense, const void* in, void* out_unscaled, int tokens,
+                       gevva_stream_t stream);
+const float* gevva_dense_output_scales(const gevva_dense* dense);
+/* stage buffers for parity tests: 0 input e4m3, 1 input scales, 2 gate|up bf16 unscaled,
+ * 3 product e4m3, 4 product scales */
+int gevva_dense_buffer(const gevva_dense* dense, int which, void** device_ptr, size_t* bytes);
+/* Per-tensor FP8 quantiser (tools/pack_fp8_dense.py:64-70): scale = amax/448, q = e4m3(w/scale). */
+int gevva_pack_fp8(const float* weights, size_t count, void* out, float* scale, gevva_stream_t stream);
+
 /* Expert packer for synthetic or freshly quantised weights; stands where
  * tools/pack_trtllm_experts.py:51-65 stands in the reference (stack experts,
  * interleave block scales) and also performs the NVFP4 quantisation itself:

@@ -431,6 +431,183 @@ int gvo_threads(void);
 
 }  // extern "C"
 
+
+// =====================================================================================
+// Dense FP8 GeGLU MLP and the feed-forward pre/post steps (the 30-layer configuration)
+// =====================================================================================
+namespace {
+
+constexpr int kHidden = 2816;
+constexpr int kDense = 2112;
+constexpr int kRowThreads = kHidden / 8;  // the CUDA kernels use 352 threads x 8 columns
+
+// Sum of squares of one 2816-wide row in the order of the CUDA kernels: each of 352
+// threads folds its 8 consecutive columns with fmaf, each warp folds its lanes with the
+// shuffle-down tree (offsets 16..1), thread 0 adds the 11 warp sums in order.
+inline float row_sum_squares(const float* x) {
+  float lane_sum[kRowThreads];
+  for (int t = 0; t < kRowThreads; ++t) {
+    float s = 0.0f;
+    for (int i = 0; i < 8; ++i) s = std::fmaf(x[8 * t + i], x[8 * t + i], s);
+    lane_sum[t] = s;
+  }
+  float total = 0.0f;
+  for (int w = 0; w < kRowThreads / 32; ++w) {
+    float v[32];
+    for (int l = 0; l < 32; ++l) v[l] = lane_sum[32 * w + l];
+    for (int offset = 16; offset; offset >>= 1)
+      for (int l = 0; l < 32; ++l) v[l] = l + offset < 32 ? v[l] + v[l + offset] : v[l];
+    total = w == 0 ? v[0] : total + v[0];
+  }
+  return total;
+}
+
+inline float through_bf16(float v) { return bf16_to_float(float_to_bf16(v)); }
+
+}  // namespace
+
+extern "C" {
+
+// Step before the path: dual_rmsnorm_router_2816_kernel,
+// src/cuda/kernels/normalization.cuh:83-123.
+void gvo_ff_prepare(const uint16_t* input, const uint16_t* dense_weight, const uint16_t* expert_weight,
+                    const uint16_t* router_scale, uint16_t* dense_out, uint16_t* expert_out,
+                    uint16_t* router_out, int rows) {
+  const float root = gv_rsqrtf(static_cast<float>(kHidden));
+#pragma omp parallel for schedule(static)
+  for (int row = 0; row < rows; ++row) {
+    float x[kHidden];
+    for (int c = 0; c < kHidden; ++c) x[c] = bf16_to_float(input[static_cast<size_t>(row) * kHidden + c]);
+    const float inverse = gv_rsqrtf(row_sum_squares(x) / kHidden + 1e-6f);
+    for (int c = 0; c < kHidden; ++c) {
+      const size_t i = static_cast<size_t>(row) * kHidden + c;
+      const float normalized = x[c] * inverse;
+      dense_out[i] = float_to_bf16(normalized * bf16_to_float(dense_weight[c]));
+      expert_out[i] = float_to_bf16(normalized * bf16_to_float(expert_weight[c]));
+      const float routed = through_bf16(through_bf16(normalized) * bf16_to_float(router_scale[c]));
+      router_out[i] = float_to_bf16(routed * root);
+    }
+  }
+}
+
+// quantize_fp8_rows_kernel, src/cuda/kernels/fp8.cuh:2-26.
+void gvo_fp8_quantize_rows(const uint16_t* input, int rows, int width, uint8_t* out, float* scales) {
+#pragma omp parallel for schedule(static)
+  for (int row = 0; row < rows; ++row) {
+    float maximum = 0.0f;
+    for (int c = 0; c < width; ++c)
+      maximum = std::fmax(maximum, std::fabs(bf16_to_float(input[static_cast<size_t>(row) * width + c])));
+    const float scale = std::fmax(maximum / 448.0f, 1.17549435e-38f);
+    scales[row] = scale;
+    const float inverse = 1.0f / scale;
+    for (int c = 0; c < width; ++c)
+      out[static_cast<size_t>(row) * width + c] =
+          encode_e4m3(bf16_to_float(input[static_cast<size_t>(row) * width + c]) * inverse);
+  }
+}
+
+// E4M3 x E4M3 -> bf16 with unit scales (the reference's launch_unscaled,
+// src/cuda/runtime/fp8_linear.cuh:215-473): out[r,n] = bf16(sum_k a[r,k] * w[n,k]).
+void gvo_fp8_gemm_unscaled(const uint8_t* a, const uint8_t* w, int rows, int n_out, int k_in,
+                           uint16_t* out) {
+  float table[256];
+  for (int c = 0; c < 256; ++c) table[c] = decode_e4m3(static_cast<uint8_t>(c));
+  std::vector<float> af(static_cast<size_t>(rows) * k_in), wf(static_cast<size_t>(n_out) * k_in);
+  for (size_t i = 0; i < af.size(); ++i) af[i] = table[a[i]];
+  for (size_t i = 0; i < wf.size(); ++i) wf[i] = table[w[i]];
+#pragma omp parallel for schedule(static) collapse(2)
+  for (int r = 0; r < rows; ++r)
+    for (int n = 0; n < n_out; ++n) {
+      const float* ar = af.data() + static_cast<size_t>(r) * k_in;
+      const float* wn = wf.data() + static_cast<size_t>(n) * k_in;
+      float lanes[16] = {0};
+      for (int k = 0; k < k_in; k += 16)
+        for (int i = 0; i < 16; ++i) lanes[i] += ar[k + i] * wn[k + i];
+      float sum = 0.0f;
+      for (int i = 0; i < 16; ++i) sum += lanes[i];
+      out[static_cast<size_t>(r) * n_out + n] = float_to_bf16(sum);
+    }
+}
+
+// gelu_quantize_fp8_2112_kernel, src/cuda/kernels/fp8.cuh:308-364 (gelu at :299-306).
+// gate_up holds the unscaled bf16 outputs, gate in columns [0,2112), up in [2112,4224).
+void gvo_gelu_quantize_fp8(const uint16_t* gate_up, const float* activation_scales, float gate_w_scale,
+                           float up_w_scale, int rows, uint8_t* out, float* scales) {
+#pragma omp parallel for schedule(static)
+  for (int row = 0; row < rows; ++row) {
+    float value[kDense];
+    const float gate_scale = activation_scales[row] * gate_w_scale;
+    const float up_scale = activation_scales[row] * up_w_scale;
+    float maximum = 0.0f;
+    for (int c = 0; c < kDense; ++c) {
+      const float g = through_bf16(bf16_to_float(gate_up[static_cast<size_t>(row) * 2 * kDense + c]) * gate_scale);
+      const float u =
+          through_bf16(bf16_to_float(gate_up[static_cast<size_t>(row) * 2 * kDense + kDense + c]) * up_scale);
+      value[c] = through_bf16(gv_gelu_tanh(g) * u);
+      maximum = std::fmax(maximum, std::fabs(value[c]));
+    }
+    const float scale = std::fmax(maximum / 448.0f, 1.17549435e-38f);
+    scales[row] = scale;
+    const float inverse = 1.0f / scale;
+    for (int c = 0; c < kDense; ++c)
+      out[static_cast<size_t>(row) * kDense + c] = encode_e4m3(value[c] * inverse);
+  }
+}
+
+// Step after the path: finalize_feedforward_routes_2816_kernel,
+// src/cuda/kernels/normalization.cuh:249-377.
+void gvo_ff_finalize(const uint16_t* dense, const uint16_t* dense_weight, const uint16_t* expert_routes,
+                     const float* route_weights, const int* inverse_routes,
+                     const uint16_t* expert_weight, const uint16_t* combined_weight,
+                     const uint16_t* residual, uint16_t layer_scalar, uint16_t* output, int rows,
+                     const float* dense_activation_scales, float dense_projection_scale) {
+  const float scalar = bf16_to_float(layer_scalar);
+#pragma omp parallel for schedule(static)
+  for (int row = 0; row < rows; ++row) {
+    float d[kHidden], e[kHidden], combined[kHidden];
+    for (int c = 0; c < kHidden; ++c) {
+      float dv = bf16_to_float(dense[static_cast<size_t>(row) * kHidden + c]);
+      if (dense_activation_scales) dv = through_bf16(dv * (dense_activation_scales[row] * dense_projection_scale));
+      d[c] = dv;
+      float acc = 0.0f;
+      for (int k = 0; k < kTopK; ++k) {
+        const int index = row * kTopK + k;
+        const int source = inverse_routes ? inverse_routes[index] : index;
+        acc = std::fmaf(bf16_to_float(expert_routes[static_cast<size_t>(source) * kHidden + c]),
+                        route_weights[index], acc);
+      }
+      e[c] = through_bf16(acc);
+    }
+    const float dense_inverse = gv_rsqrtf(row_sum_squares(d) / kHidden + 1e-6f);
+    const float expert_inverse = gv_rsqrtf(row_sum_squares(e) / kHidden + 1e-6f);
+    for (int c = 0; c < kHidden; ++c) {
+      const float dense_norm = through_bf16(d[c] * dense_inverse * bf16_to_float(dense_weight[c]));
+      const float expert_norm = through_bf16(e[c] * expert_inverse * bf16_to_float(expert_weight[c]));
+      combined[c] = through_bf16(dense_norm + expert_norm);
+    }
+    const float combined_inverse = gv_rsqrtf(row_sum_squares(combined) / kHidden + 1e-6f);
+    for (int c = 0; c < kHidden; ++c) {
+      const size_t i = static_cast<size_t>(row) * kHidden + c;
+      const float normalized = through_bf16(combined[c] * combined_inverse * bf16_to_float(combined_weight[c]));
+      const float added = through_bf16(bf16_to_float(residual[i]) + normalized);
+      output[i] = float_to_bf16(added * scalar);
+    }
+  }
+}
+
+// Per-tensor FP8 weight quantiser of tools/pack_fp8_dense.py:64-70: scale = amax/448
+// (at least FLT_MIN), q = e4m3(w / scale).
+float gvo_pack_fp8_weight(const float* w, size_t count, uint8_t* out) {
+  float amax = 0.0f;
+  for (size_t i = 0; i < count; ++i) amax = std::fmax(amax, std::fabs(w[i]));
+  const float scale = std::fmax(amax / 448.0f, 1.17549435e-38f);
+#pragma omp parallel for schedule(static)
+  for (long long i = 0; i < static_cast<long long>(count); ++i) out[i] = encode_e4m3(w[i] / scale);
+  return scale;
+}
+
+}  // extern "C"
+
 #if defined(_OPENMP)
 #include <omp.h>
 extern "C" int gvo_threads(void) { return omp_get_max_threads(); }

@@ -134,3 +134,60 @@ class Oracle:
             _p(weights["in_scale_q2"]), _p(out), _p(routed), _p(inverse))
         assert status == 0
         return (out, routed, inverse) if want_routed else out
+
+
+class DenseOracle:
+    """Dense FP8 MLP and feed-forward pre/post steps of the oracle."""
+
+    def __init__(self, oracle):
+        self.lib = oracle.lib
+        self.lib.gvo_pack_fp8_weight.restype = ctypes.c_float
+
+    def ff_prepare(self, x, dense_w, expert_w, router_scale):
+        rows = x.shape[0]
+        outs = [np.zeros((rows, HIDDEN), np.uint16) for _ in range(3)]
+        self.lib.gvo_ff_prepare(_p(np.ascontiguousarray(x)), _p(dense_w), _p(expert_w), _p(router_scale),
+                                _p(outs[0]), _p(outs[1]), _p(outs[2]), ctypes.c_int(rows))
+        return outs
+
+    def quantize_rows(self, x):
+        rows, width = x.shape
+        out = np.zeros((rows, width), np.uint8)
+        scales = np.zeros(rows, np.float32)
+        self.lib.gvo_fp8_quantize_rows(_p(np.ascontiguousarray(x)), ctypes.c_int(rows), ctypes.c_int(width),
+                                       _p(out), _p(scales))
+        return out, scales
+
+    def gemm(self, a, w):
+        rows, k = a.shape
+        n = w.shape[0]
+        out = np.zeros((rows, n), np.uint16)
+        self.lib.gvo_fp8_gemm_unscaled(_p(np.ascontiguousarray(a)), _p(np.ascontiguousarray(w)),
+                                       ctypes.c_int(rows), ctypes.c_int(n), ctypes.c_int(k), _p(out))
+        return out
+
+    def gelu_quantize(self, gate_up, act_scales, gate_scale, up_scale):
+        rows = gate_up.shape[0]
+        out = np.zeros((rows, 2112), np.uint8)
+        scales = np.zeros(rows, np.float32)
+        self.lib.gvo_gelu_quantize_fp8(_p(np.ascontiguousarray(gate_up)), _p(act_scales),
+                                       ctypes.c_float(gate_scale), ctypes.c_float(up_scale),
+                                       ctypes.c_int(rows), _p(out), _p(scales))
+        return out, scales
+
+    def finalize(self, dense, dense_w, routes, route_weights, inverse, expert_w, combined_w, residual,
+                 layer_scalar_bits, act_scales, proj_scale):
+        rows = dense.shape[0]
+        out = np.zeros((rows, HIDDEN), np.uint16)
+        self.lib.gvo_ff_finalize(_p(np.ascontiguousarray(dense)), _p(dense_w), _p(np.ascontiguousarray(routes)),
+                                 _p(np.ascontiguousarray(route_weights, dtype=np.float32)), _p(inverse),
+                                 _p(expert_w), _p(combined_w), _p(np.ascontiguousarray(residual)),
+                                 ctypes.c_uint16(int(layer_scalar_bits)), _p(out), ctypes.c_int(rows),
+                                 _p(act_scales), ctypes.c_float(proj_scale))
+        return out
+
+    def pack_fp8(self, w):
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        out = np.zeros(w.shape, np.uint8)
+        scale = self.lib.gvo_pack_fp8_weight(_p(w), ctypes.c_size_t(w.size), _p(out))
+        return out, np.float32(scale)

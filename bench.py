@@ -27,6 +27,9 @@ FLOP_PER_TOKEN = TOP_K * (2 * 2 * INTER * HIDDEN + 2 * HIDDEN * INTER)  # 95 158
 W13_FLOP_PER_TOKEN = TOP_K * 2 * 2 * INTER * HIDDEN                      # 63 438 848
 LAYER_WEIGHT_BYTES = 428212224
 NOMINAL_FP4_TFLOPS = 9000.0
+# fused w13 launch at 4096 tokens: weights + weight scales + operand codes/scales + output codes/scales
+W13_ALGORITHMIC_BYTES = 128 * (1982464 + 247808) + 32768 * (1408 + 176) + 32768 * (352 + 44)
+W13_DRAM_TRAFFIC_BYTES = 353359616
 WORKLOAD = "prefill_4096_tokens_router_bias_N(0,0.5)"
 
 
@@ -298,20 +301,47 @@ def run_gpu(args):
     check()
 
     # ---- end to end through host buffers ("e2e") -------------------------------
+    # Every step copies its 4096-token batch from pinned host memory and its result back.
+    # Three streams, two buffers: the copy-in of step i+1 and the copy-out of step i-1 run
+    # beside the layer of step i (PCIe is full duplex); everything is inside the timed region.
     host_in = x.cpu().pin_memory()
-    host_out = torch.empty_like(host_in).pin_memory()
-    dev_in = torch.empty_like(x)
-    for _ in range(2):
-        dev_in.copy_(host_in, non_blocking=True)
-        layer_step(layer, dev_in, out, weights, ids)
-        host_out.copy_(out, non_blocking=True)
+    host_out = [torch.empty_like(host_in).pin_memory() for _ in range(2)]
+    dev_in = [torch.empty_like(x) for _ in range(2)]
+    dev_out = [torch.empty_like(x) for _ in range(2)]
+    s_in, s_run, s_out = (torch.cuda.Stream(device=device) for _ in range(3))
+
+    def e2e_loop(steps):
+        ev_in = [None, None]
+        ev_run = [None, None]
+        ev_out = [None, None]
+        for i in range(steps):
+            b = i & 1
+            with torch.cuda.stream(s_in):
+                if ev_run[b] is not None:
+                    s_in.wait_event(ev_run[b])      # the layer of step i-2 has read this buffer
+                dev_in[b].copy_(host_in, non_blocking=True)
+                ev_in[b] = s_in.record_event()
+            with torch.cuda.stream(s_run):
+                s_run.wait_event(ev_in[b])
+                if ev_out[b] is not None:
+                    s_run.wait_event(ev_out[b])     # the result of step i-2 has left this buffer
+                layer_step(layer, dev_in[b], dev_out[b], weights, ids)
+                ev_run[b] = s_run.record_event()
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_run[b])
+                host_out[b].copy_(dev_out[b], non_blocking=True)
+                ev_out[b] = s_out.record_event()
+
+    main = torch.cuda.current_stream()
+    e2e_loop(4)
     barrier()
     e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e_start.record()
-    for _ in range(args.steps):
-        dev_in.copy_(host_in, non_blocking=True)
-        layer_step(layer, dev_in, out, weights, ids)
-        host_out.copy_(out, non_blocking=True)
+    for s_ in (s_in, s_run, s_out):
+        s_.wait_stream(main)
+    e2e_loop(args.steps)
+    for s_ in (s_in, s_run, s_out):
+        main.wait_stream(s_)
     e_stop.record()
     barrier()
     e2e_ms = e_start.elapsed_time(e_stop)
@@ -371,7 +401,9 @@ def run_gpu(args):
             "layer_tflops": FLOP_PER_TOKEN * TOKENS / (elapsed_ms / args.steps * 1e-3) / 1e12,
             "roofline": {"bound": "tensor", "kernel": "grouped_nvfp4_gemm_kernel<kGeglu> (w13 + GeGLU + requantise)",
                          "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s",
-                         "frac": achieved / fp4_peak, "traffic": None,
+                         "frac": achieved / fp4_peak,
+                         # dram__bytes_read + dram__bytes_write of one launch, ncu capture of this workload
+                         "traffic": W13_DRAM_TRAFFIC_BYTES, "algorithmic_bytes": W13_ALGORITHMIC_BYTES,
                          "peak_source": f"4 x bf16_tflops of MEASURED_PEAKS.json ({peak_kind}); "
                                         "no FP4 entry exists",
                          "frac_of_nominal_9000": achieved / NOMINAL_FP4_TFLOPS,

@@ -156,6 +156,21 @@ bool make_operand_tensor_map(CUtensorMap* map, const void* base, uint64_t rows, 
 }
 }  // namespace gv
 
+namespace {
+// The bounded-wait primitive of the GEMM kernels, exercised on its own: one thread waits on
+// a local mbarrier that nothing will ever complete, gives up after `limit_cycles`, records
+// kWaitTimeout in the status word and returns normally.
+__global__ void bounded_wait_probe_kernel(int* status, long long limit_cycles) {
+  __shared__ uint64_t barrier;
+  if (threadIdx.x == 0) {
+    gv::mbar_init(&barrier, 1);
+    gv::fence_barrier_init();
+    if (!gv::mbar_wait_bounded(&barrier, 0, limit_cycles))
+      atomicExch(status, static_cast<int>(gv::kWaitTimeout));
+  }
+}
+}  // namespace
+
 struct gevva_moe {
   Scratch* scratch = nullptr;
   gevva_moe_weights weights{};
@@ -344,6 +359,13 @@ int gevva_moe_last_status(gevva_moe* runner) {
           "status read");
   if (status != 0) GV_CUDA(cudaMemset(runner->scratch->plan.status, 0, sizeof(int)), "status clear");
   return -status;
+}
+
+int gevva_moe_probe_bounded_wait(gevva_moe* runner, long long limit_cycles, gevva_stream_t stream) {
+  if (!runner || limit_cycles < 1 || limit_cycles > 2000000000ll) return GEVVA_MOE_BAD_ARGUMENT;
+  bounded_wait_probe_kernel<<<1, 32, 0, stream>>>(runner->scratch->plan.status, limit_cycles);
+  GV_CUDA(cudaGetLastError(), "bounded wait probe");
+  return GEVVA_MOE_OK;
 }
 
 int gevva_moe_buffer(const gevva_moe* runner, int buffer_id, void** device_ptr, size_t* bytes) {

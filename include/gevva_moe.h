@@ -103,6 +103,12 @@ int gevva_moe_last_status(gevva_moe* runner);
 
 const char* gevva_moe_strerror(int status);
 
+/* Failure-detection self-check (no reference counterpart): enqueues one thread that waits,
+ * with the same bounded wait the GEMM kernels use, on a local barrier nothing completes; after
+ * `limit_cycles` SM cycles (<= 2e9) it gives up, the status word becomes
+ * GEVVA_MOE_WAIT_TIMEOUT and the kernel ends normally, leaving the context usable. */
+int gevva_moe_probe_bounded_wait(gevva_moe* runner, long long limit_cycles, gevva_stream_t stream);
+
 /* ---- stage access, for parity tests and debugging ---------------------------
  * The reference materialises every intermediate in ExpertScratch
  * (src/nvfp4_cutlass.cu:1680-1700); these two calls expose the same buffers and

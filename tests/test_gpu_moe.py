@@ -435,6 +435,28 @@ def test_against_committed_golden_vectors(gm, packed, weights, cuda_device):
     assert rel_l2(bf16_to_f32(bits(out)), bf16_to_f32(golden["layer_out"])) < REL_L2
 
 
+def test_bounded_wait_times_out_and_context_survives(gm, weights, cuda_device):
+    """A wait that nothing satisfies must end by itself with WAIT_TIMEOUT in the status word
+    (about a millisecond here) and leave the device usable: the next layer launch is correct."""
+    import ctypes
+    from gevva_b200 import runtime as rt
+    runner = gm.Nvfp4ExpertRunner(weights[0], 16)
+    lib = rt.library()
+    lib.gevva_moe_probe_bounded_wait.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p]
+    status = lib.gevva_moe_probe_bounded_wait(runner._handle, 2000000,
+                                              ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert status == 0
+    assert runner.last_status() == -2
+    assert runner.last_status() == 0
+    x = hashgen.activations(16, HIDDEN, 41, cuda_device)
+    ids = torch.from_numpy(random_ids(16, 3)).to(cuda_device)
+    rw = torch.full((16, TOP_K), 0.125, device=cuda_device)
+    out = torch.empty_like(x)
+    runner.launch_batch(x, ids, rw, out, 16)
+    runner.check()
+    assert torch.isfinite(out.float()).all()
+
+
 def test_full_size_properties(gm, weights, cuda_device):
     """4096 tokens (the prefill configuration's size): properties that need no oracle."""
     from gevva_b200 import runtime as rt

@@ -88,6 +88,8 @@ int gevva_dense_create(gevva_dense** out, const gevva_dense_weights* weights, in
   d->plan.status = carve(1);
   bool ok = true;
   ok = ok && gv::make_operand_tensor_map(&d->gate_up.map_a, d->act_fp8, t, gv::kHidden, gv::kTileM);
+  ok = ok && gv::make_operand_tensor_map(&d->gate_up.map_a32, d->act_fp8, t, gv::kHidden, 32);
+  ok = ok && gv::make_operand_tensor_map(&d->down.map_a32, d->prod_fp8, t, kDense, 32);
   ok = ok && gv::make_operand_tensor_map(&d->gate_up.map_b, weights->gate_up, 2 * kDense, gv::kHidden, gv::kTileM);
   ok = ok && gv::make_operand_tensor_map(&d->down.map_a, d->prod_fp8, t, kDense, gv::kTileM);
   ok = ok && gv::make_operand_tensor_map(&d->down.map_b, weights->down, gv::kHidden, kDense, gv::kTileM);

@@ -401,6 +401,8 @@ int gevva_moe_ep_create(gevva_moe_ep** out, const gevva_moe_weights* local_weigh
   if (e == cudaSuccess) e = cudaStreamSynchronize(nullptr);
   bool ok = e == cudaSuccess;
   ok = ok && make_map(&ep->w13.map_a, ep->dev.peer_codes[rank], cap, kHidden / 2, kTileM);
+  ok = ok && make_map(&ep->w13.map_a32, ep->dev.peer_codes[rank], cap, kHidden / 2, 32);
+  ok = ok && make_map(&ep->w2.map_a32, ep->inter_codes, cap, kInter / 2, 32);
   ok = ok && make_map(&ep->w13.map_b, local_weights->w13, static_cast<uint64_t>(el) * kW13Out,
                       kHidden / 2, 64);
   ok = ok && make_map(&ep->w2.map_a, ep->inter_codes, cap, kInter / 2, kTileM);

@@ -67,15 +67,17 @@ enum GemmMode { kPlain = 0, kGeglu = 1, kFp8 = 2 };  // kFp8: dense E4M3 operand
 // as many cycles as one K block's MMAs take on the tensor pipe, so the long-K GEMM (w13,
 // eleven K blocks) moves two K blocks per stage; the short-K one (w2, 2.75 K blocks) keeps
 // one per stage and spends the shared memory on the store staging instead.
-template <int kMode> struct StageShape {
-  static constexpr int kAtoms = kMode == kGeglu ? 2 : 1;
-  static constexpr int kStages = kMode == kGeglu ? 3 : 5;
+// Decode-sized launches stream weights from HBM (latency 1.5-3 us under load) and are bound by
+// how soon a freed slot is refilled, so they use six single-K-block stages instead.
+template <int kMode, int kAtomsPerStage> struct StageShape {
+  static constexpr int kAtoms = kAtomsPerStage;
+  static constexpr int kStages = kMode == kGeglu ? 6 / kAtomsPerStage : 5;
 };
 
-template <int kMode>
+template <int kMode, int kAtomsPerStage>
 struct alignas(1024) GemmSmem {
-  static constexpr int kAtoms = StageShape<kMode>::kAtoms;
-  static constexpr int kStages = StageShape<kMode>::kStages;
+  static constexpr int kAtoms = StageShape<kMode, kAtomsPerStage>::kAtoms;
+  static constexpr int kStages = StageShape<kMode, kAtomsPerStage>::kStages;
   uint8_t a[kStages][kAtoms * kOperandStageBytes];
   uint8_t b[kStages][kAtoms * kOperandStageBytes];
   uint8_t sfa[kStages][kAtoms * kSfStageBytes];
@@ -94,12 +96,13 @@ struct alignas(1024) GemmSmem {
 #endif
 };
 
-template <int kMode> constexpr size_t gemm_smem_bytes() { return sizeof(GemmSmem<kMode>) + 1024; }
-static_assert(gemm_smem_bytes<kPlain>() <= 232448 && gemm_smem_bytes<kGeglu>() <= 232448 &&
-                  gemm_smem_bytes<kFp8>() <= 232448,
+template <int kMode, int kAtoms> constexpr size_t gemm_smem_bytes() {
+  return sizeof(GemmSmem<kMode, kAtoms>) + 1024;
+}
+static_assert(gemm_smem_bytes<kPlain, 1>() <= 232448 && gemm_smem_bytes<kGeglu, 2>() <= 232448 &&
+                  gemm_smem_bytes<kGeglu, 1>() <= 232448 && gemm_smem_bytes<kFp8, 1>() <= 232448,
               "shared memory budget of one sm_100 CTA");
-static_assert(kSfColumn + kSfColumnsPerAtom * 2 * 3 <= kTmemColumns &&
-                  kSfColumn + kSfColumnsPerAtom * 5 <= kTmemColumns,
+static_assert(kSfColumn + kSfColumnsPerAtom * 6 <= kTmemColumns,
               "tensor memory budget");
 
 // Instruction descriptor: E2M1 x E2M1 (format 1 in the mxf4 kinds), both K-major,
@@ -256,11 +259,12 @@ __device__ __forceinline__ float round_through_bf16(float alpha, uint32_t acc_bi
   return __bfloat162float(__float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(acc_bits))));
 }
 
-template <int kMode>
+template <int kMode, int kAtomsPerStage>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
+                          const __grid_constant__ CUtensorMap map_a32,
                           const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
-  using Smem = GemmSmem<kMode>;
+  using Smem = GemmSmem<kMode, kAtomsPerStage>;
   constexpr int kStages = Smem::kStages;
   constexpr int kAtoms = Smem::kAtoms;
   extern __shared__ uint8_t smem_raw[];
@@ -284,6 +288,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
 #endif
     fence_barrier_init();
     prefetch_tensor_map(&map_a);
+    prefetch_tensor_map(&map_a32);
     prefetch_tensor_map(&map_b);
   }
   if (warp == 1) {
@@ -311,8 +316,10 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       const int expert = p.tile_expert[m_tile];
       int row = 0, row2 = 0;
       const uint8_t* sf_src;
+      bool short_tile = false;  // decode-sized groups: fetch 32 activation rows instead of 128
       if (!weight_side) {
         row = p.expert_offsets[expert] + (m_tile * kTileM - p.scale_row_offsets[expert]);
+        short_tile = p.expert_offsets[expert + 1] - row <= 32;
         sf_src = p.a_scales + static_cast<size_t>(m_tile) * kTileM * p.groups;
       } else if (kMode == kGeglu) {
         row = expert * kW13Out + n_tile * 64;  // up rows; the gate rows lie kInter further on
@@ -332,13 +339,15 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           const uint32_t sf_bytes =
               kMode == kFp8 ? 0u
                             : static_cast<uint32_t>((atoms - 1) * 4 + (has_last ? p.last_mmas : 4)) * kSfAtomBytes;
-          mbar_arrive_expect_tx(&smem->full[stage], atoms * kOperandStageBytes + sf_bytes);
+          mbar_arrive_expect_tx(&smem->full[stage],
+                                atoms * (short_tile ? kOperandStageBytes / 4 : kOperandStageBytes) + sf_bytes);
 #pragma unroll
           for (int atom = 0; atom < kAtoms; ++atom) {
             if (atom >= atoms) break;
             const int x = (kb + atom) * kTileKBytes;
             if (!weight_side) {
-              tma_load_2d(smem->a[stage] + atom * kOperandStageBytes, &map_a, &smem->full[stage], x, row);
+              tma_load_2d(smem->a[stage] + atom * kOperandStageBytes, short_tile ? &map_a32 : &map_a,
+                          &smem->full[stage], x, row);
             } else if (kMode == kGeglu) {
               tma_load_2d(smem->b[stage] + atom * kOperandStageBytes, &map_b, &smem->full[stage], x, row);
               tma_load_2d(smem->b[stage] + atom * kOperandStageBytes + kOperandStageBytes / 2, &map_b,
@@ -484,6 +493,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         tmem_load_wait();
         tc_fence_before_sync();
         mbar_arrive(&smem->acc_empty[acc_stage]);  // accumulators are in registers now
+        if (quarter * 32 >= rows_valid) goto next_item;  // same decision in all four warps of the quarter
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           uint4 v;
@@ -529,6 +539,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         tmem_load_wait();
         tc_fence_before_sync();
         mbar_arrive(&smem->acc_empty[acc_stage]);
+        if (quarter * 32 >= rows_valid) goto next_item;  // none of this warp's rows exist
         float values[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -547,6 +558,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                         sf_offset(row_local, 4 * n_tile + sub, groups)] = static_cast<uint8_t>(scale);
         }
       }
+    next_item:
       if (threadIdx.x == 64) GV_STAMP(2);
       if (++acc_stage == kAccStages) {
         acc_stage = 0;
@@ -604,17 +616,19 @@ extern "C" void gv_trace_read(unsigned int* out, int* counts) {
 }
 #endif
 
+namespace {
+template <int kMode, int kAtoms> cudaError_t raise_smem_limit() {
+  return cudaFuncSetAttribute(grouped_nvfp4_gemm_kernel<kMode, kAtoms>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(gemm_smem_bytes<kMode, kAtoms>()));
+}
+}  // namespace
+
 int prepare_grouped_gemm() {
-  cudaError_t e = cudaFuncSetAttribute(grouped_nvfp4_gemm_kernel<kPlain>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(gemm_smem_bytes<kPlain>()));
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(grouped_nvfp4_gemm_kernel<kGeglu>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(gemm_smem_bytes<kGeglu>()));
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(grouped_nvfp4_gemm_kernel<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(gemm_smem_bytes<kFp8>()));
+  cudaError_t e = raise_smem_limit<kPlain, 1>();
+  if (e == cudaSuccess) e = raise_smem_limit<kGeglu, 2>();
+  if (e == cudaSuccess) e = raise_smem_limit<kGeglu, 1>();
+  if (e == cudaSuccess) e = raise_smem_limit<kFp8, 1>();
   return static_cast<int>(e);
 }
 
@@ -652,16 +666,20 @@ void launch_grouped_gemm(const GemmOperands& op, const RoutePlan& plan, int sm_c
   p.last_mmas = (k_bytes - (p.k_blocks - 1) * kTileKBytes) / 32;
   if (op.fp8) {
     p.n_tiles = op.n_out / kTileN;
-    grouped_nvfp4_gemm_kernel<kFp8>
-        <<<sm_count, kGemmThreads, gemm_smem_bytes<kFp8>(), stream>>>(op.map_a, op.map_b, p);
+    grouped_nvfp4_gemm_kernel<kFp8, 1>
+        <<<sm_count, kGemmThreads, gemm_smem_bytes<kFp8, 1>(), stream>>>(op.map_a, op.map_a32, op.map_b, p);
   } else if (op.fused_geglu) {
     p.n_tiles = kInter / 64;
-    grouped_nvfp4_gemm_kernel<kGeglu>
-        <<<sm_count, kGemmThreads, gemm_smem_bytes<kGeglu>(), stream>>>(op.map_a, op.map_b, p);
+    if (op.small_batch)
+      grouped_nvfp4_gemm_kernel<kGeglu, 1>
+          <<<sm_count, kGemmThreads, gemm_smem_bytes<kGeglu, 1>(), stream>>>(op.map_a, op.map_a32, op.map_b, p);
+    else
+      grouped_nvfp4_gemm_kernel<kGeglu, 2>
+          <<<sm_count, kGemmThreads, gemm_smem_bytes<kGeglu, 2>(), stream>>>(op.map_a, op.map_a32, op.map_b, p);
   } else {
     p.n_tiles = op.n_out / kTileN;
-    grouped_nvfp4_gemm_kernel<kPlain>
-        <<<sm_count, kGemmThreads, gemm_smem_bytes<kPlain>(), stream>>>(op.map_a, op.map_b, p);
+    grouped_nvfp4_gemm_kernel<kPlain, 1>
+        <<<sm_count, kGemmThreads, gemm_smem_bytes<kPlain, 1>(), stream>>>(op.map_a, op.map_a32, op.map_b, p);
   }
 }
 

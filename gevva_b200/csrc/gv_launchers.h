@@ -46,6 +46,7 @@ void launch_reduce_routes(const void* routed_bf16, const float* route_weights,
 // Grouped NVFP4 GEMM: out[r, n] = bf16(alpha[e] * sum_k A[r,k] B[e,n,k]).
 struct GemmOperands {
   CUtensorMap map_a;        // [row capacity, K/2] bytes, box 128 x 128 B, 128B swizzle
+  CUtensorMap map_a32;      // same matrix through a 32-row box (groups of at most 32 rows)
   CUtensorMap map_b;        // [128*N, K/2] bytes, same box
   const uint8_t* a_scales;  // activation scale regions
   const uint8_t* b_scales;  // [128, N, K/16] swizzled per expert
@@ -58,6 +59,7 @@ struct GemmOperands {
   // 64-row box, b_scales is the re-tiled copy made by launch_retile_w13_scales, and the
   // results go to the w2 operand buffers below.
   bool fused_geglu;
+  bool small_batch;           // decode-sized launch: six single-K-block stages (fused form)
   bool fp8;                   // dense E4M3 x E4M3 (no block scales); k_in counts bytes = elements
   uint8_t* next_codes;        // [row capacity, 352]
   uint8_t* next_scales;       // scale regions of the w2 operand

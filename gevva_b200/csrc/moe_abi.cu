@@ -231,6 +231,8 @@ int gevva_moe_create(gevva_moe** out, const gevva_moe_weights* weights, int max_
   const uint64_t rows = static_cast<uint64_t>(s->routes);
   bool ok = true;
   ok = ok && make_operand_map(&m->w13.map_a, s->input_codes, rows, kHidden / 2);
+  ok = ok && make_operand_map(&m->w13.map_a32, s->input_codes, rows, kHidden / 2, 32);
+  ok = ok && make_operand_map(&m->w2.map_a32, s->inter_codes, rows, kInter / 2, 32);
   ok = ok && make_operand_map(&m->w13.map_b, weights->w13, static_cast<uint64_t>(kExperts) * kW13Out,
                               kHidden / 2);
   ok = ok && make_operand_map(&m->w2.map_a, s->inter_codes, rows, kInter / 2);
@@ -320,7 +322,9 @@ int gevva_moe_launch_stages(gevva_moe* runner, const void* in, const int* ids,
   const unsigned both = GEVVA_MOE_STAGE_W13 | GEVVA_MOE_STAGE_GEGLU;
   if ((stages & both) == both && !(stages & GEVVA_MOE_STAGE_UNFUSED)) {
     // production path: GeGLU + requantise inside the w13 epilogue, no bf16 w13 output
-    gv::launch_grouped_gemm(runner->w13_fused, s->plan, runner->sm_count, stream);
+    gv::GemmOperands fused = runner->w13_fused;
+    fused.small_batch = tokens <= 512;  // weights come from HBM, not L2: favour refill latency
+    gv::launch_grouped_gemm(fused, s->plan, runner->sm_count, stream);
   } else {
     if (stages & GEVVA_MOE_STAGE_W13)
       gv::launch_grouped_gemm(runner->w13, s->plan, runner->sm_count, stream);

@@ -404,7 +404,7 @@ int gevva_moe_ep_create(gevva_moe_ep** out, const gevva_moe_weights* local_weigh
   ok = ok && make_map(&ep->w13.map_a32, ep->dev.peer_codes[rank], cap, kHidden / 2, 32);
   ok = ok && make_map(&ep->w2.map_a32, ep->inter_codes, cap, kInter / 2, 32);
   ok = ok && make_map(&ep->w13.map_b, local_weights->w13, static_cast<uint64_t>(el) * kW13Out,
-                      kHidden / 2, 64);
+                      kHidden / 2, kTileM);
   ok = ok && make_map(&ep->w2.map_a, ep->inter_codes, cap, kInter / 2, kTileM);
   ok = ok && make_map(&ep->w2.map_b, local_weights->w2, static_cast<uint64_t>(el) * kHidden, kInter / 2,
                       kTileM);

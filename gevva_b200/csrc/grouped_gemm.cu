@@ -10,21 +10,28 @@
 // the accumulators before anything is written.
 //
 // Mapping.  Tokens (sorted routes) sit on MMA-M, weight rows on MMA-N.  A work
-// item is (128-row tile of one expert) x (128 weight rows).  Row tiles are listed
+// item is (128-row tile of one expert) x (kN weight rows), kN = 256 for the two expert
+// GEMMs and 128 elsewhere.  The main loop is bound by how fast one thread can issue
+// tcgen05 instructions (about 90 cycles per MMA with its scale copies, against 64 cycles
+// of tensor-pipe time at N = 128), so the wide tile, which does twice the work per
+// instruction, is what keeps the tensor pipe fed.  Row tiles are listed
 // in device memory by the route sort; CTAs are persistent and take items
 // round-robin.  Warps 0 and 18 are the TMA producers (activation side, weight side),
-// warp 1 allocates tensor memory and issues the MMAs, warps 2..17 drain accumulators (two accumulator stages, so the
-// epilogue of one item overlaps the main loop of the next).  Warps 0 and 1 walk
+// warp 1 allocates tensor memory and issues the MMAs, warps 2..17 drain accumulators (two
+// accumulator stages at N = 128; at N = 256 one, which the epilogue copies to registers and
+// releases before it does its arithmetic, so the epilogue of one item still overlaps the
+// main loop of the next).  Warps 0 and 1 walk
 // their loops as whole warps (warp-uniform addresses) and one elected lane issues.
 //
 // Two epilogues:
 //   kPlain  bf16(alpha*acc), staged through shared memory so that every global
 //           store instruction writes two full 256-byte row segments;
-//   kGeglu  the 128 weight rows of an item are up rows [64j,64j+64) and gate rows
-//           [704+64j, 704+64j+64) of w13, so a thread holds up and gate of the same
-//           64 columns: v = gelu_erf(bf16(gate)) * bf16(up), four 16-value blocks ->
-//           32 code bytes and one 4-byte scale word per row, written straight into the
-//           w2 operand buffers.  The bf16 w13 output never exists in memory.
+//   kGeglu  the 256 weight rows of an item are up rows [128j,128j+128) and gate rows
+//           [704+128j, 704+128j+128) of w13 (the sixth item of a row tile is half empty),
+//           so a thread holds up and gate of the same columns: v = gelu_erf(bf16(gate)) *
+//           bf16(up), two 16-value blocks per thread -> 16 code bytes and two scale bytes,
+//           written straight into the w2 operand buffers.  The bf16 w13 output never
+//           exists in memory.
 //
 // Scale factors.  Both operands keep scales in the 128-row x 4-scale atoms of
 // 512 bytes (row%32)*16 + (row/32)*4 + k that the reference writes
@@ -32,7 +39,7 @@
 // consumes and what tcgen05.cp 32x128b.warpx4 moves, so a K block of 256 needs a
 // contiguous 2 KiB per operand, fetched with one untiled bulk copy.  For kGeglu the
 // weight scales come from a copy re-tiled once at runner creation so that the
-// [64 up | 64 gate] rows of an item form such atoms (retile_w13_scales_kernel below).
+// [128 up | 128 gate] rows of an item form such atoms (retile_w13_scales_kernel below).
 //
 // Every wait is bounded: on expiry the kernel records kWaitTimeout in the status
 // word, all roles leave their loops, tensor memory is released and the CTA exits.
@@ -43,7 +50,6 @@ namespace gv {
 
 namespace {
 
-constexpr int kAccStages = 2;
 constexpr int kEpilogueWarpsPerQuarter = 4;  // each takes a quarter of a tile's columns
 constexpr int kEpilogueThreads = 4 * kEpilogueWarpsPerQuarter * 32;
 // Warp roles: 0 = producer of the activation side (A + its scales), 1 = MMA issuer,
@@ -52,36 +58,44 @@ constexpr int kEpilogueThreads = 4 * kEpilogueWarpsPerQuarter * 32;
 constexpr int kWeightProducerWarp = 2 + 4 * kEpilogueWarpsPerQuarter;
 constexpr int kGemmThreads = (kWeightProducerWarp + 1) * 32;
 constexpr uint32_t kTmemColumns = 512;
-// Scale-factor columns are per pipeline stage and K atom: a copy for the next K block must
-// not wait for the MMAs of the previous one to finish reading theirs.
-constexpr uint32_t kSfColumn = kAccStages * kTileN;   // 256
-constexpr uint32_t kSfColumnsPerAtom = 32;            // 16 for A then 16 for B
-constexpr int kOperandStageBytes = kTileM * kTileKBytes;  // 16 KiB, same for A and B
-constexpr int kStageRowBytes = kTileN * 2;                // one bf16 output row of a tile
+// Accumulators take tensor-memory columns [0, 256) in every configuration (2 x 128 or
+// 1 x 256); scale factors follow, per pipeline stage and K block: a copy for the next K
+// block must not wait for the MMAs of the previous one to finish reading theirs.
+constexpr uint32_t kSfColumn = 256;
+constexpr int kOperandStageBytes = kTileM * kTileKBytes;  // 16 KiB: 128 rows of one K block
+constexpr int kStoreColumns = 128;                        // columns per store pass (plain epilogue)
+constexpr int kStageRowBytes = kStoreColumns * 2;         // one bf16 row of a store pass
 constexpr int kStagingBytesPerWarp = 32 * kStageRowBytes; // 8 KiB
 
 enum GemmMode { kPlain = 0, kGeglu = 1, kFp8 = 2 };  // kFp8: dense E4M3 operands, plain epilogue
 
-// A pipeline stage holds kAtoms K blocks of 256 elements (one 128-byte swizzle row each).
-// The barrier round trip of a stage (wait, fence, commit, loop) costs the issuing warp about
-// as many cycles as one K block's MMAs take on the tensor pipe, so the long-K GEMM (w13,
-// eleven K blocks) moves two K blocks per stage; the short-K one (w2, 2.75 K blocks) keeps
-// one per stage and spends the shared memory on the store staging instead.
-// Decode-sized launches stream weights from HBM (latency 1.5-3 us under load) and are bound by
-// how soon a freed slot is refilled, so they use six single-K-block stages instead.
-template <int kMode, int kAtomsPerStage> struct StageShape {
+// A pipeline stage holds kAtoms K blocks of 256 elements (one 128-byte swizzle row each) of
+// 128 activation rows and kN weight rows.  At N = 256 a stage is 54 KiB, so four stages fit
+// (three beside the store staging of the plain epilogue); at N = 128 five or six.
+template <int kMode, int kAtomsPerStage, int kN> struct StageShape {
+  static_assert(kN == 128 || kN == 256, "weight rows per item");
+  static_assert(kN == 128 || kAtomsPerStage == 1, "wide tiles take one K block per stage");
   static constexpr int kAtoms = kAtomsPerStage;
-  static constexpr int kStages = kMode == kGeglu ? 6 / kAtomsPerStage : 5;
+  static constexpr int kStages =
+      kN == 256 ? (kMode == kGeglu ? 4 : 3) : (kMode == kGeglu ? 6 / kAtomsPerStage : 5);
+  static constexpr int kAccStages = kN == 256 ? 1 : 2;
+  static constexpr int kWeightBytes = kN * kTileKBytes;        // per K block
+  static constexpr int kWeightSfBytes = (kN / 128) * kSfStageBytes;
+  // Scale-factor columns per K block: at N = 128 sixteen for A then sixteen for B; at N = 256
+  // sixteen per MMA (A at +0, B rows 0..127 at +4, B rows 128..255 at +8).
+  static constexpr uint32_t kSfColumns = kN == 256 ? 64 : 32;
 };
 
-template <int kMode, int kAtomsPerStage>
+template <int kMode, int kAtomsPerStage, int kN>
 struct alignas(1024) GemmSmem {
-  static constexpr int kAtoms = StageShape<kMode, kAtomsPerStage>::kAtoms;
-  static constexpr int kStages = StageShape<kMode, kAtomsPerStage>::kStages;
+  using Shape = StageShape<kMode, kAtomsPerStage, kN>;
+  static constexpr int kAtoms = Shape::kAtoms;
+  static constexpr int kStages = Shape::kStages;
+  static constexpr int kAccStages = Shape::kAccStages;
   uint8_t a[kStages][kAtoms * kOperandStageBytes];
-  uint8_t b[kStages][kAtoms * kOperandStageBytes];
+  uint8_t b[kStages][kAtoms * Shape::kWeightBytes];
   uint8_t sfa[kStages][kAtoms * kSfStageBytes];
-  uint8_t sfb[kStages][kAtoms * kSfStageBytes];
+  uint8_t sfb[kStages][kAtoms * Shape::kWeightSfBytes];
   uint8_t staging[4][kMode != kGeglu ? kStagingBytesPerWarp : 16];  // plain epilogue only
   uint64_t full[kStages];
   uint64_t empty[kStages];
@@ -96,19 +110,19 @@ struct alignas(1024) GemmSmem {
 #endif
 };
 
-template <int kMode, int kAtoms> constexpr size_t gemm_smem_bytes() {
-  return sizeof(GemmSmem<kMode, kAtoms>) + 1024;
+template <int kMode, int kAtoms, int kN> constexpr size_t gemm_smem_bytes() {
+  return sizeof(GemmSmem<kMode, kAtoms, kN>) + 1024;
 }
-static_assert(gemm_smem_bytes<kPlain, 1>() <= 232448 && gemm_smem_bytes<kGeglu, 2>() <= 232448 &&
-                  gemm_smem_bytes<kGeglu, 1>() <= 232448 && gemm_smem_bytes<kFp8, 1>() <= 232448,
+static_assert(gemm_smem_bytes<kPlain, 1, 128>() <= 232448 && gemm_smem_bytes<kPlain, 1, 256>() <= 232448 &&
+                  gemm_smem_bytes<kGeglu, 1, 256>() <= 232448 && gemm_smem_bytes<kFp8, 1, 128>() <= 232448,
               "shared memory budget of one sm_100 CTA");
-static_assert(kSfColumn + kSfColumnsPerAtom * 6 <= kTmemColumns,
-              "tensor memory budget");
+static_assert(kSfColumn + 64 * 4 <= kTmemColumns && kSfColumn + 32 * 6 <= kTmemColumns, "tensor memory budget");
 
 // Instruction descriptor: E2M1 x E2M1 (format 1 in the mxf4 kinds), both K-major,
 // UE4M3 scales (bit 23 clear), N at [17,23) in units of 8, M at [24,29) in units of 16,
 // K = 64 (bit 31 clear), scale ids 0.
-constexpr uint32_t kInstrDesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kTileN >> 3) << 17) |
+template <int kN>
+constexpr uint32_t kInstrDesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kN >> 3) << 17) |
                                 (static_cast<uint32_t>(kTileM >> 4) << 24);
 
 struct GemmParams {
@@ -167,11 +181,29 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Sm
 //   a_lo / b_lo     low words of the operand descriptors of this stage (address >> 4)
 //   sfa_lo / sfb_lo low words of the scale-factor descriptors of this stage
 //   hi_ab / hi_sf   high words (stride, version, swizzle) shared by all stages
-template <int kMmas>
+template <int kMmas, int kN>
 __device__ __forceinline__ void issue_k_block(uint32_t tmem_acc, uint32_t tmem_sf, uint32_t a_lo,
                                               uint32_t b_lo, uint32_t sfa_lo, uint32_t sfb_lo,
                                               uint32_t hi_ab, uint32_t hi_sf, uint32_t accumulate) {
   static_assert(kMmas >= 1 && kMmas <= 4, "a K block holds one to four MMAs");
+#define GV_OPERANDS                                                                            \
+  ::"r"(tmem_acc), "r"(tmem_sf), "r"(a_lo), "r"(b_lo), "r"(sfa_lo), "r"(sfb_lo), "r"(hi_ab),   \
+    "r"(hi_sf), "r"(kInstrDesc<kN>), "r"(accumulate)                                           \
+  : "memory"
+#define GV_PROLOGUE "{\n\t.reg .pred p, pt;\n\t.reg .b32 lo, ta, tb;\n\t.reg .b64 d0, d1;\n\t" \
+                    "setp.ne.b32 p, %9, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+#define GV_MMA(j, step, pred)                                              \
+  "add.u32 lo, %2, " #j "*2;\n\t"                                          \
+  "mov.b64 d0, {lo, %6};\n\t"                                              \
+  "add.u32 lo, %3, " #j "*2;\n\t"                                          \
+  "mov.b64 d1, {lo, %6};\n\t"                                              \
+  "add.u32 ta, %1, " #j "*" #step ";\n\t"                                  \
+  "add.u32 tb, %1, " #j "*" #step "+" GV_SFB_COLUMN ";\n\t"                \
+  "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X"      \
+  " [%0], d0, d1, %8, [ta], [tb], " pred ";\n\t"
+  if constexpr (kN == 128) {
+    // scale columns of a K block: A of MMA j at +4j, B at +16+4j
+#define GV_SFB_COLUMN "16"
 #define GV_SF_COPY(j)                                                      \
   "add.u32 lo, %4, " #j "*32;\n\t"                                         \
   "mov.b64 d0, {lo, %7};\n\t"                                              \
@@ -181,26 +213,36 @@ __device__ __forceinline__ void issue_k_block(uint32_t tmem_acc, uint32_t tmem_s
   "mov.b64 d0, {lo, %7};\n\t"                                              \
   "add.u32 ta, %1, 16+" #j "*4;\n\t"                                       \
   "tcgen05.cp.cta_group::1.32x128b.warpx4 [ta], d0;\n\t"
-#define GV_MMA(j, pred)                                                    \
-  "add.u32 lo, %2, " #j "*2;\n\t"                                          \
-  "mov.b64 d0, {lo, %6};\n\t"                                              \
-  "add.u32 lo, %3, " #j "*2;\n\t"                                          \
-  "mov.b64 d1, {lo, %6};\n\t"                                              \
-  "add.u32 ta, %1, " #j "*4;\n\t"                                          \
-  "add.u32 tb, %1, 16+" #j "*4;\n\t"                                       \
-  "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X"      \
-  " [%0], d0, d1, %8, [ta], [tb], " pred ";\n\t"
-#define GV_OPERANDS                                                                            \
-  ::"r"(tmem_acc), "r"(tmem_sf), "r"(a_lo), "r"(b_lo), "r"(sfa_lo), "r"(sfb_lo), "r"(hi_ab),   \
-    "r"(hi_sf), "r"(kInstrDesc), "r"(accumulate)                                               \
-  : "memory"
-#define GV_PROLOGUE "{\n\t.reg .pred p, pt;\n\t.reg .b32 lo, ta, tb;\n\t.reg .b64 d0, d1;\n\t" \
-                    "setp.ne.b32 p, %9, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
-  asm volatile(GV_PROLOGUE GV_SF_COPY(0) GV_MMA(0, "p") "}" GV_OPERANDS);
-  if constexpr (kMmas >= 2) asm volatile(GV_PROLOGUE GV_SF_COPY(1) GV_MMA(1, "pt") "}" GV_OPERANDS);
-  if constexpr (kMmas >= 3) asm volatile(GV_PROLOGUE GV_SF_COPY(2) GV_MMA(2, "pt") "}" GV_OPERANDS);
-  if constexpr (kMmas >= 4) asm volatile(GV_PROLOGUE GV_SF_COPY(3) GV_MMA(3, "pt") "}" GV_OPERANDS);
+    asm volatile(GV_PROLOGUE GV_SF_COPY(0) GV_MMA(0, 4, "p") "}" GV_OPERANDS);
+    if constexpr (kMmas >= 2) asm volatile(GV_PROLOGUE GV_SF_COPY(1) GV_MMA(1, 4, "pt") "}" GV_OPERANDS);
+    if constexpr (kMmas >= 3) asm volatile(GV_PROLOGUE GV_SF_COPY(2) GV_MMA(2, 4, "pt") "}" GV_OPERANDS);
+    if constexpr (kMmas >= 4) asm volatile(GV_PROLOGUE GV_SF_COPY(3) GV_MMA(3, 4, "pt") "}" GV_OPERANDS);
 #undef GV_SF_COPY
+#undef GV_SFB_COLUMN
+  } else {
+    // scale columns of MMA j: A at +16j, B rows 0..127 at +16j+4, B rows 128..255 at +16j+8;
+    // the second half of the weight scales lies 2 KiB (128 descriptor units) after the first
+#define GV_SFB_COLUMN "4"
+#define GV_SF_COPY(j)                                                      \
+  "add.u32 lo, %4, " #j "*32;\n\t"                                         \
+  "mov.b64 d0, {lo, %7};\n\t"                                              \
+  "add.u32 ta, %1, " #j "*16;\n\t"                                         \
+  "tcgen05.cp.cta_group::1.32x128b.warpx4 [ta], d0;\n\t"                   \
+  "add.u32 lo, %5, " #j "*32;\n\t"                                         \
+  "mov.b64 d0, {lo, %7};\n\t"                                              \
+  "add.u32 ta, %1, 4+" #j "*16;\n\t"                                       \
+  "tcgen05.cp.cta_group::1.32x128b.warpx4 [ta], d0;\n\t"                   \
+  "add.u32 lo, %5, 128+" #j "*32;\n\t"                                     \
+  "mov.b64 d0, {lo, %7};\n\t"                                              \
+  "add.u32 ta, %1, 8+" #j "*16;\n\t"                                       \
+  "tcgen05.cp.cta_group::1.32x128b.warpx4 [ta], d0;\n\t"
+    asm volatile(GV_PROLOGUE GV_SF_COPY(0) GV_MMA(0, 16, "p") "}" GV_OPERANDS);
+    if constexpr (kMmas >= 2) asm volatile(GV_PROLOGUE GV_SF_COPY(1) GV_MMA(1, 16, "pt") "}" GV_OPERANDS);
+    if constexpr (kMmas >= 3) asm volatile(GV_PROLOGUE GV_SF_COPY(2) GV_MMA(2, 16, "pt") "}" GV_OPERANDS);
+    if constexpr (kMmas >= 4) asm volatile(GV_PROLOGUE GV_SF_COPY(3) GV_MMA(3, 16, "pt") "}" GV_OPERANDS);
+#undef GV_SF_COPY
+#undef GV_SFB_COLUMN
+  }
 #undef GV_MMA
 #undef GV_OPERANDS
 #undef GV_PROLOGUE
@@ -259,14 +301,74 @@ __device__ __forceinline__ float round_through_bf16(float alpha, uint32_t acc_bi
   return __bfloat162float(__float2bfloat16_rn(__fmul_rn(alpha, __uint_as_float(acc_bits))));
 }
 
-template <int kMode, int kAtomsPerStage>
+// Plain epilogue, one store pass: this warp's 32 rows x 32 columns (already scaled and
+// rounded) go to the quarter's staging tile (32 rows x 256 bytes), then the four warps of the
+// quarter write the tile out so that every store instruction covers two full 256-byte row
+// segments.  16-byte chunk c of row r lives at chunk position c ^ (r & 15), which keeps the
+// row-wise writes and the two-rows-per-instruction reads at the minimum number of bank passes.
+__device__ __forceinline__ void stage_and_store(const uint32_t (&r)[32], float alpha, uint8_t* staging,
+                                                int quarter, int sub, int lane, int rows_valid,
+                                                int row0, int column0, const GemmParams& p) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 v;
+    v.x = pack_bf16x2(__fmul_rn(alpha, __uint_as_float(r[8 * i])),
+                      __fmul_rn(alpha, __uint_as_float(r[8 * i + 1])));
+    v.y = pack_bf16x2(__fmul_rn(alpha, __uint_as_float(r[8 * i + 2])),
+                      __fmul_rn(alpha, __uint_as_float(r[8 * i + 3])));
+    v.z = pack_bf16x2(__fmul_rn(alpha, __uint_as_float(r[8 * i + 4])),
+                      __fmul_rn(alpha, __uint_as_float(r[8 * i + 5])));
+    v.w = pack_bf16x2(__fmul_rn(alpha, __uint_as_float(r[8 * i + 6])),
+                      __fmul_rn(alpha, __uint_as_float(r[8 * i + 7])));
+    const int c = sub * 4 + i;
+    *reinterpret_cast<uint4*>(staging + lane * kStageRowBytes + ((c ^ (lane & 15)) << 4)) = v;
+  }
+  named_barrier(1 + quarter, kEpilogueWarpsPerQuarter * 32);
+  const int c = lane & 15;
+  __nv_bfloat16* dst = p.out + static_cast<size_t>(row0 + quarter * 32) * p.n_out + column0 + c * 8;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r2 = 2 * (sub * 4 + i) + (lane >> 4);
+    const uint4 v = *reinterpret_cast<const uint4*>(staging + r2 * kStageRowBytes + ((c ^ (r2 & 15)) << 4));
+    if (quarter * 32 + r2 < rows_valid) {
+      if (p.row_dest) {
+        // expert-parallel combine: the row goes straight to its source rank's buffer
+        __nv_bfloat16* remote = reinterpret_cast<__nv_bfloat16*>(p.row_dest[row0 + quarter * 32 + r2]);
+        *reinterpret_cast<uint4*>(remote + column0 + c * 8) = v;
+      } else {
+        *reinterpret_cast<uint4*>(dst + static_cast<size_t>(r2) * p.n_out) = v;
+      }
+    }
+  }
+  named_barrier(1 + quarter, kEpilogueWarpsPerQuarter * 32);  // staging is rewritten next pass
+}
+
+// Fused epilogue arithmetic for one 16-value block of one row.
+__device__ __forceinline__ uint32_t geglu_block(const uint32_t (&up)[16], const uint32_t (&gate)[16],
+                                                float alpha, float multiplier, const float* erf_table,
+                                                uint32_t& codes_lo, uint32_t& codes_hi) {
+  float values[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float g = round_through_bf16(alpha, gate[i]);
+    const float u = round_through_bf16(alpha, up[i]);
+    values[i] = __fmul_rn(gv_gelu_erf(g, erf_table), u);
+  }
+  return quantize_block16(values, multiplier, codes_lo, codes_hi);
+}
+
+template <int kMode, int kAtomsPerStage, int kN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                           const __grid_constant__ CUtensorMap map_a32,
                           const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
-  using Smem = GemmSmem<kMode, kAtomsPerStage>;
+  using Smem = GemmSmem<kMode, kAtomsPerStage, kN>;
+  using Shape = typename Smem::Shape;
   constexpr int kStages = Smem::kStages;
   constexpr int kAtoms = Smem::kAtoms;
+  constexpr int kAccStages = Smem::kAccStages;
+  constexpr bool kWide = kN == 256;
+  static_assert(kMode != kFp8 || !kWide, "the dense path uses 128-row weight tiles");
   extern __shared__ uint8_t smem_raw[];
   Smem* smem = reinterpret_cast<Smem*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -316,18 +418,24 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       const int expert = p.tile_expert[m_tile];
       int row = 0, row2 = 0;
       const uint8_t* sf_src;
+      const uint8_t* sf_src2 = nullptr;  // wide plain tiles: scales of weight rows 128..255
       bool short_tile = false;  // decode-sized groups: fetch 32 activation rows instead of 128
       if (!weight_side) {
         row = p.expert_offsets[expert] + (m_tile * kTileM - p.scale_row_offsets[expert]);
         short_tile = p.expert_offsets[expert + 1] - row <= 32;
         sf_src = p.a_scales + static_cast<size_t>(m_tile) * kTileM * p.groups;
       } else if (kMode == kGeglu) {
-        row = expert * kW13Out + n_tile * 64;  // up rows; the gate rows lie kInter further on
+        // up rows; the gate rows lie kInter further on.  The last item of a row tile runs
+        // past the 704 up (and gate) rows: those weight rows belong to someone else or lie
+        // outside the tensor (zero fill) and their columns are dropped by the epilogue.
+        row = expert * kW13Out + n_tile * (kN / 2);
         row2 = row + kInter;
-        sf_src = p.b_scales + (static_cast<size_t>(expert) * p.n_tiles + n_tile) * kTileN * p.groups;
+        sf_src = p.b_scales + (static_cast<size_t>(expert) * p.n_tiles + n_tile) * kN * p.groups;
       } else {
-        row = expert * p.n_out + n_tile * kTileN;
+        row = expert * p.n_out + n_tile * kN;
+        row2 = row + 128;
         sf_src = p.b_scales + static_cast<size_t>(row) * p.groups;
+        sf_src2 = sf_src + static_cast<size_t>(128) * p.groups;
       }
       for (int kb = 0; kb < p.k_blocks; kb += kAtoms) {
         ok = __all_sync(0xffffffffu, wait_or_abort<true>(&smem->empty[stage], phase ^ 1u, smem, p.status));
@@ -339,8 +447,14 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           const uint32_t sf_bytes =
               kMode == kFp8 ? 0u
                             : static_cast<uint32_t>((atoms - 1) * 4 + (has_last ? p.last_mmas : 4)) * kSfAtomBytes;
-          mbar_arrive_expect_tx(&smem->full[stage],
-                                atoms * (short_tile ? kOperandStageBytes / 4 : kOperandStageBytes) + sf_bytes);
+          uint32_t expected;
+          if (!weight_side)
+            expected = atoms * (short_tile ? kOperandStageBytes / 4 : kOperandStageBytes) + sf_bytes;
+          else if (kWide && kMode == kGeglu)
+            expected = Shape::kWeightBytes + Shape::kWeightSfBytes;
+          else
+            expected = atoms * Shape::kWeightBytes + (kWide ? 2u : 1u) * sf_bytes;
+          mbar_arrive_expect_tx(&smem->full[stage], expected);
 #pragma unroll
           for (int atom = 0; atom < kAtoms; ++atom) {
             if (atom >= atoms) break;
@@ -348,6 +462,9 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
             if (!weight_side) {
               tma_load_2d(smem->a[stage] + atom * kOperandStageBytes, short_tile ? &map_a32 : &map_a,
                           &smem->full[stage], x, row);
+            } else if (kWide) {
+              tma_load_2d(smem->b[stage], &map_b, &smem->full[stage], x, row);
+              tma_load_2d(smem->b[stage] + kOperandStageBytes, &map_b, &smem->full[stage], x, row2);
             } else if (kMode == kGeglu) {
               tma_load_2d(smem->b[stage] + atom * kOperandStageBytes, &map_b, &smem->full[stage], x, row);
               tma_load_2d(smem->b[stage] + atom * kOperandStageBytes + kOperandStageBytes / 2, &map_b,
@@ -356,9 +473,22 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
               tma_load_2d(smem->b[stage] + atom * kOperandStageBytes, &map_b, &smem->full[stage], x, row);
             }
           }
-          if (kMode != kFp8)
-            bulk_load_1d(weight_side ? smem->sfb[stage] : smem->sfa[stage],
-                         sf_src + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes, &smem->full[stage]);
+          if (kMode != kFp8) {
+            if (!weight_side) {
+              bulk_load_1d(smem->sfa[stage], sf_src + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes,
+                           &smem->full[stage]);
+            } else if (kWide && kMode == kGeglu) {
+              // re-tiled scales: [rows 0..127 | rows 128..255] x four MMAs, 4 KiB per K block
+              bulk_load_1d(smem->sfb[stage], sf_src + static_cast<size_t>(kb) * Shape::kWeightSfBytes,
+                           Shape::kWeightSfBytes, &smem->full[stage]);
+            } else {
+              bulk_load_1d(smem->sfb[stage], sf_src + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes,
+                           &smem->full[stage]);
+              if (kWide)
+                bulk_load_1d(smem->sfb[stage] + kSfStageBytes, sf_src2 + static_cast<size_t>(kb) * kSfStageBytes,
+                             sf_bytes, &smem->full[stage]);
+            }
+          }
           if (!weight_side) GV_STAMP(0);
         }
         __syncwarp();
@@ -414,10 +544,10 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         // Descriptor low words advance by whole stages and K atoms; the K offset of each MMA
         // (+32 bytes inside the swizzle row) and each scale atom (+512 bytes) are immediates.
         const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * (kAtoms * kOperandStageBytes >> 4);
-        const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(stage) * (kAtoms * kOperandStageBytes >> 4);
+        const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(stage) * (kAtoms * Shape::kWeightBytes >> 4);
         const uint32_t sfa_lo = sfa_lo0 + static_cast<uint32_t>(stage) * (kAtoms * kSfStageBytes >> 4);
-        const uint32_t sfb_lo = sfb_lo0 + static_cast<uint32_t>(stage) * (kAtoms * kSfStageBytes >> 4);
-        const uint32_t tmem_sf = tmem_base + kSfColumn + kSfColumnsPerAtom * kAtoms * stage;
+        const uint32_t sfb_lo = sfb_lo0 + static_cast<uint32_t>(stage) * (kAtoms * Shape::kWeightSfBytes >> 4);
+        const uint32_t tmem_sf = tmem_base + kSfColumn + Shape::kSfColumns * kAtoms * stage;
         if (leader) {
           GV_STAMP(1);
 #pragma unroll
@@ -426,23 +556,23 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
             if (k >= p.k_blocks) break;
             const uint32_t accumulate = k != 0 ? 1u : 0u;
             const uint32_t aa = a_lo + atom * (kOperandStageBytes >> 4);
-            const uint32_t bb = b_lo + atom * (kOperandStageBytes >> 4);
+            const uint32_t bb = b_lo + atom * (Shape::kWeightBytes >> 4);
             const uint32_t sa = sfa_lo + atom * (kSfStageBytes >> 4);
-            const uint32_t sb = sfb_lo + atom * (kSfStageBytes >> 4);
-            const uint32_t ts = tmem_sf + atom * kSfColumnsPerAtom;
+            const uint32_t sb = sfb_lo + atom * (Shape::kWeightSfBytes >> 4);
+            const uint32_t ts = tmem_sf + atom * Shape::kSfColumns;
             if (kMode == kFp8) {
               if (k != p.k_blocks - 1 || full_last) issue_k_block_fp8<4>(tmem_acc, aa, bb, hi_ab, accumulate);
               else if (p.last_mmas == 3) issue_k_block_fp8<3>(tmem_acc, aa, bb, hi_ab, accumulate);
               else if (p.last_mmas == 2) issue_k_block_fp8<2>(tmem_acc, aa, bb, hi_ab, accumulate);
               else issue_k_block_fp8<1>(tmem_acc, aa, bb, hi_ab, accumulate);
             } else if (k != p.k_blocks - 1 || full_last) {
-              issue_k_block<4>(tmem_acc, ts, aa, bb, sa, sb, hi_ab, hi_sf, accumulate);
+              issue_k_block<4, kN>(tmem_acc, ts, aa, bb, sa, sb, hi_ab, hi_sf, accumulate);
             } else if (p.last_mmas == 3) {
-              issue_k_block<3>(tmem_acc, ts, aa, bb, sa, sb, hi_ab, hi_sf, accumulate);
+              issue_k_block<3, kN>(tmem_acc, ts, aa, bb, sa, sb, hi_ab, hi_sf, accumulate);
             } else if (p.last_mmas == 2) {
-              issue_k_block<2>(tmem_acc, ts, aa, bb, sa, sb, hi_ab, hi_sf, accumulate);
+              issue_k_block<2, kN>(tmem_acc, ts, aa, bb, sa, sb, hi_ab, hi_sf, accumulate);
             } else {
-              issue_k_block<1>(tmem_acc, ts, aa, bb, sa, sb, hi_ab, hi_sf, accumulate);
+              issue_k_block<1, kN>(tmem_acc, ts, aa, bb, sa, sb, hi_ab, hi_sf, accumulate);
             }
           }
           tc_commit(&smem->empty[stage]);  // frees the stage once these MMAs have read it
@@ -483,52 +613,29 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       const int row_local = quarter * 32 + lane;
       const uint32_t tmem_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                 static_cast<uint32_t>(acc_stage * kTileN);
-      if (kMode != kGeglu) {
-        // This warp's 32 rows x 32 columns go to the quarter's staging tile (32 rows x 256
-        // bytes).  16-byte chunk c of row r lives at chunk position c ^ (r & 15), which keeps
-        // the row-wise writes here and the two-rows-per-instruction reads below at the
-        // minimum number of bank passes.
+      if constexpr (kMode != kGeglu && !kWide) {
         uint32_t r[32];
         tmem_load_32x32(tmem_row + sub * 32, r);
         tmem_load_wait();
         tc_fence_before_sync();
         mbar_arrive(&smem->acc_empty[acc_stage]);  // accumulators are in registers now
-        if (quarter * 32 >= rows_valid) goto next_item;  // same decision in all four warps of the quarter
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint4 v;
-          v.x = pack_bf16x2(__fmul_rn(alpha, __uint_as_float(r[8 * i])),
-                            __fmul_rn(alpha, __uint_as_float(r[8 * i + 1])));
-          v.y = pack_bf16x2(__fmul_rn(alpha, __uint_as_float(r[8 * i + 2])),
-                            __fmul_rn(alpha, __uint_as_float(r[8 * i + 3])));
-          v.z = pack_bf16x2(__fmul_rn(alpha, __uint_as_float(r[8 * i + 4])),
-                            __fmul_rn(alpha, __uint_as_float(r[8 * i + 5])));
-          v.w = pack_bf16x2(__fmul_rn(alpha, __uint_as_float(r[8 * i + 6])),
-                            __fmul_rn(alpha, __uint_as_float(r[8 * i + 7])));
-          const int c = sub * 4 + i;
-          *reinterpret_cast<uint4*>(staging + lane * kStageRowBytes + ((c ^ (lane & 15)) << 4)) = v;
+        // same decision in all four warps of the quarter
+        if (quarter * 32 < rows_valid)
+          stage_and_store(r, alpha, staging, quarter, sub, lane, rows_valid, row0, n_tile * kN, p);
+      } else if constexpr (kMode != kGeglu) {
+        // 256 columns: both halves are taken into registers before the accumulator is released
+        uint32_t r0[32], r1[32];
+        tmem_load_32x32(tmem_row + sub * 32, r0);
+        tmem_load_32x32(tmem_row + kStoreColumns + sub * 32, r1);
+        tmem_load_wait();
+        tc_fence_before_sync();
+        mbar_arrive(&smem->acc_empty[acc_stage]);
+        if (quarter * 32 < rows_valid) {
+          stage_and_store(r0, alpha, staging, quarter, sub, lane, rows_valid, row0, n_tile * kN, p);
+          stage_and_store(r1, alpha, staging, quarter, sub, lane, rows_valid, row0,
+                          n_tile * kN + kStoreColumns, p);
         }
-        named_barrier(1 + quarter, kEpilogueWarpsPerQuarter * 32);
-        const int c = lane & 15;
-        __nv_bfloat16* dst = p.out + static_cast<size_t>(row0 + quarter * 32) * p.n_out +
-                             n_tile * kTileN + c * 8;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int r2 = 2 * (sub * 4 + i) + (lane >> 4);
-          const uint4 v =
-              *reinterpret_cast<const uint4*>(staging + r2 * kStageRowBytes + ((c ^ (r2 & 15)) << 4));
-          if (quarter * 32 + r2 < rows_valid) {
-            if (p.row_dest) {
-              // expert-parallel combine: the row goes straight to its source rank's buffer
-              __nv_bfloat16* remote = reinterpret_cast<__nv_bfloat16*>(p.row_dest[row0 + quarter * 32 + r2]);
-              *reinterpret_cast<uint4*>(remote + n_tile * kTileN + c * 8) = v;
-            } else {
-              *reinterpret_cast<uint4*>(dst + static_cast<size_t>(r2) * p.n_out) = v;
-            }
-          }
-        }
-        named_barrier(1 + quarter, kEpilogueWarpsPerQuarter * 32);  // staging is rewritten next item
-      } else {
+      } else if constexpr (!kWide) {
         // Fused GeGLU + NVFP4 requantise.  Accumulator columns [0,64) are up, [64,128) gate,
         // of intermediate columns [64*n_tile, 64*n_tile+64); this warp owns the 16-column
         // block `sub` of them.
@@ -539,17 +646,9 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         tmem_load_wait();
         tc_fence_before_sync();
         mbar_arrive(&smem->acc_empty[acc_stage]);
-        if (quarter * 32 >= rows_valid) goto next_item;  // none of this warp's rows exist
-        float values[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float g = round_through_bf16(alpha, gate[i]);
-          const float u = round_through_bf16(alpha, up[i]);
-          values[i] = __fmul_rn(gv_gelu_erf(g, smem->erf_table), u);
-        }
-        uint32_t codes_lo, codes_hi;
-        const uint32_t scale = quantize_block16(values, multiplier, codes_lo, codes_hi);
         if (row_local < rows_valid) {
+          uint32_t codes_lo, codes_hi;
+          const uint32_t scale = geglu_block(up, gate, alpha, multiplier, smem->erf_table, codes_lo, codes_hi);
           *reinterpret_cast<uint2*>(p.next_codes + static_cast<size_t>(row0 + row_local) * (kInter / 2) +
                                     n_tile * 32 + sub * 8) = make_uint2(codes_lo, codes_hi);
           // scale group 4*n_tile+sub of row (128*m_tile + row_local) of the w2 operand
@@ -557,8 +656,34 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           p.next_scales[static_cast<size_t>(m_tile) * kTileM * groups +
                         sf_offset(row_local, 4 * n_tile + sub, groups)] = static_cast<uint8_t>(scale);
         }
+      } else {
+        // Fused GeGLU + NVFP4 requantise, wide tile.  Accumulator columns [0,128) are up and
+        // [128,256) gate of intermediate columns [128*n_tile, 128*n_tile+128); this warp owns
+        // the two 16-column blocks 2*sub and 2*sub+1 of them.
+        const float multiplier = p.next_scale_q[expert];
+        uint32_t up0[16], gate0[16], up1[16], gate1[16];
+        tmem_load_32x16(tmem_row + sub * 32, up0);
+        tmem_load_32x16(tmem_row + 128 + sub * 32, gate0);
+        tmem_load_32x16(tmem_row + sub * 32 + 16, up1);
+        tmem_load_32x16(tmem_row + 128 + sub * 32 + 16, gate1);
+        tmem_load_wait();
+        tc_fence_before_sync();
+        mbar_arrive(&smem->acc_empty[acc_stage]);
+        const bool columns_exist = n_tile * 128 + sub * 32 < kInter;  // the last item is half empty
+        if (row_local < rows_valid && columns_exist) {
+          uint4 codes;
+          const uint32_t scale0 = geglu_block(up0, gate0, alpha, multiplier, smem->erf_table, codes.x, codes.y);
+          const uint32_t scale1 = geglu_block(up1, gate1, alpha, multiplier, smem->erf_table, codes.z, codes.w);
+          *reinterpret_cast<uint4*>(p.next_codes + static_cast<size_t>(row0 + row_local) * (kInter / 2) +
+                                    n_tile * 64 + sub * 16) = codes;
+          // scale groups 8*n_tile+2*sub and the next one (same 4-group word) of row
+          // (128*m_tile + row_local) of the w2 operand
+          constexpr int groups = kInter / 16;
+          *reinterpret_cast<uint16_t*>(p.next_scales + static_cast<size_t>(m_tile) * kTileM * groups +
+                                       sf_offset(row_local, 8 * n_tile + 2 * sub, groups)) =
+              static_cast<uint16_t>(scale0 | (scale1 << 8));
+        }
       }
-    next_item:
       if (threadIdx.x == 64) GV_STAMP(2);
       if (++acc_stage == kAccStages) {
         acc_stage = 0;
@@ -586,25 +711,39 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
 }
 
 // Re-tiles the w13 block scales for the fused epilogue: item j of an expert takes up rows
-// [64j, 64j+64) and gate rows [704+64j, 704+64j+64) as its 128 MMA-N rows, so its scale
-// atoms must hold those rows' scales at (n%32)*16 + (n/32)*4 + k.  One thread per byte.
+// [128j, 128j+128) and gate rows [704+128j, 704+128j+128) as its 256 MMA-N rows.  Per item
+// and K block of 256 the copy holds [half (up, gate)][MMA 0..3][512-byte atom], the atom
+// being (n%32)*16 + (n/32)*4 + k over the 128 rows n of the half; rows past 704 get scale 0.
+// One thread per byte.
+constexpr int kFusedItems = (kInter + 127) / 128;  // 6
+
 __global__ void retile_w13_scales_kernel(const uint8_t* __restrict__ sidecar,
                                          uint8_t* __restrict__ tiled, int experts) {
   constexpr int groups = kHidden / 16;          // 176
-  constexpr int atoms = groups / 4;             // 44
-  constexpr int tiles = kInter / 64;            // 11
+  constexpr int k_blocks = kHidden / 256;       // 11
   const size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const size_t total = static_cast<size_t>(experts) * tiles * atoms * kSfAtomBytes;
+  const size_t total = static_cast<size_t>(experts) * kFusedItems * k_blocks * 8 * kSfAtomBytes;
   if (index >= total) return;
   const int byte = static_cast<int>(index % kSfAtomBytes);
-  const int atom = static_cast<int>((index / kSfAtomBytes) % atoms);
-  const int tile = static_cast<int>((index / (static_cast<size_t>(kSfAtomBytes) * atoms)) % tiles);
-  const int expert = static_cast<int>(index / (static_cast<size_t>(kSfAtomBytes) * atoms * tiles));
-  const int n = ((byte & 15) >> 2) * 32 + (byte >> 4);  // MMA-N row of this byte
+  size_t rest = index / kSfAtomBytes;
+  const int mma = static_cast<int>(rest % 4);
+  rest /= 4;
+  const int half = static_cast<int>(rest % 2);
+  rest /= 2;
+  const int k_block = static_cast<int>(rest % k_blocks);
+  rest /= k_blocks;
+  const int item = static_cast<int>(rest % kFusedItems);
+  const int expert = static_cast<int>(rest / kFusedItems);
+  const int n = ((byte & 15) >> 2) * 32 + (byte >> 4);  // row of this byte within the half
   const int k = byte & 3;
-  const int source_row = n < 64 ? tile * 64 + n : kInter + tile * 64 + (n - 64);
-  tiled[index] = sidecar[static_cast<size_t>(expert) * kW13Out * groups +
-                         sf_offset(source_row, atom * 4 + k, groups)];
+  const int column = item * 128 + n;                    // intermediate column
+  uint8_t value = 0;
+  if (column < kInter) {
+    const int source_row = half == 0 ? column : kInter + column;
+    value = sidecar[static_cast<size_t>(expert) * kW13Out * groups +
+                    sf_offset(source_row, (k_block * 4 + mma) * 4 + k, groups)];
+  }
+  tiled[index] = value;
 }
 
 }  // namespace
@@ -617,23 +756,29 @@ extern "C" void gv_trace_read(unsigned int* out, int* counts) {
 #endif
 
 namespace {
-template <int kMode, int kAtoms> cudaError_t raise_smem_limit() {
-  return cudaFuncSetAttribute(grouped_nvfp4_gemm_kernel<kMode, kAtoms>,
+template <int kMode, int kAtoms, int kN> cudaError_t raise_smem_limit() {
+  return cudaFuncSetAttribute(grouped_nvfp4_gemm_kernel<kMode, kAtoms, kN>,
                               cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              static_cast<int>(gemm_smem_bytes<kMode, kAtoms>()));
+                              static_cast<int>(gemm_smem_bytes<kMode, kAtoms, kN>()));
+}
+
+template <int kMode, int kN>
+void launch_variant(const GemmOperands& op, const GemmParams& p, int sm_count, cudaStream_t stream) {
+  grouped_nvfp4_gemm_kernel<kMode, 1, kN>
+      <<<sm_count, kGemmThreads, gemm_smem_bytes<kMode, 1, kN>(), stream>>>(op.map_a, op.map_a32, op.map_b, p);
 }
 }  // namespace
 
 int prepare_grouped_gemm() {
-  cudaError_t e = raise_smem_limit<kPlain, 1>();
-  if (e == cudaSuccess) e = raise_smem_limit<kGeglu, 2>();
-  if (e == cudaSuccess) e = raise_smem_limit<kGeglu, 1>();
-  if (e == cudaSuccess) e = raise_smem_limit<kFp8, 1>();
+  cudaError_t e = raise_smem_limit<kPlain, 1, 128>();
+  if (e == cudaSuccess) e = raise_smem_limit<kPlain, 1, 256>();
+  if (e == cudaSuccess) e = raise_smem_limit<kGeglu, 1, 256>();
+  if (e == cudaSuccess) e = raise_smem_limit<kFp8, 1, 128>();
   return static_cast<int>(e);
 }
 
 size_t retiled_w13_scale_bytes(int experts) {
-  return static_cast<size_t>(experts) * (kInter / 64) * (kHidden / 64) * kSfAtomBytes;
+  return static_cast<size_t>(experts) * kFusedItems * (kHidden / 256) * 8 * kSfAtomBytes;
 }
 
 void launch_retile_w13_scales(const uint8_t* sidecar_scales, uint8_t* tiled, int experts,
@@ -666,20 +811,16 @@ void launch_grouped_gemm(const GemmOperands& op, const RoutePlan& plan, int sm_c
   p.last_mmas = (k_bytes - (p.k_blocks - 1) * kTileKBytes) / 32;
   if (op.fp8) {
     p.n_tiles = op.n_out / kTileN;
-    grouped_nvfp4_gemm_kernel<kFp8, 1>
-        <<<sm_count, kGemmThreads, gemm_smem_bytes<kFp8, 1>(), stream>>>(op.map_a, op.map_a32, op.map_b, p);
+    launch_variant<kFp8, 128>(op, p, sm_count, stream);
   } else if (op.fused_geglu) {
-    p.n_tiles = kInter / 64;
-    if (op.small_batch)
-      grouped_nvfp4_gemm_kernel<kGeglu, 1>
-          <<<sm_count, kGemmThreads, gemm_smem_bytes<kGeglu, 1>(), stream>>>(op.map_a, op.map_a32, op.map_b, p);
-    else
-      grouped_nvfp4_gemm_kernel<kGeglu, 2>
-          <<<sm_count, kGemmThreads, gemm_smem_bytes<kGeglu, 2>(), stream>>>(op.map_a, op.map_a32, op.map_b, p);
+    p.n_tiles = kFusedItems;
+    launch_variant<kGeglu, 256>(op, p, sm_count, stream);
+  } else if (op.n_out % 256 == 0) {
+    p.n_tiles = op.n_out / 256;
+    launch_variant<kPlain, 256>(op, p, sm_count, stream);
   } else {
     p.n_tiles = op.n_out / kTileN;
-    grouped_nvfp4_gemm_kernel<kPlain, 1>
-        <<<sm_count, kGemmThreads, gemm_smem_bytes<kPlain, 1>(), stream>>>(op.map_a, op.map_a32, op.map_b, p);
+    launch_variant<kPlain, 128>(op, p, sm_count, stream);
   }
 }
 

@@ -59,7 +59,6 @@ struct GemmOperands {
   // 64-row box, b_scales is the re-tiled copy made by launch_retile_w13_scales, and the
   // results go to the w2 operand buffers below.
   bool fused_geglu;
-  bool small_batch;           // decode-sized launch: six single-K-block stages (fused form)
   bool fp8;                   // dense E4M3 x E4M3 (no block scales); k_in counts bytes = elements
   uint8_t* next_codes;        // [row capacity, 352]
   uint8_t* next_scales;       // scale regions of the w2 operand

@@ -238,9 +238,6 @@ int gevva_moe_create(gevva_moe** out, const gevva_moe_weights* weights, int max_
   ok = ok && make_operand_map(&m->w2.map_a, s->inter_codes, rows, kInter / 2);
   ok = ok && make_operand_map(&m->w2.map_b, weights->w2, static_cast<uint64_t>(kExperts) * kHidden,
                               kInter / 2);
-  CUtensorMap w13_half_rows;  // same matrix through a 64-row box: up rows and gate rows apart
-  ok = ok && make_operand_map(&w13_half_rows, weights->w13, static_cast<uint64_t>(kExperts) * kW13Out,
-                              kHidden / 2, 64);
   if (!ok) {
     gevva_moe_destroy(m);
     std::snprintf(g_error_text, sizeof(g_error_text), "cuTensorMapEncodeTiled failed");
@@ -267,7 +264,6 @@ int gevva_moe_create(gevva_moe** out, const gevva_moe_weights* weights, int max_
   m->w13.n_out = kW13Out;
   m->w13.k_in = kHidden;
   m->w13_fused = m->w13;
-  m->w13_fused.map_b = w13_half_rows;
   m->w13_fused.b_scales = m->w13_sf_tiled;
   m->w13_fused.out = nullptr;
   m->w13_fused.fused_geglu = true;
@@ -322,9 +318,7 @@ int gevva_moe_launch_stages(gevva_moe* runner, const void* in, const int* ids,
   const unsigned both = GEVVA_MOE_STAGE_W13 | GEVVA_MOE_STAGE_GEGLU;
   if ((stages & both) == both && !(stages & GEVVA_MOE_STAGE_UNFUSED)) {
     // production path: GeGLU + requantise inside the w13 epilogue, no bf16 w13 output
-    gv::GemmOperands fused = runner->w13_fused;
-    fused.small_batch = tokens <= 512;  // weights come from HBM, not L2: favour refill latency
-    gv::launch_grouped_gemm(fused, s->plan, runner->sm_count, stream);
+    gv::launch_grouped_gemm(runner->w13_fused, s->plan, runner->sm_count, stream);
   } else {
     if (stages & GEVVA_MOE_STAGE_W13)
       gv::launch_grouped_gemm(runner->w13, s->plan, runner->sm_count, stream);

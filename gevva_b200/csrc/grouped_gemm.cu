@@ -537,10 +537,13 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         break;
       const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc_stage * kTileN);
       bool ok = true;
+      tc_fence_after_sync();  // the epilogue's tensor-memory loads of this accumulator are done
       for (int kb = 0; kb < p.k_blocks; kb += kAtoms) {
-        ok = __all_sync(0xffffffffu, wait_or_abort<false>(&smem->full[stage], phase, smem, p.status));
+        // All lanes execute the same test on the same barrier, so the result is warp-uniform
+        // without a vote.  The operands were written by the async proxy and are read by it;
+        // the barrier's transaction count is what orders the two, no tcgen05 fence is needed.
+        ok = wait_or_abort<false>(&smem->full[stage], phase, smem, p.status);
         if (!ok) break;
-        tc_fence_after_sync();
         // Descriptor low words advance by whole stages and K atoms; the K offset of each MMA
         // (+32 bytes inside the swizzle row) and each scale atom (+512 bytes) are immediates.
         const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * (kAtoms * kOperandStageBytes >> 4);

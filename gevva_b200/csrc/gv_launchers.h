@@ -21,6 +21,7 @@ struct RoutePlan {
   int* chunk_hist;         // [ceil(R/1024) * 128] scratch of the multi-block sort
   int* status;             // [1]   device status word (gv::Status)
   const int* remap;        // optional [128]: sort key = remap[expert id] (expert-parallel placement)
+  int* sync;               // optional [2], zero on entry: arrival/departure counters of the one-launch sort
 };
 
 void launch_route(const void* logits_bf16, int ld, const void* expert_scale_bf16, float* weights,

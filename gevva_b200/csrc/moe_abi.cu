@@ -143,6 +143,7 @@ int make_scratch(int tokens, Scratch** out) {
   s->plan.num_m_tiles = carve(1);
   s->plan.chunk_hist = carve(chunks * kExperts);
   s->plan.status = carve(1);
+  s->plan.sync = carve(2);  // taken from the 64 spare ints; zero like everything else here
   *out = s;
   return GEVVA_MOE_OK;
 }

@@ -231,13 +231,118 @@ route_scatter_kernel(const int* __restrict__ expert_ids, int routes, RoutePlan p
   }
 }
 
+// Barrier over the CTAs of one cooperative launch.  sync[0] counts arrivals, sync[1]
+// departures; the last CTA to leave zeroes both for the next launch.  The wait is bounded:
+// on expiry the status word gets kWaitTimeout and every thread of the CTA sees false.
+__device__ __forceinline__ bool grid_barrier(int* sync, int ctas, int* status) {
+  __shared__ int passed;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(&sync[0], 1);
+    const long long start = clock64();
+    int ok = 1;
+    while (*reinterpret_cast<volatile int*>(&sync[0]) < ctas) {
+      if (clock64() - start > 4000000000ll) {
+        atomicExch(status, static_cast<int>(kWaitTimeout));
+        ok = 0;
+        break;
+      }
+    }
+    __threadfence();
+    if (atomicAdd(&sync[1], 1) == ctas - 1) {
+      sync[0] = 0;
+      sync[1] = 0;
+    }
+    passed = ok;
+  }
+  __syncthreads();
+  return passed != 0;
+}
+
+// The three phases above in one cooperative launch (chunks <= number of SMs): every CTA
+// counts its chunk, all meet at a grid barrier, every CTA scans the chunk histograms for
+// its own base (the group geometry is written by all of them with identical values) and
+// scatters its routes.
+__global__ void __launch_bounds__(kSortChunk)
+route_sort_fused_kernel(const int* __restrict__ expert_ids, int routes, int chunks, RoutePlan plan) {
+  __shared__ int warp_counts[32 * kExperts];
+  __shared__ int scan_scratch[16];
+  const int tid = threadIdx.x;
+  for (int i = tid; i < 32 * kExperts; i += kSortChunk) warp_counts[i] = 0;
+  __syncthreads();
+  const int route = blockIdx.x * kSortChunk + tid;
+  int expert = kExperts;
+  if (route < routes) {
+    expert = expert_ids[route];
+    if (expert < 0 || expert >= kExperts) {
+      atomicExch(plan.status, static_cast<int>(kBadExpertId));
+      expert = kExperts;
+    } else if (plan.remap) {
+      expert = plan.remap[expert];
+    }
+  }
+  const uint32_t peers = count_chunk(expert, warp_counts);
+  __syncthreads();
+  if (tid < kExperts) {
+    int total = 0;
+    for (int w = 0; w < 32; ++w) total += warp_counts[w * kExperts + tid];
+    plan.chunk_hist[blockIdx.x * kExperts + tid] = total;
+  }
+  if (!grid_barrier(plan.sync, chunks, plan.status)) return;
+  if (tid < kExperts) {
+    int before = 0, total = 0;
+    for (int c = 0; c < chunks; ++c) {
+      const int v = __ldcg(&plan.chunk_hist[c * kExperts + tid]);
+      if (c < static_cast<int>(blockIdx.x)) before += v;
+      total += v;
+    }
+    int running = publish_groups(total, routes, plan, scan_scratch) + before;
+    for (int w = 0; w < 32; ++w) {
+      const int c = warp_counts[w * kExperts + tid];
+      warp_counts[w * kExperts + tid] = running;
+      running += c;
+    }
+  }
+  __syncthreads();
+  if (expert < kExperts) {
+    const int lane = tid & 31, warp = tid >> 5;
+    const int dst = warp_counts[warp * kExperts + expert] + __popc(peers & ((1u << lane) - 1u));
+    plan.sorted_experts[dst] = expert;
+    plan.sorted_routes[dst] = route;
+    plan.inverse_routes[route] = dst;
+  }
+}
+
+namespace {
+// SM count of the current device, cached per device ordinal.
+int current_sm_count() {
+  static int cached[64] = {0};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
+  if (cached[device] == 0) {
+    int count = 0;
+    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) == cudaSuccess) cached[device] = count;
+  }
+  return cached[device];
+}
+}  // namespace
+
 void launch_route_sort(const int* expert_ids, int routes, const RoutePlan& plan,
                        cudaStream_t stream) {
   if (routes <= kSortChunk) {
     route_sort_single_kernel<<<1, kSortChunk, 0, stream>>>(expert_ids, routes, plan);
     return;
   }
-  const int chunks = (routes + kSortChunk - 1) / kSortChunk;
+  int chunks = (routes + kSortChunk - 1) / kSortChunk;
+  if (plan.sync != nullptr && chunks <= current_sm_count()) {
+    RoutePlan plan_copy = plan;
+    void* args[] = {&expert_ids, &routes, &chunks, &plan_copy};
+    const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(route_sort_fused_kernel),
+                                                      dim3(chunks), dim3(kSortChunk), args, 0, stream);
+    if (e == cudaSuccess) return;
+    (void)cudaGetLastError();  // not launchable as one grid here: fall through to the three launches
+  }
   route_histogram_kernel<<<chunks, kSortChunk, 0, stream>>>(expert_ids, routes, plan);
   route_prefix_kernel<<<1, kExperts, 0, stream>>>(chunks, routes, plan);
   route_scatter_kernel<<<chunks, kSortChunk, 0, stream>>>(expert_ids, routes, plan);
@@ -246,13 +351,16 @@ void launch_route_sort(const int* expert_ids, int routes, const RoutePlan& plan,
 // ---------------------------------------------------------------------------
 // Input quantiser.  Reference: quantize_bf16_sorted_moe, src/nvfp4_cutlass.cu:
 // 290-327 (one CTA per sorted route, 16 scalar loads per thread, byte stores, the
-// token row fetched eight times).  Here one CTA per token reads the row once with
-// one coalesced 16-byte load per thread; a lane pair owns a 16-value block (amax by
-// one shuffle); then for each of the token's eight routes the block is quantised
-// with that expert's static scale and every warp store covers 128 contiguous bytes
-// of the route's sorted row.  Scale bytes leave as 4-byte words (four blocks each).
+// token row fetched eight times).  Here a token row is read once; a thread owns 32
+// consecutive columns (two 16-value blocks, four 16-byte loads) and, for each of the
+// token's eight routes, quantises them with that expert's static scale, storing 16 code
+// bytes and the two scale bytes (adjacent in the swizzled layout) of the route's sorted
+// row.  The kernel is bound by instruction issue (two IEEE divisions per block and
+// route), so nothing is computed twice: no lane shares a block with another.
 // ---------------------------------------------------------------------------
-constexpr int kQuantizeThreads = kHidden / 8;  // 352: eleven warps of 256 columns each
+constexpr int kQuantizeThreadsPerToken = kHidden / 32;  // 88
+constexpr int kQuantizeTokensPerBlock = 4;
+constexpr int kQuantizeThreads = kQuantizeThreadsPerToken * kQuantizeTokensPerBlock;  // 352
 
 __device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* out) {
   out[0] = __uint_as_float(raw.x << 16);
@@ -267,69 +375,87 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* out) {
 
 __global__ void __launch_bounds__(kQuantizeThreads)
 quantize_input_kernel(const __nv_bfloat16* __restrict__ input, const int* __restrict__ expert_ids,
-                      const float* __restrict__ in_scale_q, RoutePlan plan,
+                      const float* __restrict__ in_scale_q, RoutePlan plan, int tokens,
                       uint8_t* __restrict__ packed, uint8_t* __restrict__ scales) {
   constexpr int groups = kHidden / 16;
-  __shared__ float route_multiplier[kTopK];
-  __shared__ int route_row[kTopK];            // sorted row, or -1 for a rejected expert id
-  __shared__ unsigned long long route_scale_base[kTopK];
-  const int token = blockIdx.x;
-  if (threadIdx.x < kTopK) {
-    const int route = token * kTopK + threadIdx.x;
-    const int expert = expert_ids[route];
-    if (expert < 0 || expert >= kExperts) {  // flagged by the route sort
-      route_row[threadIdx.x] = -1;
-    } else {
-      const int dst = plan.inverse_routes[route];
-      const int row = dst - plan.expert_offsets[expert];
-      route_row[threadIdx.x] = dst;
-      route_multiplier[threadIdx.x] = in_scale_q[expert];
-      route_scale_base[threadIdx.x] =
-          static_cast<unsigned long long>(plan.scale_row_offsets[expert]) * groups + sf_offset(row, 0, groups);
+  __shared__ float route_multiplier[kQuantizeTokensPerBlock][kTopK];
+  __shared__ int route_row[kQuantizeTokensPerBlock][kTopK];  // sorted row, or -1 for a rejected expert id
+  __shared__ unsigned long long route_scale_base[kQuantizeTokensPerBlock][kTopK];
+  if (threadIdx.x < kQuantizeTokensPerBlock * kTopK) {
+    const int slot = threadIdx.x / kTopK;
+    const int k = threadIdx.x % kTopK;
+    const int token = blockIdx.x * kQuantizeTokensPerBlock + slot;
+    int dst = -1;
+    if (token < tokens) {
+      const int route = token * kTopK + k;
+      const int expert = expert_ids[route];
+      if (expert >= 0 && expert < kExperts) {  // others are flagged by the route sort
+        dst = plan.inverse_routes[route];
+        const int row = dst - plan.expert_offsets[expert];
+        route_multiplier[slot][k] = in_scale_q[expert];
+        route_scale_base[slot][k] =
+            static_cast<unsigned long long>(plan.scale_row_offsets[expert]) * groups + sf_offset(row, 0, groups);
+      }
+    }
+    route_row[slot][k] = dst;
+  }
+  const int slot = threadIdx.x / kQuantizeThreadsPerToken;
+  const int part = threadIdx.x - slot * kQuantizeThreadsPerToken;  // columns [32*part, 32*part+32)
+  const int token = blockIdx.x * kQuantizeTokensPerBlock + slot;
+  float values[32];
+  float maximum[2] = {0.0f, 0.0f};
+  if (token < tokens) {
+    const uint4* source = reinterpret_cast<const uint4*>(input + static_cast<size_t>(token) * kHidden) + 4 * part;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) unpack_bf16x8(__ldg(source + i), values + 8 * i);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      maximum[0] = fmaxf(maximum[0], fabsf(values[i]));
+      maximum[1] = fmaxf(maximum[1], fabsf(values[16 + i]));
     }
   }
-  const int lane = threadIdx.x & 31;
-  float values[8];
-  unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(input + static_cast<size_t>(token) * kHidden) +
-                      threadIdx.x),
-                values);
-  float maximum = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) maximum = fmaxf(maximum, fabsf(values[i]));
-  maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, 1));
   __syncthreads();
-  const int quad = threadIdx.x >> 3;  // four blocks = one scale word = 64 columns
+  if (token >= tokens) return;
+  // scale groups 2*part and 2*part+1 share a 4-group word of the swizzled layout
+  const unsigned scale_offset = static_cast<unsigned>(part >> 1) * 512u + static_cast<unsigned>(part & 1) * 2u;
 #pragma unroll 2
   for (int k = 0; k < kTopK; ++k) {
-    const int dst = route_row[k];
+    const int dst = route_row[slot][k];
     if (dst < 0) continue;
-    const float multiplier = route_multiplier[k];
-    const float unrounded = __fdiv_rn(__fmul_rn(multiplier, maximum), 6.0f);
-    const uint32_t scale = encode_e4m3(unrounded);
-    const float rounded = decode_e4m3(scale);
-    const float inverse = rounded == 0.0f ? 0.0f : __fdiv_rn(multiplier, rounded);
-    uint32_t codes = 0;
+    const float multiplier = route_multiplier[slot][k];
+    uint32_t codes[4];
+    uint32_t scale_pair = 0;
 #pragma unroll
-    for (int pair = 0; pair < 4; ++pair)
-      codes |= encode_e2m1x2(__fmul_rn(values[2 * pair], inverse),
-                             __fmul_rn(values[2 * pair + 1], inverse)) << (8 * pair);
-    reinterpret_cast<uint32_t*>(packed + static_cast<size_t>(dst) * (kHidden / 2))[threadIdx.x] = codes;
-    // lanes 8q, 8q+2, 8q+4, 8q+6 hold the four scale bytes of one word
-    const int base_lane = lane & ~7;
-    uint32_t word = __shfl_sync(0xffffffffu, scale, base_lane);
-    word |= __shfl_sync(0xffffffffu, scale, base_lane + 2) << 8;
-    word |= __shfl_sync(0xffffffffu, scale, base_lane + 4) << 16;
-    word |= __shfl_sync(0xffffffffu, scale, base_lane + 6) << 24;
-    if ((lane & 7) == 0)
-      *reinterpret_cast<uint32_t*>(scales + route_scale_base[k] + static_cast<size_t>(quad) * 512) = word;
+    for (int block = 0; block < 2; ++block) {
+      const float unrounded = __fdiv_rn(__fmul_rn(multiplier, maximum[block]), 6.0f);
+      const uint32_t scale = encode_e4m3(unrounded);
+      const float rounded = decode_e4m3(scale);
+      const float inverse = rounded == 0.0f ? 0.0f : __fdiv_rn(multiplier, rounded);
+      scale_pair |= scale << (8 * block);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int pair = 0; pair < 4; ++pair)
+          word |= encode_e2m1x2(__fmul_rn(values[16 * block + 8 * half + 2 * pair], inverse),
+                                __fmul_rn(values[16 * block + 8 * half + 2 * pair + 1], inverse))
+                  << (8 * pair);
+        codes[2 * block + half] = word;
+      }
+    }
+    reinterpret_cast<uint4*>(packed + static_cast<size_t>(dst) * (kHidden / 2))[part] =
+        make_uint4(codes[0], codes[1], codes[2], codes[3]);
+    *reinterpret_cast<uint16_t*>(scales + route_scale_base[slot][k] + scale_offset) =
+        static_cast<uint16_t>(scale_pair);
   }
 }
 
 void launch_quantize_input(const void* input_bf16, const int* expert_ids, const float* in_scale_q,
                            const RoutePlan& plan, int tokens, uint8_t* packed, uint8_t* scales,
                            cudaStream_t stream) {
-  quantize_input_kernel<<<tokens, kQuantizeThreads, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(input_bf16), expert_ids, in_scale_q, plan, packed, scales);
+  const int blocks = (tokens + kQuantizeTokensPerBlock - 1) / kQuantizeTokensPerBlock;
+  quantize_input_kernel<<<blocks, kQuantizeThreads, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(input_bf16), expert_ids, in_scale_q, plan, tokens, packed, scales);
 }
 
 // ---------------------------------------------------------------------------

@@ -378,6 +378,7 @@ int gevva_moe_ep_create(gevva_moe_ep** out, const gevva_moe_weights* local_weigh
   sp.num_m_tiles = carve(1);
   sp.chunk_hist = carve(chunks * kExperts);
   sp.status = carve(1);
+  sp.sync = carve(2);  // from the 64 spare ints
   gv::RoutePlan& rp = ep->receive_plan;
   rp.expert_offsets = carve(kExperts + 1);
   rp.scale_row_offsets = carve(kExperts + 1);
@@ -405,6 +406,8 @@ int gevva_moe_ep_create(gevva_moe_ep** out, const gevva_moe_weights* local_weigh
   ok = ok && make_map(&ep->w2.map_a32, ep->inter_codes, cap, kInter / 2, 32);
   ok = ok && make_map(&ep->w13.map_b, local_weights->w13, static_cast<uint64_t>(el) * kW13Out,
                       kHidden / 2, kTileM);
+  ok = ok && make_map(&ep->w13.map_b64, local_weights->w13, static_cast<uint64_t>(el) * kW13Out,
+                      kHidden / 2, 64);
   ok = ok && make_map(&ep->w2.map_a, ep->inter_codes, cap, kInter / 2, kTileM);
   ok = ok && make_map(&ep->w2.map_b, local_weights->w2, static_cast<uint64_t>(el) * kHidden, kInter / 2,
                       kTileM);

@@ -357,11 +357,46 @@ __device__ __forceinline__ uint32_t geglu_block(const uint32_t (&up)[16], const 
   return quantize_block16(values, multiplier, codes_lo, codes_hi);
 }
 
+// Work distribution.  Items are numbered with the expensive ones first (in the fused wide
+// form the half-filled last item of every row tile comes after all full ones) and dealt to
+// the persistent CTAs in snake order: round r goes to CTA b as item r*G + b for even r and
+// r*G + (G-1-b) for odd r.  With equal-cost items this is plain round-robin; with the cheap
+// items at the end it is the longest-first rule, which is what balances a decode-sized
+// launch (768 items of two sizes over 148 CTAs).
+struct WorkItem {
+  int m_tile;
+  int n_tile;
+};
+
+template <int kMode, int kN>
+__device__ __forceinline__ bool work_item(int round, int total_items, int m_tiles, int n_tiles,
+                                          WorkItem& item) {
+  const int grid = static_cast<int>(gridDim.x);
+  const int slot = (round & 1) ? grid - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
+  const int index = round * grid + slot;
+  if (index >= total_items) return false;
+  if (kMode == kGeglu && kN == 256) {
+    const int full = m_tiles * (n_tiles - 1);
+    if (index < full) {
+      item.m_tile = index / (n_tiles - 1);
+      item.n_tile = index - item.m_tile * (n_tiles - 1);
+    } else {
+      item.m_tile = index - full;
+      item.n_tile = n_tiles - 1;
+    }
+  } else {
+    item.m_tile = index / n_tiles;
+    item.n_tile = index - item.m_tile * n_tiles;
+  }
+  return true;
+}
+
 template <int kMode, int kAtomsPerStage, int kN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                           const __grid_constant__ CUtensorMap map_a32,
-                          const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+                          const __grid_constant__ CUtensorMap map_b,
+                          const __grid_constant__ CUtensorMap map_b64, const GemmParams p) {
   using Smem = GemmSmem<kMode, kAtomsPerStage, kN>;
   using Shape = typename Smem::Shape;
   constexpr int kStages = Smem::kStages;
@@ -392,6 +427,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     prefetch_tensor_map(&map_a);
     prefetch_tensor_map(&map_a32);
     prefetch_tensor_map(&map_b);
+    if (kMode == kGeglu) prefetch_tensor_map(&map_b64);
   }
   if (warp == 1) {
     tmem_alloc(&smem->tmem_base, kTmemColumns);
@@ -403,7 +439,9 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   tc_fence_after_sync();
   const uint32_t tmem_base = smem->tmem_base;
 
-  const int total_items = p.num_m_tiles[0] * p.n_tiles;
+  const int m_tiles = p.num_m_tiles[0];
+  const int total_items = m_tiles * p.n_tiles;
+  const int rounds = (total_items + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
 
   if (warp == 0 || warp == kWeightProducerWarp) {
     // ---------------- TMA producers ----------------
@@ -412,24 +450,29 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     uint32_t phase = 0;
     int issued = 0;
     bool ok = true;
-    for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
-      const int m_tile = item / p.n_tiles;
-      const int n_tile = item - m_tile * p.n_tiles;
+    for (int round = 0; ok && round < rounds; ++round) {
+      WorkItem item;
+      if (!work_item<kMode, kN>(round, total_items, m_tiles, p.n_tiles, item)) continue;
+      const int m_tile = item.m_tile;
+      const int n_tile = item.n_tile;
       const int expert = p.tile_expert[m_tile];
       int row = 0, row2 = 0;
       const uint8_t* sf_src;
       const uint8_t* sf_src2 = nullptr;  // wide plain tiles: scales of weight rows 128..255
       bool short_tile = false;  // decode-sized groups: fetch 32 activation rows instead of 128
+      bool half_item = false;   // fused wide tiles: the last item of a row tile has 64 up and 64 gate rows
       if (!weight_side) {
         row = p.expert_offsets[expert] + (m_tile * kTileM - p.scale_row_offsets[expert]);
         short_tile = p.expert_offsets[expert + 1] - row <= 32;
         sf_src = p.a_scales + static_cast<size_t>(m_tile) * kTileM * p.groups;
       } else if (kMode == kGeglu) {
-        // up rows; the gate rows lie kInter further on.  The last item of a row tile runs
-        // past the 704 up (and gate) rows: those weight rows belong to someone else or lie
-        // outside the tensor (zero fill) and their columns are dropped by the epilogue.
+        // up rows; the gate rows lie kInter further on.  The last item of a row tile has only
+        // 64 up and 64 gate rows left: only those are fetched (64-row boxes); the rest of each
+        // 128-row half keeps whatever the stage held, its scales are zero in the re-tiled copy
+        // and its columns are dropped by the epilogue.
         row = expert * kW13Out + n_tile * (kN / 2);
         row2 = row + kInter;
+        half_item = kWide && (n_tile + 1) * (kN / 2) > kInter;
         sf_src = p.b_scales + (static_cast<size_t>(expert) * p.n_tiles + n_tile) * kN * p.groups;
       } else {
         row = expert * p.n_out + n_tile * kN;
@@ -451,7 +494,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           if (!weight_side)
             expected = atoms * (short_tile ? kOperandStageBytes / 4 : kOperandStageBytes) + sf_bytes;
           else if (kWide && kMode == kGeglu)
-            expected = Shape::kWeightBytes + Shape::kWeightSfBytes;
+            expected = (half_item ? Shape::kWeightBytes / 2 : Shape::kWeightBytes) + Shape::kWeightSfBytes;
           else
             expected = atoms * Shape::kWeightBytes + (kWide ? 2u : 1u) * sf_bytes;
           mbar_arrive_expect_tx(&smem->full[stage], expected);
@@ -463,8 +506,9 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
               tma_load_2d(smem->a[stage] + atom * kOperandStageBytes, short_tile ? &map_a32 : &map_a,
                           &smem->full[stage], x, row);
             } else if (kWide) {
-              tma_load_2d(smem->b[stage], &map_b, &smem->full[stage], x, row);
-              tma_load_2d(smem->b[stage] + kOperandStageBytes, &map_b, &smem->full[stage], x, row2);
+              const CUtensorMap* map = half_item ? &map_b64 : &map_b;
+              tma_load_2d(smem->b[stage], map, &smem->full[stage], x, row);
+              tma_load_2d(smem->b[stage] + kOperandStageBytes, map, &smem->full[stage], x, row2);
             } else if (kMode == kGeglu) {
               tma_load_2d(smem->b[stage] + atom * kOperandStageBytes, &map_b, &smem->full[stage], x, row);
               tma_load_2d(smem->b[stage] + atom * kOperandStageBytes + kOperandStageBytes / 2, &map_b,
@@ -531,7 +575,9 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     constexpr uint32_t hi_sf = (128u >> 4) | (1u << 14);                // 8 rows x 16 B, no swizzle
     const bool full_last = p.last_mmas == 4;
     const bool leader = elect_one();
-    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+    for (int round = 0; round < rounds; ++round) {
+      WorkItem item;
+      if (!work_item<kMode, kN>(round, total_items, m_tiles, p.n_tiles, item)) continue;
       if (!__all_sync(0xffffffffu,
                       wait_or_abort<false>(&smem->acc_empty[acc_stage], acc_phase ^ 1u, smem, p.status)))
         break;
@@ -602,9 +648,11 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     int acc_stage = 0;
     uint32_t acc_phase = 0;
     uint8_t* staging = smem->staging[quarter];
-    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
-      const int m_tile = item / p.n_tiles;
-      const int n_tile = item - m_tile * p.n_tiles;
+    for (int round = 0; round < rounds; ++round) {
+      WorkItem item;
+      if (!work_item<kMode, kN>(round, total_items, m_tiles, p.n_tiles, item)) continue;
+      const int m_tile = item.m_tile;
+      const int n_tile = item.n_tile;
       const int expert = p.tile_expert[m_tile];
       const int local0 = m_tile * kTileM - p.scale_row_offsets[expert];
       const int row0 = p.expert_offsets[expert] + local0;
@@ -768,7 +816,8 @@ template <int kMode, int kAtoms, int kN> cudaError_t raise_smem_limit() {
 template <int kMode, int kN>
 void launch_variant(const GemmOperands& op, const GemmParams& p, int sm_count, cudaStream_t stream) {
   grouped_nvfp4_gemm_kernel<kMode, 1, kN>
-      <<<sm_count, kGemmThreads, gemm_smem_bytes<kMode, 1, kN>(), stream>>>(op.map_a, op.map_a32, op.map_b, p);
+      <<<sm_count, kGemmThreads, gemm_smem_bytes<kMode, 1, kN>(), stream>>>(op.map_a, op.map_a32, op.map_b,
+                                                                            op.map_b64, p);
 }
 }  // namespace
 

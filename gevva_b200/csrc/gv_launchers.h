@@ -49,6 +49,7 @@ struct GemmOperands {
   CUtensorMap map_a;        // [row capacity, K/2] bytes, box 128 x 128 B, 128B swizzle
   CUtensorMap map_a32;      // same matrix through a 32-row box (groups of at most 32 rows)
   CUtensorMap map_b;        // [128*N, K/2] bytes, same box
+  CUtensorMap map_b64;      // fused w13 form only: the same matrix through a 64-row box
   const uint8_t* a_scales;  // activation scale regions
   const uint8_t* b_scales;  // [128, N, K/16] swizzled per expert
   const float* alpha;       // [128]
@@ -56,9 +57,9 @@ struct GemmOperands {
   const unsigned long long* row_dest;  // optional: per-row output address instead of `out`
   int n_out;                // N: 1408 or 2816
   int k_in;                 // K: 2816 or 704
-  // Fused w13 form (GeGLU + requantise in the epilogue, no bf16 output): map_b then has a
-  // 64-row box, b_scales is the re-tiled copy made by launch_retile_w13_scales, and the
-  // results go to the w2 operand buffers below.
+  // Fused w13 form (GeGLU + requantise in the epilogue, no bf16 output): b_scales is the
+  // re-tiled copy made by launch_retile_w13_scales, map_b64 serves the last, half-filled item
+  // of each row tile, and the results go to the w2 operand buffers below.
   bool fused_geglu;
   bool fp8;                   // dense E4M3 x E4M3 (no block scales); k_in counts bytes = elements
   uint8_t* next_codes;        // [row capacity, 352]

@@ -239,6 +239,8 @@ int gevva_moe_create(gevva_moe** out, const gevva_moe_weights* weights, int max_
   ok = ok && make_operand_map(&m->w2.map_a, s->inter_codes, rows, kInter / 2);
   ok = ok && make_operand_map(&m->w2.map_b, weights->w2, static_cast<uint64_t>(kExperts) * kHidden,
                               kInter / 2);
+  ok = ok && make_operand_map(&m->w13.map_b64, weights->w13, static_cast<uint64_t>(kExperts) * kW13Out,
+                              kHidden / 2, 64);
   if (!ok) {
     gevva_moe_destroy(m);
     std::snprintf(g_error_text, sizeof(g_error_text), "cuTensorMapEncodeTiled failed");

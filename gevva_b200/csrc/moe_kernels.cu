@@ -359,7 +359,7 @@ void launch_route_sort(const int* expert_ids, int routes, const RoutePlan& plan,
 // route), so nothing is computed twice: no lane shares a block with another.
 // ---------------------------------------------------------------------------
 constexpr int kQuantizeThreadsPerToken = kHidden / 32;  // 88
-constexpr int kQuantizeTokensPerBlock = 4;
+constexpr int kQuantizeTokensPerBlock = 4;  // large batches; decode-sized ones take one token per CTA
 constexpr int kQuantizeThreads = kQuantizeThreadsPerToken * kQuantizeTokensPerBlock;  // 352
 
 __device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* out) {
@@ -373,18 +373,19 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* out) {
   out[7] = __uint_as_float(raw.w & 0xffff0000u);
 }
 
-__global__ void __launch_bounds__(kQuantizeThreads)
+template <int kTokensPerBlock>
+__global__ void __launch_bounds__(kQuantizeThreadsPerToken * kTokensPerBlock)
 quantize_input_kernel(const __nv_bfloat16* __restrict__ input, const int* __restrict__ expert_ids,
                       const float* __restrict__ in_scale_q, RoutePlan plan, int tokens,
                       uint8_t* __restrict__ packed, uint8_t* __restrict__ scales) {
   constexpr int groups = kHidden / 16;
-  __shared__ float route_multiplier[kQuantizeTokensPerBlock][kTopK];
-  __shared__ int route_row[kQuantizeTokensPerBlock][kTopK];  // sorted row, or -1 for a rejected expert id
-  __shared__ unsigned long long route_scale_base[kQuantizeTokensPerBlock][kTopK];
-  if (threadIdx.x < kQuantizeTokensPerBlock * kTopK) {
+  __shared__ float route_multiplier[kTokensPerBlock][kTopK];
+  __shared__ int route_row[kTokensPerBlock][kTopK];  // sorted row, or -1 for a rejected expert id
+  __shared__ unsigned long long route_scale_base[kTokensPerBlock][kTopK];
+  if (threadIdx.x < kTokensPerBlock * kTopK) {
     const int slot = threadIdx.x / kTopK;
     const int k = threadIdx.x % kTopK;
-    const int token = blockIdx.x * kQuantizeTokensPerBlock + slot;
+    const int token = blockIdx.x * kTokensPerBlock + slot;
     int dst = -1;
     if (token < tokens) {
       const int route = token * kTopK + k;
@@ -401,7 +402,7 @@ quantize_input_kernel(const __nv_bfloat16* __restrict__ input, const int* __rest
   }
   const int slot = threadIdx.x / kQuantizeThreadsPerToken;
   const int part = threadIdx.x - slot * kQuantizeThreadsPerToken;  // columns [32*part, 32*part+32)
-  const int token = blockIdx.x * kQuantizeTokensPerBlock + slot;
+  const int token = blockIdx.x * kTokensPerBlock + slot;
   float values[32];
   float maximum[2] = {0.0f, 0.0f};
   if (token < tokens) {
@@ -453,9 +454,15 @@ quantize_input_kernel(const __nv_bfloat16* __restrict__ input, const int* __rest
 void launch_quantize_input(const void* input_bf16, const int* expert_ids, const float* in_scale_q,
                            const RoutePlan& plan, int tokens, uint8_t* packed, uint8_t* scales,
                            cudaStream_t stream) {
+  const __nv_bfloat16* input = static_cast<const __nv_bfloat16*>(input_bf16);
+  if (tokens <= 1024) {  // too few tokens to fill the SMs four at a time
+    quantize_input_kernel<1><<<tokens, kQuantizeThreadsPerToken, 0, stream>>>(
+        input, expert_ids, in_scale_q, plan, tokens, packed, scales);
+    return;
+  }
   const int blocks = (tokens + kQuantizeTokensPerBlock - 1) / kQuantizeTokensPerBlock;
-  quantize_input_kernel<<<blocks, kQuantizeThreads, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(input_bf16), expert_ids, in_scale_q, plan, tokens, packed, scales);
+  quantize_input_kernel<kQuantizeTokensPerBlock><<<blocks, kQuantizeThreads, 0, stream>>>(
+      input, expert_ids, in_scale_q, plan, tokens, packed, scales);
 }
 
 // ---------------------------------------------------------------------------

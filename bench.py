@@ -29,7 +29,8 @@ LAYER_WEIGHT_BYTES = 428212224
 NOMINAL_FP4_TFLOPS = 9000.0
 # fused w13 launch at 4096 tokens: weights + weight scales + operand codes/scales + output codes/scales
 W13_ALGORITHMIC_BYTES = 128 * (1982464 + 247808) + 32768 * (1408 + 176) + 32768 * (352 + 44)
-W13_DRAM_TRAFFIC_BYTES = 353359616
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch (ncu capture summarised under profiles/)
+W13_DRAM_TRAFFIC_BYTES = 392952832 + 18171136
 WORKLOAD = "prefill_4096_tokens_router_bias_N(0,0.5)"
 
 

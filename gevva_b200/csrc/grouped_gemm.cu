@@ -434,10 +434,14 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     tmem_relinquish();
   }
   if (kMode == kGeglu) load_erf_table(smem->erf_table);
+  grid_launch_dependents();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = smem->tmem_base;
+  // Everything above touched only this CTA's shared and tensor memory; from here on the
+  // kernel reads what earlier kernels of the stream wrote.
+  grid_dependency_wait();
 
   const int m_tiles = p.num_m_tiles[0];
   const int total_items = m_tiles * p.n_tiles;
@@ -815,9 +819,8 @@ template <int kMode, int kAtoms, int kN> cudaError_t raise_smem_limit() {
 
 template <int kMode, int kN>
 void launch_variant(const GemmOperands& op, const GemmParams& p, int sm_count, cudaStream_t stream) {
-  grouped_nvfp4_gemm_kernel<kMode, 1, kN>
-      <<<sm_count, kGemmThreads, gemm_smem_bytes<kMode, 1, kN>(), stream>>>(op.map_a, op.map_a32, op.map_b,
-                                                                            op.map_b64, p);
+  launch_chained(grouped_nvfp4_gemm_kernel<kMode, 1, kN>, dim3(sm_count), dim3(kGemmThreads),
+                 gemm_smem_bytes<kMode, 1, kN>(), stream, op.map_a, op.map_a32, op.map_b, op.map_b64, p);
 }
 }  // namespace
 

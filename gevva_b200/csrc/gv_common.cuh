@@ -121,6 +121,39 @@ __device__ __forceinline__ bool elect_one() {
   return elected != 0;
 }
 
+// Programmatic dependent launch.  A kernel launched with launch_chained() below may begin
+// while its predecessor in the stream is still running; it must call grid_dependency_wait()
+// before it touches anything the predecessor (or any earlier kernel) reads or writes.  The
+// wait returns once the predecessor has completed and its writes are visible; in a kernel
+// launched the ordinary way it returns at once.  grid_launch_dependents() lets the successor
+// start its own preamble early.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// Host side: launches `kernel` so that it may start before the previous kernel of `stream`
+// has finished (see grid_dependency_wait above).  Every kernel launched this way waits at its
+// top, so results are those of ordinary stream order.
+template <class... Params, class... Args>
+inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem_bytes,
+                                  cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem_bytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));

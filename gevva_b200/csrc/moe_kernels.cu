@@ -121,6 +121,7 @@ __device__ __forceinline__ uint32_t count_chunk(int expert, int* warp_counts) {
 
 __global__ void __launch_bounds__(kSortChunk)
 route_sort_single_kernel(const int* __restrict__ expert_ids, int routes, RoutePlan plan) {
+  grid_launch_dependents();
   __shared__ int warp_counts[32 * kExperts];
   __shared__ int begins[kExperts];
   __shared__ int scan_scratch[16];
@@ -200,6 +201,7 @@ route_prefix_kernel(int chunks, int routes, RoutePlan plan) {
 
 __global__ void __launch_bounds__(kSortChunk)
 route_scatter_kernel(const int* __restrict__ expert_ids, int routes, RoutePlan plan) {
+  grid_launch_dependents();
   __shared__ int warp_counts[32 * kExperts];
   const int tid = threadIdx.x;
   for (int i = tid; i < 32 * kExperts; i += kSortChunk) warp_counts[i] = 0;
@@ -266,6 +268,7 @@ __device__ __forceinline__ bool grid_barrier(int* sync, int ctas, int* status) {
 // scatters its routes.
 __global__ void __launch_bounds__(kSortChunk)
 route_sort_fused_kernel(const int* __restrict__ expert_ids, int routes, int chunks, RoutePlan plan) {
+  grid_launch_dependents();
   __shared__ int warp_counts[32 * kExperts];
   __shared__ int scan_scratch[16];
   const int tid = threadIdx.x;
@@ -382,6 +385,8 @@ quantize_input_kernel(const __nv_bfloat16* __restrict__ input, const int* __rest
   __shared__ float route_multiplier[kTokensPerBlock][kTopK];
   __shared__ int route_row[kTokensPerBlock][kTopK];  // sorted row, or -1 for a rejected expert id
   __shared__ unsigned long long route_scale_base[kTokensPerBlock][kTopK];
+  grid_launch_dependents();
+  grid_dependency_wait();  // the route sort's plan, and the previous user of the output buffers
   if (threadIdx.x < kTokensPerBlock * kTopK) {
     const int slot = threadIdx.x / kTopK;
     const int k = threadIdx.x % kTopK;
@@ -456,13 +461,13 @@ void launch_quantize_input(const void* input_bf16, const int* expert_ids, const 
                            cudaStream_t stream) {
   const __nv_bfloat16* input = static_cast<const __nv_bfloat16*>(input_bf16);
   if (tokens <= 1024) {  // too few tokens to fill the SMs four at a time
-    quantize_input_kernel<1><<<tokens, kQuantizeThreadsPerToken, 0, stream>>>(
-        input, expert_ids, in_scale_q, plan, tokens, packed, scales);
+    launch_chained(quantize_input_kernel<1>, dim3(tokens), dim3(kQuantizeThreadsPerToken), 0, stream, input,
+                   expert_ids, in_scale_q, plan, tokens, packed, scales);
     return;
   }
   const int blocks = (tokens + kQuantizeTokensPerBlock - 1) / kQuantizeTokensPerBlock;
-  quantize_input_kernel<kQuantizeTokensPerBlock><<<blocks, kQuantizeThreads, 0, stream>>>(
-      input, expert_ids, in_scale_q, plan, tokens, packed, scales);
+  launch_chained(quantize_input_kernel<kQuantizeTokensPerBlock>, dim3(blocks), dim3(kQuantizeThreads), 0, stream,
+                 input, expert_ids, in_scale_q, plan, tokens, packed, scales);
 }
 
 // ---------------------------------------------------------------------------
@@ -527,6 +532,8 @@ reduce_routes_kernel(const __nv_bfloat16* __restrict__ routed, const float* __re
                      const int* __restrict__ inverse_routes, __nv_bfloat16* __restrict__ output) {
   const int token = blockIdx.x;
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  grid_launch_dependents();
+  grid_dependency_wait();  // the down GEMM's rows
 #pragma unroll
   for (int k = 0; k < kTopK; ++k) {
     const int index = token * kTopK + k;
@@ -552,9 +559,9 @@ reduce_routes_kernel(const __nv_bfloat16* __restrict__ routed, const float* __re
 void launch_reduce_routes(const void* routed_bf16, const float* route_weights,
                           const int* inverse_routes, int tokens, void* output_bf16,
                           cudaStream_t stream) {
-  reduce_routes_kernel<<<tokens, kHidden / 8, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(routed_bf16), route_weights, inverse_routes,
-      static_cast<__nv_bfloat16*>(output_bf16));
+  launch_chained(reduce_routes_kernel, dim3(tokens), dim3(kHidden / 8), 0, stream,
+                 static_cast<const __nv_bfloat16*>(routed_bf16), route_weights, inverse_routes,
+                 static_cast<__nv_bfloat16*>(output_bf16));
 }
 
 // ---------------------------------------------------------------------------

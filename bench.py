@@ -104,6 +104,30 @@ def build_layer(device, rank):
     return layer, layer.inputs(TOKENS, seed=1000 + rank)
 
 
+def library_nvfp4_gemm_tflops(device, size=8192, launches=20):
+    """Comparison figure only: the library's block-scaled NVFP4 GEMM (cuBLASLt through
+    torch._scaled_mm) on a dense size^3 problem, timed here with CUDA events.  It is the FP4
+    throughput this box reaches with a library kernel; MEASURED_PEAKS.json has no FP4 entry."""
+    import torch
+    try:
+        a = torch.randint(0, 255, (size, size // 2), dtype=torch.uint8, device=device).view(torch.float4_e2m1fn_x2)
+        b = torch.randint(0, 255, (size, size // 2), dtype=torch.uint8, device=device).view(torch.float4_e2m1fn_x2)
+        sa = torch.ones(size * size // 16, device=device).to(torch.float8_e4m3fn)
+        sb = torch.ones(size * size // 16, device=device).to(torch.float8_e4m3fn)
+        run = lambda: torch._scaled_mm(a, b.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16)
+        for _ in range(3):
+            run()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(launches):
+            run()
+        end.record()
+        torch.cuda.synchronize()
+        return 2.0 * size ** 3 / (start.elapsed_time(end) / launches * 1e-3) / 1e12
+    except Exception:  # not every torch build exposes the FP4 path
+        return None
+
+
 def layer_step(layer, x, out, weights, ids):
     """The timed unit: router projection with bias (one library GEMM) + our kernels.  With more
     than one GPU the experts are sharded and `layer.ep` exchanges rows over NVLink."""
@@ -384,9 +408,10 @@ def run_gpu(args):
         achieved = W13_FLOP_PER_TOKEN * TOKENS / (w13_ms * 1e-3) / 1e12
         total_tokens = TOKENS * world * args.steps
         value = total_tokens / (elapsed_ms * 1e-3)
-        # single GPU: route, 3 sort kernels, quantise, w13 (+GeGLU), w2, reduce; expert parallel:
-        # route, 3 sort, publish, send-bases, dispatch, receive-plan, w13, w2, combine, reduce
-        launches_per_step = 8 if world == 1 else 12
+        # our kernels per step.  Single GPU: route, sort, quantise, w13 (+GeGLU), w2, reduce.
+        # Expert parallel: route, sort, publish counts, 3 barriers, send bases, dispatch, receive
+        # plan, scale swizzle, row destinations, w13, w2, reduce.
+        launches_per_step = 6 if world == 1 else 15
         line = {
             "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -416,6 +441,13 @@ def run_gpu(args):
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }
+        if world == 1 and not args.no_library_compare:
+            library = library_nvfp4_gemm_tflops(device)
+            if library:
+                line["roofline"]["library_nvfp4_gemm_tflops"] = library
+                line["roofline"]["frac_of_library_nvfp4_gemm"] = achieved / library
+                line["roofline"]["library_note"] = ("comparison only: cuBLASLt block-scaled NVFP4 GEMM, dense "
+                                                    "8192^3, timed in this run")
         if ep_phases is not None:
             line["ep_phases_us_rank0"] = ep_phases
         if world == 1 and not args.no_decode:
@@ -436,6 +468,8 @@ def run_gpu(args):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--no-library-compare", action="store_true",
+                        help="skip timing the library NVFP4 GEMM that is reported beside the roofline")
     parser.add_argument("--steps", type=int, default=50)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])

@@ -10,7 +10,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libgevva_moe.so")
-SOURCES = ["moe_kernels.cu", "grouped_gemm.cu", "moe_abi.cu", "route_sort_noalloc.cu", "ep.cu", "dense_ff.cu", "dense_abi.cu"]
+SOURCES = ["moe_kernels.cu", "grouped_gemm.cu", "moe_abi.cu", "route_sort_noalloc.cu", "ep.cu", "dense_ff.cu", "dense_abi.cu", "sidecar.cpp"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -24,7 +24,7 @@ def needs_build():
     built = os.path.getmtime(LIB)
     for root, _, files in os.walk(CSRC):
         for name in files:
-            if name.endswith((".cu", ".cuh", ".h")) and os.path.getmtime(os.path.join(root, name)) > built:
+            if name.endswith((".cu", ".cuh", ".h", ".cpp")) and os.path.getmtime(os.path.join(root, name)) > built:
                 return True
     header = os.path.join(HERE, "..", "include", "gevva_moe.h")
     return os.path.getmtime(header) > built

@@ -271,6 +271,34 @@ int gevva_pack_fp8(const float* weights, size_t count, void* out, float* scale, 
 int gevva_moe_pack_experts(const float* weights, int experts, int n_out, int k_in, void* codes,
                            void* scales, float* global_scales, gevva_stream_t stream);
 
+/* Packed expert sidecar reader (host only, no CUDA call).  Replaces, for this path,
+ * inspect_safetensors / MappedShard::tensor (include/gevva/safetensors.hpp:12-27, :36-53,
+ * src/safetensors.cpp) and the 13-tensors-per-layer schema check of the runtime
+ * (src/runtime.cpp:222-254).  The file is mapped read-only; views point into the mapping and
+ * die with gevva_sidecar_close.  Validation is strict: integer shapes and offsets only, known
+ * whole-byte dtypes, end-begin = numel*itemsize without overflow, tensors tile the data
+ * section exactly, __metadata__ holds strings.  Failures return GEVVA_MOE_BAD_ARGUMENT and
+ * leave a message for gevva_sidecar_error() (thread-local). */
+typedef struct gevva_sidecar gevva_sidecar;
+typedef struct {
+  char dtype[16];     /* "U8", "F32", "BF16", ... */
+  int rank;           /* at most 8 */
+  uint64_t shape[8];
+  const void* data;   /* host pointer into the mapping */
+  uint64_t bytes;
+} gevva_sidecar_view;
+int gevva_sidecar_open(gevva_sidecar** out, const char* path);
+void gevva_sidecar_close(gevva_sidecar* sidecar);
+int gevva_sidecar_tensor_count(const gevva_sidecar* sidecar);
+int gevva_sidecar_tensor(const gevva_sidecar* sidecar, const char* name, gevva_sidecar_view* view);
+/* Names, dtypes and shapes of layers 0..layers-1 and nothing else in the file (the reference
+ * checks 30 layers x 13 tensors). */
+int gevva_sidecar_check_layers(const gevva_sidecar* sidecar, int layers);
+/* HOST views of the eight tensors of one layer that gevva_moe_create reads; the caller copies
+ * them to the device. */
+int gevva_sidecar_layer_weights(const gevva_sidecar* sidecar, int layer, gevva_moe_weights* host_views);
+const char* gevva_sidecar_error(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -21,7 +21,7 @@ def lib():
 def declared_functions():
     text = open(os.path.join(ROOT, "include", "gevva_moe.h")).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(gevva_moe_[a-z0-9_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(gevva_(?:moe|ff|dense|pack|sidecar)_[a-z0-9_]+)\s*\(", text)))
 
 
 def test_every_declared_symbol_is_exported(lib):

@@ -71,13 +71,13 @@ enum GemmMode { kPlain = 0, kGeglu = 1, kFp8 = 2 };  // kFp8: dense E4M3 operand
 
 // A pipeline stage holds kAtoms K blocks of 256 elements (one 128-byte swizzle row each) of
 // 128 activation rows and kN weight rows.  At N = 256 a stage is 54 KiB, so four stages fit
-// (three beside the store staging of the plain epilogue); at N = 128 five or six.
+// (three beside the store staging of the plain epilogue); at N = 128 five.
 template <int kMode, int kAtomsPerStage, int kN> struct StageShape {
   static_assert(kN == 128 || kN == 256, "weight rows per item");
   static_assert(kN == 128 || kAtomsPerStage == 1, "wide tiles take one K block per stage");
   static constexpr int kAtoms = kAtomsPerStage;
   static constexpr int kStages =
-      kN == 256 ? (kMode == kGeglu ? 4 : 3) : (kMode == kGeglu ? 6 / kAtomsPerStage : 5);
+      kN == 256 ? (kMode == kGeglu ? 4 : 3) : 5;
   static constexpr int kAccStages = kN == 256 ? 1 : 2;
   static constexpr int kWeightBytes = kN * kTileKBytes;        // per K block
   static constexpr int kWeightSfBytes = (kN / 128) * kSfStageBytes;
@@ -404,6 +404,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   constexpr int kAccStages = Smem::kAccStages;
   constexpr bool kWide = kN == 256;
   static_assert(kMode != kFp8 || !kWide, "the dense path uses 128-row weight tiles");
+  static_assert(kMode != kGeglu || kWide, "the fused form exists for 256-row weight tiles only");
   extern __shared__ uint8_t smem_raw[];
   Smem* smem = reinterpret_cast<Smem*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -513,10 +514,6 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
               const CUtensorMap* map = half_item ? &map_b64 : &map_b;
               tma_load_2d(smem->b[stage], map, &smem->full[stage], x, row);
               tma_load_2d(smem->b[stage] + kOperandStageBytes, map, &smem->full[stage], x, row2);
-            } else if (kMode == kGeglu) {
-              tma_load_2d(smem->b[stage] + atom * kOperandStageBytes, &map_b, &smem->full[stage], x, row);
-              tma_load_2d(smem->b[stage] + atom * kOperandStageBytes + kOperandStageBytes / 2, &map_b,
-                          &smem->full[stage], x, row2);
             } else {
               tma_load_2d(smem->b[stage] + atom * kOperandStageBytes, &map_b, &smem->full[stage], x, row);
             }
@@ -689,27 +686,6 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           stage_and_store(r0, alpha, staging, quarter, sub, lane, rows_valid, row0, n_tile * kN, p);
           stage_and_store(r1, alpha, staging, quarter, sub, lane, rows_valid, row0,
                           n_tile * kN + kStoreColumns, p);
-        }
-      } else if constexpr (!kWide) {
-        // Fused GeGLU + NVFP4 requantise.  Accumulator columns [0,64) are up, [64,128) gate,
-        // of intermediate columns [64*n_tile, 64*n_tile+64); this warp owns the 16-column
-        // block `sub` of them.
-        const float multiplier = p.next_scale_q[expert];
-        uint32_t up[16], gate[16];
-        tmem_load_32x16(tmem_row + sub * 16, up);
-        tmem_load_32x16(tmem_row + 64 + sub * 16, gate);
-        tmem_load_wait();
-        tc_fence_before_sync();
-        mbar_arrive(&smem->acc_empty[acc_stage]);
-        if (row_local < rows_valid) {
-          uint32_t codes_lo, codes_hi;
-          const uint32_t scale = geglu_block(up, gate, alpha, multiplier, smem->erf_table, codes_lo, codes_hi);
-          *reinterpret_cast<uint2*>(p.next_codes + static_cast<size_t>(row0 + row_local) * (kInter / 2) +
-                                    n_tile * 32 + sub * 8) = make_uint2(codes_lo, codes_hi);
-          // scale group 4*n_tile+sub of row (128*m_tile + row_local) of the w2 operand
-          constexpr int groups = kInter / 16;
-          p.next_scales[static_cast<size_t>(m_tile) * kTileM * groups +
-                        sf_offset(row_local, 4 * n_tile + sub, groups)] = static_cast<uint8_t>(scale);
         }
       } else {
         // Fused GeGLU + NVFP4 requantise, wide tile.  Accumulator columns [0,128) are up and

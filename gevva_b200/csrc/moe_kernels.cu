@@ -338,7 +338,11 @@ void launch_route_sort(const int* expert_ids, int routes, const RoutePlan& plan,
     return;
   }
   int chunks = (routes + kSortChunk - 1) / kSortChunk;
-  if (plan.sync != nullptr && chunks <= current_sm_count()) {
+  // While a stream is being captured into a graph the three plain launches are used: they
+  // need no co-residency guarantee and are certain to be capturable.
+  cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &capture) != cudaSuccess) capture = cudaStreamCaptureStatusActive;
+  if (plan.sync != nullptr && chunks <= current_sm_count() && capture == cudaStreamCaptureStatusNone) {
     RoutePlan plan_copy = plan;
     void* args[] = {&expert_ids, &routes, &chunks, &plan_copy};
     const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(route_sort_fused_kernel),

@@ -173,19 +173,18 @@ def write_sidecar(path, layers):
             out.write(blob.tobytes())
 
 
-def synthetic_layer_tensors(packed, s1, s2):
-    """The thirteen tensors of one layer from `make_packed_experts` output and the two static
-    activation scales, following tools/pack_trtllm_experts.py:134-148 (alpha = input scale x
-    weight global scale, input_scale_quant = 1 / input scale)."""
+def synthetic_layer_tensors(packed, weights, s1, s2):
+    """The thirteen tensors of one layer from `make_packed_experts` output, the runner's
+    `ExpertWeights` (whose alpha and input_scale_quant vectors are stored as they are) and the
+    two static activation scales, following tools/pack_trtllm_experts.py:134-148."""
     ones = np.ones(EXPERTS, dtype=np.float32)
     g13 = packed["g13"].detach().cpu().numpy().astype(np.float32)
     g2 = packed["g2"].detach().cpu().numpy().astype(np.float32)
     return {
-        "w13.weight": packed["w13"], "w13.weight_scale": packed["w13_sf"],
-        "w2.weight": packed["w2"], "w2.weight_scale": packed["w2_sf"],
+        "w13.weight": weights.w13, "w13.weight_scale": weights.w13_sf,
+        "w2.weight": weights.w2, "w2.weight_scale": weights.w2_sf,
         "w13.input_scale": ones * np.float32(s1), "w2.input_scale": ones * np.float32(s2),
         "w13.weight_scale_2": np.stack([g13, g13], axis=1), "w2.weight_scale_2": g2,
-        "g1.alpha": g13 * np.float32(s1), "g1.alpha_up": g13 * np.float32(s1),
-        "g2.alpha": g2 * np.float32(s2),
-        "g1.input_scale_quant": ones / np.float32(s1), "g2.input_scale_quant": ones / np.float32(s2),
+        "g1.alpha": weights.alpha1, "g1.alpha_up": weights.alpha1, "g2.alpha": weights.alpha2,
+        "g1.input_scale_quant": weights.in_scale_q1, "g2.input_scale_quant": weights.in_scale_q2,
     }

@@ -20,7 +20,7 @@ def test_sidecar_round_trip_runs_the_layer(tmp_path):
     torch.cuda.synchronize()
 
     path = tmp_path / "experts-00.safetensors"
-    write_sidecar(path, [synthetic_layer_tensors(layer.packed, layer.s1, layer.s2)])
+    write_sidecar(path, [synthetic_layer_tensors(layer.packed, layer.weights, layer.s1, layer.s2)])
     with ExpertSidecar(path) as sidecar:
         sidecar.check_layers(1)
         weights = sidecar.layer_weights(0, device=x.device)

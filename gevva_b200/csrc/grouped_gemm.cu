@@ -103,7 +103,7 @@ struct alignas(1024) GemmSmem {
   uint64_t acc_empty[kAccStages];
   uint32_t tmem_base;
   volatile int abort;
-  float erf_table[GV_ERF_TABLE_FLOATS];
+  alignas(16) float erf_table[GV_ERF_TABLE_FLOATS];
 #if defined(GV_TRACE)
   unsigned int trace[3][768];
   int trace_count[3];

@@ -84,6 +84,18 @@ GV_HD float gv_erff(float x, const float* table) {
   const float index = truncf(GV_MUL(clamped, 2.0f));
   const float u = GV_SUB(GV_FMA(index, -0.5f, clamped), 0.25f);
   const float* c = table + 8 * (int)index;
+#if defined(__CUDA_ARCH__)
+  // two 16-byte loads instead of seven 4-byte ones (the table is 16-byte aligned in kernels)
+  const float4 lo = *reinterpret_cast<const float4*>(c);
+  const float4 hi = *reinterpret_cast<const float4*>(c + 4);
+  float p = hi.z;
+  p = GV_FMA(p, u, hi.y);
+  p = GV_FMA(p, u, hi.x);
+  p = GV_FMA(p, u, lo.w);
+  p = GV_FMA(p, u, lo.z);
+  p = GV_FMA(p, u, lo.y);
+  p = GV_FMA(p, u, lo.x);
+#else
   float p = c[6];
   p = GV_FMA(p, u, c[5]);
   p = GV_FMA(p, u, c[4]);
@@ -91,6 +103,7 @@ GV_HD float gv_erff(float x, const float* table) {
   p = GV_FMA(p, u, c[2]);
   p = GV_FMA(p, u, c[1]);
   p = GV_FMA(p, u, c[0]);
+#endif
   const float r = a >= 4.0f ? 1.0f : p;
   return copysignf(r, x);
 }

@@ -486,7 +486,7 @@ __global__ void __launch_bounds__(kGegluRowsPerBlock * kQuadsInter)
 geglu_quantize_kernel(const __nv_bfloat16* __restrict__ fused, const float* __restrict__ in_scale_q,
                       RoutePlan plan, int routes, uint8_t* __restrict__ packed,
                       uint8_t* __restrict__ scales) {
-  __shared__ float erf_table[GV_ERF_TABLE_FLOATS];
+  __shared__ __align__(16) float erf_table[GV_ERF_TABLE_FLOATS];
   load_erf_table(erf_table);
   __syncthreads();
   const int route = blockIdx.x * kGegluRowsPerBlock + threadIdx.x / kQuadsInter;

@@ -110,80 +110,108 @@ __global__ void __launch_bounds__(kExperts) ep_send_bases_kernel(EpDevice ep) {
 }
 
 // ---- 2b: quantise and store into the owners' operand buffers -----------------------
-// Same arithmetic and thread mapping as quantize_input_kernel (one CTA per token, the row
-// read once); only the destination differs.
-constexpr int kQuantizeThreads = kHidden / 8;
+// Same arithmetic and thread mapping as quantize_input_kernel (a token row is read once, a
+// thread owns 32 consecutive columns = two 16-value blocks, four tokens per CTA); only the
+// destination differs.
+constexpr int kDispatchThreadsPerToken = kHidden / 32;  // 88
+constexpr int kDispatchTokensPerBlock = 4;
+constexpr int kDispatchThreads = kDispatchThreadsPerToken * kDispatchTokensPerBlock;
 
-__global__ void __launch_bounds__(kQuantizeThreads)
+__global__ void __launch_bounds__(kDispatchThreads)
 ep_dispatch_kernel(const __nv_bfloat16* __restrict__ input, const int* __restrict__ expert_ids,
-                   const float* __restrict__ in_scale_q_global, EpDevice ep, RoutePlan plan) {
+                   const float* __restrict__ in_scale_q_global, EpDevice ep, RoutePlan plan, int tokens) {
   constexpr int groups = kHidden / 16;
-  __shared__ float route_multiplier[kTopK];
-  __shared__ uint8_t* route_codes[kTopK];
-  __shared__ uint8_t* route_scales[kTopK];
-  __shared__ __align__(16) uint32_t scale_words[kTopK][groups / 4];  // one 176-byte row per route
-  const int token = blockIdx.x;
-  if (threadIdx.x < kTopK) {
-    const int route = token * kTopK + threadIdx.x;
-    const int expert = expert_ids[route];
-    if (expert < 0 || expert >= kExperts) {
-      route_codes[threadIdx.x] = nullptr;
-    } else {
-      const int v = ep.remap[expert];
-      const int owner = v / ep.local_experts;
-      const int j = plan.inverse_routes[route] - plan.expert_offsets[v];
-      const int row = ep.send_row_base[v] + j;
-      route_multiplier[threadIdx.x] = in_scale_q_global[expert];
-      route_codes[threadIdx.x] = ep.peer_codes[owner] + static_cast<size_t>(row) * (kHidden / 2);
-      route_scales[threadIdx.x] = ep.peer_scales[owner] + static_cast<size_t>(row) * groups;
+  __shared__ float route_multiplier[kDispatchTokensPerBlock][kTopK];
+  __shared__ uint8_t* route_codes[kDispatchTokensPerBlock][kTopK];
+  __shared__ uint8_t* route_scales[kDispatchTokensPerBlock][kTopK];
+  // one 176-byte scale row per route
+  __shared__ __align__(16) uint16_t scale_rows[kDispatchTokensPerBlock][kTopK][groups / 2];
+  if (threadIdx.x < kDispatchTokensPerBlock * kTopK) {
+    const int slot = threadIdx.x / kTopK;
+    const int k = threadIdx.x % kTopK;
+    const int token = blockIdx.x * kDispatchTokensPerBlock + slot;
+    uint8_t* codes_row = nullptr;
+    if (token < tokens) {
+      const int route = token * kTopK + k;
+      const int expert = expert_ids[route];
+      if (expert >= 0 && expert < kExperts) {
+        const int v = ep.remap[expert];
+        const int owner = v / ep.local_experts;
+        const int j = plan.inverse_routes[route] - plan.expert_offsets[v];
+        const int row = ep.send_row_base[v] + j;
+        route_multiplier[slot][k] = in_scale_q_global[expert];
+        codes_row = ep.peer_codes[owner] + static_cast<size_t>(row) * (kHidden / 2);
+        route_scales[slot][k] = ep.peer_scales[owner] + static_cast<size_t>(row) * groups;
+      }
+    }
+    route_codes[slot][k] = codes_row;
+  }
+  const int slot = threadIdx.x / kDispatchThreadsPerToken;
+  const int part = threadIdx.x - slot * kDispatchThreadsPerToken;  // columns [32*part, 32*part+32)
+  const int token = blockIdx.x * kDispatchTokensPerBlock + slot;
+  float values[32];
+  float maximum[2] = {0.0f, 0.0f};
+  if (token < tokens) {
+    const uint4* source = reinterpret_cast<const uint4*>(input + static_cast<size_t>(token) * kHidden) + 4 * part;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 raw = __ldg(source + i);
+      values[8 * i + 0] = __uint_as_float(raw.x << 16);
+      values[8 * i + 1] = __uint_as_float(raw.x & 0xffff0000u);
+      values[8 * i + 2] = __uint_as_float(raw.y << 16);
+      values[8 * i + 3] = __uint_as_float(raw.y & 0xffff0000u);
+      values[8 * i + 4] = __uint_as_float(raw.z << 16);
+      values[8 * i + 5] = __uint_as_float(raw.z & 0xffff0000u);
+      values[8 * i + 6] = __uint_as_float(raw.w << 16);
+      values[8 * i + 7] = __uint_as_float(raw.w & 0xffff0000u);
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      maximum[0] = fmaxf(maximum[0], fabsf(values[i]));
+      maximum[1] = fmaxf(maximum[1], fabsf(values[16 + i]));
     }
   }
-  const int lane = threadIdx.x & 31;
-  const uint4 raw = __ldg(reinterpret_cast<const uint4*>(input + static_cast<size_t>(token) * kHidden) +
-                          threadIdx.x);
-  float values[8];
-  values[0] = __uint_as_float(raw.x << 16);
-  values[1] = __uint_as_float(raw.x & 0xffff0000u);
-  values[2] = __uint_as_float(raw.y << 16);
-  values[3] = __uint_as_float(raw.y & 0xffff0000u);
-  values[4] = __uint_as_float(raw.z << 16);
-  values[5] = __uint_as_float(raw.z & 0xffff0000u);
-  values[6] = __uint_as_float(raw.w << 16);
-  values[7] = __uint_as_float(raw.w & 0xffff0000u);
-  float maximum = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) maximum = fmaxf(maximum, fabsf(values[i]));
-  maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, 1));
   __syncthreads();
-  const int quad = threadIdx.x >> 3;
+  if (token < tokens) {
 #pragma unroll 2
-  for (int k = 0; k < kTopK; ++k) {
-    uint8_t* codes_row = route_codes[k];
-    if (!codes_row) continue;
-    const float multiplier = route_multiplier[k];
-    const float unrounded = __fdiv_rn(__fmul_rn(multiplier, maximum), 6.0f);
-    const uint32_t scale = encode_e4m3(unrounded);
-    const float rounded = decode_e4m3(scale);
-    const float inverse = rounded == 0.0f ? 0.0f : __fdiv_rn(multiplier, rounded);
-    uint32_t codes = 0;
+    for (int k = 0; k < kTopK; ++k) {
+      uint8_t* codes_row = route_codes[slot][k];
+      if (!codes_row) continue;
+      const float multiplier = route_multiplier[slot][k];
+      uint32_t codes[4];
+      uint32_t scale_pair = 0;
 #pragma unroll
-    for (int pair = 0; pair < 4; ++pair)
-      codes |= encode_e2m1x2(__fmul_rn(values[2 * pair], inverse),
-                             __fmul_rn(values[2 * pair + 1], inverse)) << (8 * pair);
-    reinterpret_cast<uint32_t*>(codes_row)[threadIdx.x] = codes;
-    const int base_lane = lane & ~7;
-    uint32_t word = __shfl_sync(0xffffffffu, scale, base_lane);
-    word |= __shfl_sync(0xffffffffu, scale, base_lane + 2) << 8;
-    word |= __shfl_sync(0xffffffffu, scale, base_lane + 4) << 16;
-    word |= __shfl_sync(0xffffffffu, scale, base_lane + 6) << 24;
-    if ((lane & 7) == 0) scale_words[k][quad] = word;
+      for (int block = 0; block < 2; ++block) {
+        const float unrounded = __fdiv_rn(__fmul_rn(multiplier, maximum[block]), 6.0f);
+        const uint32_t scale = encode_e4m3(unrounded);
+        const float rounded = decode_e4m3(scale);
+        const float inverse = rounded == 0.0f ? 0.0f : __fdiv_rn(multiplier, rounded);
+        scale_pair |= scale << (8 * block);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t word = 0;
+#pragma unroll
+          for (int pair = 0; pair < 4; ++pair)
+            word |= encode_e2m1x2(__fmul_rn(values[16 * block + 8 * half + 2 * pair], inverse),
+                                  __fmul_rn(values[16 * block + 8 * half + 2 * pair + 1], inverse))
+                    << (8 * pair);
+          codes[2 * block + half] = word;
+        }
+      }
+      reinterpret_cast<uint4*>(codes_row)[part] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+      scale_rows[slot][k][part] = static_cast<uint16_t>(scale_pair);
+    }
   }
   // Scale bytes cross NVLink as one contiguous 176-byte row per route (eleven 16-byte
-  // stores by one warp); the owner puts them into the MMA's interleaved layout itself.
+  // stores); the owner puts them into the MMA's interleaved layout itself.
   __syncthreads();
-  const int k = threadIdx.x >> 5;
-  if (k < kTopK && lane < groups / 16 && route_codes[k])
-    reinterpret_cast<uint4*>(route_scales[k])[lane] = reinterpret_cast<const uint4*>(scale_words[k])[lane];
+  for (int index = threadIdx.x; index < kDispatchTokensPerBlock * kTopK * (groups / 16); index += kDispatchThreads) {
+    const int piece = index % (groups / 16);
+    const int k = (index / (groups / 16)) % kTopK;
+    const int s = index / (groups / 16) / kTopK;
+    if (route_codes[s][k])
+      reinterpret_cast<uint4*>(route_scales[s][k])[piece] = reinterpret_cast<const uint4*>(scale_rows[s][k])[piece];
+  }
 }
 
 // ---- 3a: group geometry of the local experts ---------------------------------------
@@ -454,8 +482,9 @@ int gevva_moe_ep_dispatch(gevva_moe_ep* ep, const void* in, const int* ids, int 
                           gevva_stream_t stream) {
   if (!ep || !in || !ids || tokens < 1 || tokens > ep->max_tokens) return GEVVA_MOE_BAD_ARGUMENT;
   gv::ep_send_bases_kernel<<<1, kExperts, 0, stream>>>(ep->dev);
-  gv::ep_dispatch_kernel<<<tokens, gv::kQuantizeThreads, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(in), ids, ep->in_scale_q1_global, ep->dev, ep->send_plan);
+  gv::ep_dispatch_kernel<<<(tokens + gv::kDispatchTokensPerBlock - 1) / gv::kDispatchTokensPerBlock,
+                          gv::kDispatchThreads, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(in), ids, ep->in_scale_q1_global, ep->dev, ep->send_plan, tokens);
   return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;
 }
 

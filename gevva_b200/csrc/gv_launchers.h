@@ -31,6 +31,12 @@ void launch_route(const void* logits_bf16, int ld, const void* expert_scale_bf16
 void launch_route_sort(const int* expert_ids, int routes, const RoutePlan& plan,
                        cudaStream_t stream);
 
+// Route sort and input quantiser in one launch; at most 128 tokens (1024 routes).
+constexpr int kFusedSortQuantizeMaxTokens = 128;
+void launch_route_sort_quantize_small(const void* input_bf16, const int* expert_ids, const float* in_scale_q,
+                                      const RoutePlan& plan, int tokens, uint8_t* packed, uint8_t* scales,
+                                      cudaStream_t stream);
+
 // bf16 [tokens, 2816] -> codes [R, 1408] (sorted order) + swizzled scale bytes.
 void launch_quantize_input(const void* input_bf16, const int* expert_ids, const float* in_scale_q,
                            const RoutePlan& plan, int tokens, uint8_t* packed, uint8_t* scales,

@@ -314,10 +314,17 @@ int gevva_moe_launch_stages(gevva_moe* runner, const void* in, const int* ids,
   if ((stages & GEVVA_MOE_STAGE_QUANTIZE) && !in) return GEVVA_MOE_BAD_ARGUMENT;
   if ((stages & GEVVA_MOE_STAGE_REDUCE) && (!out || !route_weights)) return GEVVA_MOE_BAD_ARGUMENT;
   const int routes = tokens * kTopK;
-  if (stages & GEVVA_MOE_STAGE_SORT) gv::launch_route_sort(ids, routes, s->plan, stream);
-  if (stages & GEVVA_MOE_STAGE_QUANTIZE)
-    gv::launch_quantize_input(in, ids, runner->weights.in_scale_q1, s->plan, tokens, s->input_codes,
-                              s->input_sf, stream);
+  const unsigned front = GEVVA_MOE_STAGE_SORT | GEVVA_MOE_STAGE_QUANTIZE;
+  if ((stages & front) == front && tokens <= gv::kFusedSortQuantizeMaxTokens) {
+    // decode-sized batch: one launch does both
+    gv::launch_route_sort_quantize_small(in, ids, runner->weights.in_scale_q1, s->plan, tokens, s->input_codes,
+                                         s->input_sf, stream);
+  } else {
+    if (stages & GEVVA_MOE_STAGE_SORT) gv::launch_route_sort(ids, routes, s->plan, stream);
+    if (stages & GEVVA_MOE_STAGE_QUANTIZE)
+      gv::launch_quantize_input(in, ids, runner->weights.in_scale_q1, s->plan, tokens, s->input_codes,
+                                s->input_sf, stream);
+  }
   const unsigned both = GEVVA_MOE_STAGE_W13 | GEVVA_MOE_STAGE_GEGLU;
   if ((stages & both) == both && !(stages & GEVVA_MOE_STAGE_UNFUSED)) {
     // production path: GeGLU + requantise inside the w13 epilogue, no bf16 w13 output

@@ -380,6 +380,62 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* out) {
   out[7] = __uint_as_float(raw.w & 0xffff0000u);
 }
 
+// The per-route part of the input quantiser: `values` are this thread's 32 columns of the
+// token, `maximum` the two block maxima; route_* describe the token's eight routes.
+__device__ __forceinline__ void quantize_routes_of_token(const float (&values)[32], const float (&maximum)[2],
+                                                         int part, const int* route_row,
+                                                         const float* route_multiplier,
+                                                         const unsigned long long* route_scale_base,
+                                                         uint8_t* __restrict__ packed,
+                                                         uint8_t* __restrict__ scales) {
+  // scale groups 2*part and 2*part+1 share a 4-group word of the swizzled layout
+  const unsigned scale_offset = static_cast<unsigned>(part >> 1) * 512u + static_cast<unsigned>(part & 1) * 2u;
+#pragma unroll 2
+  for (int k = 0; k < kTopK; ++k) {
+    const int dst = route_row[k];
+    if (dst < 0) continue;
+    const float multiplier = route_multiplier[k];
+    uint32_t codes[4];
+    uint32_t scale_pair = 0;
+#pragma unroll
+    for (int block = 0; block < 2; ++block) {
+      const float unrounded = __fdiv_rn(__fmul_rn(multiplier, maximum[block]), 6.0f);
+      const uint32_t scale = encode_e4m3(unrounded);
+      const float rounded = decode_e4m3(scale);
+      const float inverse = rounded == 0.0f ? 0.0f : __fdiv_rn(multiplier, rounded);
+      scale_pair |= scale << (8 * block);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int pair = 0; pair < 4; ++pair)
+          word |= encode_e2m1x2(__fmul_rn(values[16 * block + 8 * half + 2 * pair], inverse),
+                                __fmul_rn(values[16 * block + 8 * half + 2 * pair + 1], inverse))
+                  << (8 * pair);
+        codes[2 * block + half] = word;
+      }
+    }
+    reinterpret_cast<uint4*>(packed + static_cast<size_t>(dst) * (kHidden / 2))[part] =
+        make_uint4(codes[0], codes[1], codes[2], codes[3]);
+    *reinterpret_cast<uint16_t*>(scales + route_scale_base[k] + scale_offset) =
+        static_cast<uint16_t>(scale_pair);
+  }
+}
+
+// This thread's 32 columns of a token row and the two block maxima.
+__device__ __forceinline__ void load_token_columns(const __nv_bfloat16* __restrict__ input, int token, int part,
+                                                   float (&values)[32], float (&maximum)[2]) {
+  const uint4* source = reinterpret_cast<const uint4*>(input + static_cast<size_t>(token) * kHidden) + 4 * part;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) unpack_bf16x8(__ldg(source + i), values + 8 * i);
+  maximum[0] = maximum[1] = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    maximum[0] = fmaxf(maximum[0], fabsf(values[i]));
+    maximum[1] = fmaxf(maximum[1], fabsf(values[16 + i]));
+  }
+}
+
 template <int kTokensPerBlock>
 __global__ void __launch_bounds__(kQuantizeThreadsPerToken * kTokensPerBlock)
 quantize_input_kernel(const __nv_bfloat16* __restrict__ input, const int* __restrict__ expert_ids,
@@ -414,50 +470,129 @@ quantize_input_kernel(const __nv_bfloat16* __restrict__ input, const int* __rest
   const int token = blockIdx.x * kTokensPerBlock + slot;
   float values[32];
   float maximum[2] = {0.0f, 0.0f};
-  if (token < tokens) {
-    const uint4* source = reinterpret_cast<const uint4*>(input + static_cast<size_t>(token) * kHidden) + 4 * part;
+  if (token < tokens) load_token_columns(input, token, part, values, maximum);
+  __syncthreads();
+  if (token >= tokens) return;
+  quantize_routes_of_token(values, maximum, part, route_row[slot], route_multiplier[slot],
+                           route_scale_base[slot], packed, scales);
+}
+
+// Route sort and input quantiser in one launch, for batches of at most 1024 routes (decode
+// sizes, where the layer is a chain of short kernels and every launch costs as much as the
+// work).  One CTA per token: it counts all routes per expert in shared memory, ranks its own
+// eight routes among those with the same expert and a lower route index (the stable counting
+// sort of route_sort_single_kernel, computed redundantly per token), scans the 128 counts,
+// and quantises its token.  CTA 0 also writes the group geometry.
+__global__ void __launch_bounds__(kQuantizeThreadsPerToken)
+route_sort_quantize_small_kernel(const __nv_bfloat16* __restrict__ input, const int* __restrict__ expert_ids,
+                                 const float* __restrict__ in_scale_q, RoutePlan plan, int tokens,
+                                 uint8_t* __restrict__ packed, uint8_t* __restrict__ scales) {
+  constexpr int groups = kHidden / 16;
+  __shared__ int histogram[kExperts];
+  __shared__ int row_begin[kExperts];
+  __shared__ int scale_row_begin[kExperts];
+  __shared__ int own_expert[kTopK];
+  __shared__ int own_rank[kTopK];
+  __shared__ float route_multiplier[kTopK];
+  __shared__ int route_row[kTopK];
+  __shared__ unsigned long long route_scale_base[kTopK];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int tid = threadIdx.x;
+  const int token = blockIdx.x;
+  const int routes = tokens * kTopK;
+  for (int i = tid; i < kExperts; i += kQuantizeThreadsPerToken) histogram[i] = 0;
+  if (tid < kTopK) {
+    int expert = expert_ids[token * kTopK + tid];
+    if (expert < 0 || expert >= kExperts) expert = kExperts;
+    else if (plan.remap) expert = plan.remap[expert];
+    own_expert[tid] = expert;
+    own_rank[tid] = 0;
+  }
+  __syncthreads();
+  for (int route = tid; route < routes; route += kQuantizeThreadsPerToken) {
+    int expert = expert_ids[route];
+    if (expert < 0 || expert >= kExperts) {
+      if (token == 0) atomicExch(plan.status, static_cast<int>(kBadExpertId));
+      continue;
+    }
+    if (plan.remap) expert = plan.remap[expert];
+    atomicAdd(&histogram[expert], 1);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) unpack_bf16x8(__ldg(source + i), values + 8 * i);
+    for (int k = 0; k < kTopK; ++k)
+      if (expert == own_expert[k] && route < token * kTopK + k) atomicAdd(&own_rank[k], 1);
+  }
+  __syncthreads();
+  if (tid < 32) {
+    // lane l scans experts 4l..4l+3: rows and 128-row tiles
+    int counts[4], rows = 0, tiles = 0;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      maximum[0] = fmaxf(maximum[0], fabsf(values[i]));
-      maximum[1] = fmaxf(maximum[1], fabsf(values[16 + i]));
+    for (int i = 0; i < 4; ++i) {
+      counts[i] = histogram[4 * tid + i];
+      rows += counts[i];
+      tiles += (counts[i] + kTileM - 1) / kTileM;
+    }
+    int rows_inclusive = rows, tiles_inclusive = tiles;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+      const int r = __shfl_up_sync(0xffffffffu, rows_inclusive, offset);
+      const int t = __shfl_up_sync(0xffffffffu, tiles_inclusive, offset);
+      if (tid >= offset) {
+        rows_inclusive += r;
+        tiles_inclusive += t;
+      }
+    }
+    int row = rows_inclusive - rows, tile = tiles_inclusive - tiles;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int expert = 4 * tid + i;
+      row_begin[expert] = row;
+      scale_row_begin[expert] = tile * kTileM;
+      if (token == 0) {
+        plan.expert_offsets[expert] = row;
+        plan.scale_row_offsets[expert] = tile * kTileM;
+        const int expert_tiles = (counts[i] + kTileM - 1) / kTileM;
+        for (int j = 0; j < expert_tiles; ++j) plan.tile_expert[tile + j] = expert;
+      }
+      row += counts[i];
+      tile += (counts[i] + kTileM - 1) / kTileM;
+    }
+    if (token == 0 && tid == 31) {
+      plan.expert_offsets[kExperts] = row;
+      plan.scale_row_offsets[kExperts] = tile * kTileM;
+      plan.num_m_tiles[0] = tile;
     }
   }
   __syncthreads();
-  if (token >= tokens) return;
-  // scale groups 2*part and 2*part+1 share a 4-group word of the swizzled layout
-  const unsigned scale_offset = static_cast<unsigned>(part >> 1) * 512u + static_cast<unsigned>(part & 1) * 2u;
-#pragma unroll 2
-  for (int k = 0; k < kTopK; ++k) {
-    const int dst = route_row[slot][k];
-    if (dst < 0) continue;
-    const float multiplier = route_multiplier[slot][k];
-    uint32_t codes[4];
-    uint32_t scale_pair = 0;
-#pragma unroll
-    for (int block = 0; block < 2; ++block) {
-      const float unrounded = __fdiv_rn(__fmul_rn(multiplier, maximum[block]), 6.0f);
-      const uint32_t scale = encode_e4m3(unrounded);
-      const float rounded = decode_e4m3(scale);
-      const float inverse = rounded == 0.0f ? 0.0f : __fdiv_rn(multiplier, rounded);
-      scale_pair |= scale << (8 * block);
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t word = 0;
-#pragma unroll
-        for (int pair = 0; pair < 4; ++pair)
-          word |= encode_e2m1x2(__fmul_rn(values[16 * block + 8 * half + 2 * pair], inverse),
-                                __fmul_rn(values[16 * block + 8 * half + 2 * pair + 1], inverse))
-                  << (8 * pair);
-        codes[2 * block + half] = word;
-      }
+  if (tid < kTopK) {
+    const int route = token * kTopK + tid;
+    const int expert = own_expert[tid];
+    int dst = -1;
+    if (expert < kExperts) {
+      dst = row_begin[expert] + own_rank[tid];
+      plan.sorted_experts[dst] = expert;
+      plan.sorted_routes[dst] = route;
+      plan.inverse_routes[route] = dst;
+      // the static scale belongs to the expert id as the caller numbers it
+      route_multiplier[tid] = in_scale_q[expert_ids[route]];
+      route_scale_base[tid] = static_cast<unsigned long long>(scale_row_begin[expert]) * groups +
+                              sf_offset(own_rank[tid], 0, groups);
     }
-    reinterpret_cast<uint4*>(packed + static_cast<size_t>(dst) * (kHidden / 2))[part] =
-        make_uint4(codes[0], codes[1], codes[2], codes[3]);
-    *reinterpret_cast<uint16_t*>(scales + route_scale_base[slot][k] + scale_offset) =
-        static_cast<uint16_t>(scale_pair);
+    route_row[tid] = dst;
   }
+  float values[32];
+  float maximum[2];
+  load_token_columns(input, token, tid, values, maximum);
+  __syncthreads();
+  quantize_routes_of_token(values, maximum, tid, route_row, route_multiplier, route_scale_base, packed, scales);
+}
+
+void launch_route_sort_quantize_small(const void* input_bf16, const int* expert_ids, const float* in_scale_q,
+                                      const RoutePlan& plan, int tokens, uint8_t* packed, uint8_t* scales,
+                                      cudaStream_t stream) {
+  launch_chained(route_sort_quantize_small_kernel, dim3(tokens), dim3(kQuantizeThreadsPerToken), 0, stream,
+                 static_cast<const __nv_bfloat16*>(input_bf16), expert_ids, in_scale_q, plan, tokens, packed,
+                 scales);
 }
 
 void launch_quantize_input(const void* input_bf16, const int* expert_ids, const float* in_scale_q,

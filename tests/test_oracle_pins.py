@@ -31,7 +31,7 @@ def test_e2m1_encoder_matches_toolkit(oracle):
         assert (mine << 4) == (oracle.pin.pin_encode_e2m1x2(0.0, float(v)) & 0xF0), v
 
 
-def test_known_answers_from_survey(oracle):
+def test_known_answer_rounding_and_saturation_points(oracle):
     # round-to-nearest-even and saturation points of E2M1 / E4M3
     table = {0.25: 0x0, 0.75: 0x2, 1.25: 0x2, 1.75: 0x4, 2.5: 0x4, 3.5: 0x6, 5.0: 0x6, 7.0: 0x7,
              -6.5: 0xF}

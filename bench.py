@@ -191,9 +191,28 @@ def decode_sweep(layer, device, steps):
                      "algorithmic_bytes": algorithmic, "hbm_gbs": gbs,
                      "frac_of_measured_hbm": gbs / float(peaks["hbm_gbs"]),
                      "frac_of_8000_gbs": gbs / 8000.0, "tokens_per_s": tokens / (us * 1e-6),
-                     "launch": "CUDA graph replay, 7 kernels per layer"})
+                     "launch": "CUDA graph replay, 6 kernels per layer"})
     runner.check()
     return rows
+
+
+def decode_eager(layer, device, tokens, steps):
+    """For a profiler: `steps` decode-sized layer steps launched one by one (no CUDA graph),
+    each on a different batch so that the routed experts' weights come from HBM."""
+    import torch
+    import gevva_b200
+    from gevva_b200.runtime import Nvfp4ExpertRunner
+    runner = Nvfp4ExpertRunner(layer.weights, max(tokens, 1))
+    out = torch.empty((tokens, HIDDEN), dtype=torch.bfloat16, device=device)
+    weights = torch.empty((tokens, TOP_K), dtype=torch.float32, device=device)
+    ids = torch.empty((tokens, TOP_K), dtype=torch.int32, device=device)
+    for i in range(steps):
+        x = layer.inputs(tokens, seed=7000 + i)
+        logits = torch.matmul(x, layer.router_w.t())
+        gevva_b200.route_128_top8(logits, layer.expert_scale, weights=weights, ids=ids)
+        runner.launch_batch(x, ids, weights, out, tokens)
+    torch.cuda.synchronize()
+    runner.check()
 
 
 def oracle_sample(rank_seed, tokens):
@@ -292,6 +311,11 @@ def run_gpu(args):
 
     layer, x = build_layer(device, rank)
     layer.ep = None
+    if args.profile_decode:
+        decode_eager(layer, device, args.profile_decode, 6)
+        if rank == 0:
+            print(json.dumps({"profile_decode_tokens": args.profile_decode, "steps": 6}), flush=True)
+        return
     if world > 1:
         from gevva_b200.expert_parallel import ExpertParallelRunner, local_expert_weights
         layer.ep = ExpertParallelRunner(local_expert_weights(layer.weights, rank, world),
@@ -470,6 +494,8 @@ def main():
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--no-library-compare", action="store_true",
                         help="skip timing the library NVFP4 GEMM that is reported beside the roofline")
+    parser.add_argument("--profile-decode", type=int, default=0, metavar="TOKENS",
+                        help="run a few eager decode-sized layer steps of TOKENS tokens and exit (for ncu)")
     parser.add_argument("--steps", type=int, default=50)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])

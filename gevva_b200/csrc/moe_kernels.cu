@@ -359,13 +359,14 @@ void launch_route_sort(const int* expert_ids, int routes, const RoutePlan& plan,
 // Input quantiser.  Reference: quantize_bf16_sorted_moe, src/nvfp4_cutlass.cu:
 // 290-327 (one CTA per sorted route, 16 scalar loads per thread, byte stores, the
 // token row fetched eight times).  Here a token row is read once; a thread owns 32
-// consecutive columns (two 16-value blocks, four 16-byte loads) and, for each of the
-// token's eight routes, quantises them with that expert's static scale, storing 16 code
-// bytes and the two scale bytes (adjacent in the swizzled layout) of the route's sorted
-// row.  The kernel is bound by instruction issue (two IEEE divisions per block and
-// route), so nothing is computed twice: no lane shares a block with another.
+// consecutive columns (two 16-value blocks) and, for each of the token's eight routes,
+// quantises them with that expert's static scale, storing 16 code bytes and the two scale
+// bytes (adjacent in the swizzled layout) of the route's sorted row.  Nothing is computed
+// twice: no lane shares a block with another, and routes with equal static scales share one
+// quantisation.  At 4096 tokens the kernel moves 75 MB, 52 MB of them written, in 21 us; a
+// form with 64 columns per thread (whole 4-byte scale words, half as many threads) took 30 us.
 // ---------------------------------------------------------------------------
-constexpr int kQuantizeThreadsPerToken = kHidden / 32;  // 88
+constexpr int kQuantizeThreadsPerToken = kHidden / 32;  // 88 threads x 32 columns per token
 constexpr int kQuantizeTokensPerBlock = 4;  // large batches; decode-sized ones take one token per CTA
 constexpr int kQuantizeThreads = kQuantizeThreadsPerToken * kQuantizeTokensPerBlock;  // 352
 
@@ -380,64 +381,90 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* out) {
   out[7] = __uint_as_float(raw.w & 0xffff0000u);
 }
 
-// The per-route part of the input quantiser: `values` are this thread's 32 columns of the
-// token, `maximum` the two block maxima; route_* describe the token's eight routes.
-__device__ __forceinline__ void quantize_routes_of_token(const float (&values)[32], const float (&maximum)[2],
-                                                         int part, const int* route_row,
-                                                         const float* route_multiplier,
+// The per-route part of the input quantiser.  A thread owns kBlocks consecutive 16-value
+// blocks of the token (2 or 4): `values` are its columns, `maximum` the block maxima, `part`
+// its index along the row; route_* describe the token's eight routes.  With four blocks the
+// thread owns one whole 4-byte word of the swizzled scale layout (the launchers use two).
+template <int kBlocks>
+__device__ __forceinline__ void quantize_routes_of_token(const float (&values)[16 * kBlocks],
+                                                         const float (&maximum)[kBlocks], int part,
+                                                         const int* route_row, const float* route_multiplier,
                                                          const unsigned long long* route_scale_base,
                                                          uint8_t* __restrict__ packed,
                                                          uint8_t* __restrict__ scales) {
-  // scale groups 2*part and 2*part+1 share a 4-group word of the swizzled layout
-  const unsigned scale_offset = static_cast<unsigned>(part >> 1) * 512u + static_cast<unsigned>(part & 1) * 2u;
-#pragma unroll 2
+  static_assert(kBlocks == 2 || kBlocks == 4, "two or four blocks per thread");
+  // scale groups kBlocks*part .. +kBlocks-1 lie in one 4-group word of the swizzled layout
+  const unsigned scale_offset = kBlocks == 4
+                                    ? static_cast<unsigned>(part) * 512u
+                                    : static_cast<unsigned>(part >> 1) * 512u + static_cast<unsigned>(part & 1) * 2u;
+  // Codes and scale bytes depend on the route only through its expert's static scale, so a
+  // route whose scale equals the previous route's (bit for bit) reuses that result: with one
+  // calibration scale shared by all experts the arithmetic runs once per token, with distinct
+  // scales eight times.
+  uint32_t codes[2 * kBlocks];
+#pragma unroll
+  for (int i = 0; i < 2 * kBlocks; ++i) codes[i] = 0;
+  uint32_t scale_word = 0;
+  uint32_t previous_bits = 0;
+  bool have_previous = false;
   for (int k = 0; k < kTopK; ++k) {
     const int dst = route_row[k];
     if (dst < 0) continue;
     const float multiplier = route_multiplier[k];
-    uint32_t codes[4];
-    uint32_t scale_pair = 0;
+    if (!have_previous || __float_as_uint(multiplier) != previous_bits) {
+      have_previous = true;
+      previous_bits = __float_as_uint(multiplier);
+      scale_word = 0;
 #pragma unroll
-    for (int block = 0; block < 2; ++block) {
-      const float unrounded = __fdiv_rn(__fmul_rn(multiplier, maximum[block]), 6.0f);
-      const uint32_t scale = encode_e4m3(unrounded);
-      const float rounded = decode_e4m3(scale);
-      const float inverse = rounded == 0.0f ? 0.0f : __fdiv_rn(multiplier, rounded);
-      scale_pair |= scale << (8 * block);
+      for (int block = 0; block < kBlocks; ++block) {
+        const float unrounded = __fdiv_rn(__fmul_rn(multiplier, maximum[block]), 6.0f);
+        const uint32_t scale = encode_e4m3(unrounded);
+        const float rounded = decode_e4m3(scale);
+        const float inverse = rounded == 0.0f ? 0.0f : __fdiv_rn(multiplier, rounded);
+        scale_word |= scale << (8 * block);
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t word = 0;
+        for (int half = 0; half < 2; ++half) {
+          uint32_t word = 0;
 #pragma unroll
-        for (int pair = 0; pair < 4; ++pair)
-          word |= encode_e2m1x2(__fmul_rn(values[16 * block + 8 * half + 2 * pair], inverse),
-                                __fmul_rn(values[16 * block + 8 * half + 2 * pair + 1], inverse))
-                  << (8 * pair);
-        codes[2 * block + half] = word;
+          for (int pair = 0; pair < 4; ++pair)
+            word |= encode_e2m1x2(__fmul_rn(values[16 * block + 8 * half + 2 * pair], inverse),
+                                  __fmul_rn(values[16 * block + 8 * half + 2 * pair + 1], inverse))
+                    << (8 * pair);
+          codes[2 * block + half] = word;
+        }
       }
     }
-    reinterpret_cast<uint4*>(packed + static_cast<size_t>(dst) * (kHidden / 2))[part] =
-        make_uint4(codes[0], codes[1], codes[2], codes[3]);
-    *reinterpret_cast<uint16_t*>(scales + route_scale_base[k] + scale_offset) =
-        static_cast<uint16_t>(scale_pair);
+    uint4* row = reinterpret_cast<uint4*>(packed + static_cast<size_t>(dst) * (kHidden / 2)) + (kBlocks / 2) * part;
+    row[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+    if constexpr (kBlocks == 4) {
+      row[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+      *reinterpret_cast<uint32_t*>(scales + route_scale_base[k] + scale_offset) = scale_word;
+    } else {
+      *reinterpret_cast<uint16_t*>(scales + route_scale_base[k] + scale_offset) =
+          static_cast<uint16_t>(scale_word);
+    }
   }
 }
 
-// This thread's 32 columns of a token row and the two block maxima.
+// This thread's 16*kBlocks columns of a token row and the block maxima.
+template <int kBlocks>
 __device__ __forceinline__ void load_token_columns(const __nv_bfloat16* __restrict__ input, int token, int part,
-                                                   float (&values)[32], float (&maximum)[2]) {
-  const uint4* source = reinterpret_cast<const uint4*>(input + static_cast<size_t>(token) * kHidden) + 4 * part;
+                                                   float (&values)[16 * kBlocks], float (&maximum)[kBlocks]) {
+  const uint4* source =
+      reinterpret_cast<const uint4*>(input + static_cast<size_t>(token) * kHidden) + 2 * kBlocks * part;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) unpack_bf16x8(__ldg(source + i), values + 8 * i);
-  maximum[0] = maximum[1] = 0.0f;
+  for (int i = 0; i < 2 * kBlocks; ++i) unpack_bf16x8(__ldg(source + i), values + 8 * i);
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    maximum[0] = fmaxf(maximum[0], fabsf(values[i]));
-    maximum[1] = fmaxf(maximum[1], fabsf(values[16 + i]));
+  for (int block = 0; block < kBlocks; ++block) {
+    float m = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(values[16 * block + i]));
+    maximum[block] = m;
   }
 }
 
-template <int kTokensPerBlock>
-__global__ void __launch_bounds__(kQuantizeThreadsPerToken * kTokensPerBlock)
+template <int kTokensPerBlock, int kBlocks>
+__global__ void __launch_bounds__(kHidden / (16 * kBlocks) * kTokensPerBlock)
 quantize_input_kernel(const __nv_bfloat16* __restrict__ input, const int* __restrict__ expert_ids,
                       const float* __restrict__ in_scale_q, RoutePlan plan, int tokens,
                       uint8_t* __restrict__ packed, uint8_t* __restrict__ scales) {
@@ -465,16 +492,17 @@ quantize_input_kernel(const __nv_bfloat16* __restrict__ input, const int* __rest
     }
     route_row[slot][k] = dst;
   }
-  const int slot = threadIdx.x / kQuantizeThreadsPerToken;
-  const int part = threadIdx.x - slot * kQuantizeThreadsPerToken;  // columns [32*part, 32*part+32)
+  constexpr int threads_per_token = kHidden / (16 * kBlocks);
+  const int slot = threadIdx.x / threads_per_token;
+  const int part = threadIdx.x - slot * threads_per_token;  // columns [16*kBlocks*part, +16*kBlocks)
   const int token = blockIdx.x * kTokensPerBlock + slot;
-  float values[32];
-  float maximum[2] = {0.0f, 0.0f};
-  if (token < tokens) load_token_columns(input, token, part, values, maximum);
+  float values[16 * kBlocks];
+  float maximum[kBlocks];
+  if (token < tokens) load_token_columns<kBlocks>(input, token, part, values, maximum);
   __syncthreads();
   if (token >= tokens) return;
-  quantize_routes_of_token(values, maximum, part, route_row[slot], route_multiplier[slot],
-                           route_scale_base[slot], packed, scales);
+  quantize_routes_of_token<kBlocks>(values, maximum, part, route_row[slot], route_multiplier[slot],
+                                    route_scale_base[slot], packed, scales);
 }
 
 // Route sort and input quantiser in one launch, for batches of at most 1024 routes (decode
@@ -582,9 +610,9 @@ route_sort_quantize_small_kernel(const __nv_bfloat16* __restrict__ input, const 
   }
   float values[32];
   float maximum[2];
-  load_token_columns(input, token, tid, values, maximum);
+  load_token_columns<2>(input, token, tid, values, maximum);
   __syncthreads();
-  quantize_routes_of_token(values, maximum, tid, route_row, route_multiplier, route_scale_base, packed, scales);
+  quantize_routes_of_token<2>(values, maximum, tid, route_row, route_multiplier, route_scale_base, packed, scales);
 }
 
 void launch_route_sort_quantize_small(const void* input_bf16, const int* expert_ids, const float* in_scale_q,
@@ -600,12 +628,12 @@ void launch_quantize_input(const void* input_bf16, const int* expert_ids, const 
                            cudaStream_t stream) {
   const __nv_bfloat16* input = static_cast<const __nv_bfloat16*>(input_bf16);
   if (tokens <= 1024) {  // too few tokens to fill the SMs four at a time
-    launch_chained(quantize_input_kernel<1>, dim3(tokens), dim3(kQuantizeThreadsPerToken), 0, stream, input,
+    launch_chained(quantize_input_kernel<1, 2>, dim3(tokens), dim3(kQuantizeThreadsPerToken), 0, stream, input,
                    expert_ids, in_scale_q, plan, tokens, packed, scales);
     return;
   }
   const int blocks = (tokens + kQuantizeTokensPerBlock - 1) / kQuantizeTokensPerBlock;
-  launch_chained(quantize_input_kernel<kQuantizeTokensPerBlock>, dim3(blocks), dim3(kQuantizeThreads), 0, stream,
+  launch_chained(quantize_input_kernel<kQuantizeTokensPerBlock, 2>, dim3(blocks), dim3(kQuantizeThreads), 0, stream,
                  input, expert_ids, in_scale_q, plan, tokens, packed, scales);
 }
 

@@ -81,12 +81,17 @@ def packed(cuda_device, gm):
     return dev, host
 
 
-def make_weights(gm, packed, s1, s2, device):
+def make_weights(gm, packed, s1, s2, device, varied=False):
+    """`varied`: every expert gets its own static activation scales (s * a factor of 1 to
+    1.125 that depends on the expert), so a scale taken from the wrong expert changes bits."""
     dev, host = packed
     ones = torch.ones(EXPERTS, dtype=torch.float32, device=device)
+    index = torch.arange(EXPERTS, dtype=torch.float32, device=device)
+    f1 = ones + (index % 5) * 0.03125 if varied else ones
+    f2 = ones + (index % 3) * 0.0625 if varied else ones
     w = gm.ExpertWeights(dev["w13"], dev["w13_sf"], dev["w2"], dev["w2_sf"],
-                         (dev["g13"] * s1).contiguous(), (dev["g2"] * s2).contiguous(),
-                         (ones / s1).contiguous(), (ones / s2).contiguous())
+                         (dev["g13"] * s1 * f1).contiguous(), (dev["g2"] * s2 * f2).contiguous(),
+                         (ones / (s1 * f1)).contiguous(), (ones / (s2 * f2)).contiguous())
     hw = dict(w13=host["w13"], w13_sf=host["w13_sf"], w2=host["w2"], w2_sf=host["w2_sf"],
               alpha1=w.alpha1.cpu().numpy(), alpha2=w.alpha2.cpu().numpy(),
               in_scale_q1=w.in_scale_q1.cpu().numpy(), in_scale_q2=w.in_scale_q2.cpu().numpy())
@@ -102,6 +107,11 @@ S2 = np.float32(16.0 / (6.0 * 448.0))
 @pytest.fixture(scope="module")
 def weights(gm, packed, cuda_device):
     return make_weights(gm, packed, float(S1), float(S2), cuda_device)
+
+
+@pytest.fixture(scope="module")
+def varied_weights(gm, packed, cuda_device):
+    return make_weights(gm, packed, float(S1), float(S2), cuda_device, varied=True)
 
 
 # ---------------------------------------------------------------------------------------
@@ -405,6 +415,68 @@ def test_layer_against_oracle(gm, oracle, weights, cuda_device, tokens, kind):
     # reducing the exposed buffer by hand reproduces launch_batch bit for bit
     manual = oracle.reduce(bits(routed), rw.cpu().numpy(), want_inverse, tokens)
     assert (manual == bits(out)).all()
+
+
+@pytest.mark.parametrize("tokens", [5, 130, 300])
+def test_distinct_expert_scales_stage_by_stage(gm, oracle, varied_weights, cuda_device, tokens):
+    """Per-expert static scales that all differ: input codes and scale bytes, and the fused
+    w13 epilogue's codes and scale bytes (same GEMM output, separate kernels as the checker),
+    are those of the oracle with every expert's own scale."""
+    from gevva_b200 import runtime as rt
+    w, hw = varied_weights
+    runner = gm.Nvfp4ExpertRunner(w, tokens)
+    ids = random_ids(tokens, 900 + tokens)
+    x = hashgen.activations(tokens, HIDDEN, 77, "cpu")
+    routes = tokens * TOP_K
+    runner.launch_stages(rt.STAGE_SORT | rt.STAGE_QUANTIZE, tokens, input=x.to(cuda_device),
+                         expert_ids=torch.from_numpy(ids).to(cuda_device))
+    assert runner.last_status() == 0
+    plan = oracle.sort(ids)
+    want_codes, want_sf = oracle.quantize_sorted(bits(x), hw["in_scale_q1"], plan)
+    got_codes = runner.buffer(rt.BUF_INPUT_CODES)[: routes * HIDDEN // 2].cpu().numpy()
+    assert (got_codes.reshape(routes, -1) == want_codes).all()
+    got_sf = runner.buffer(rt.BUF_INPUT_SF)[: sf_bytes(routes, HIDDEN)].cpu().numpy()
+    groups = HIDDEN // 16
+    for expert in np.unique(ids):
+        rows = int((plan["sorted_experts"] == expert).sum())
+        base = plan["scale_rows"][expert] * groups
+        r = np.arange(rows)[:, None]
+        g = np.arange(groups)[None, :]
+        off = base + (r // 128) * (128 * groups) + (g // 4) * 512 + (r % 32) * 16 + ((r // 32) % 4) * 4 + g % 4
+        assert (got_sf[off] == want_sf[off]).all(), int(expert)
+    # fused epilogue against unfused GEMM + GeGLU kernel on the same operands
+    runner.launch_stages(rt.STAGE_W13 | rt.STAGE_GEGLU, tokens)
+    fused_codes = runner.buffer(rt.BUF_INTER_CODES)[: routes * INTER // 2].clone()
+    fused_sf = runner.buffer(rt.BUF_INTER_SF)[: sf_bytes(routes, INTER)].clone()
+    runner.launch_stages(rt.STAGE_W13 | rt.STAGE_GEGLU | rt.STAGE_UNFUSED, tokens)
+    runner.check()
+    assert torch.equal(fused_codes, runner.buffer(rt.BUF_INTER_CODES)[: routes * INTER // 2])
+    w13_out = runner.buffer(rt.BUF_W13_OUT, torch.bfloat16)[: routes * W13_OUT]
+    want_inter, want_inter_sf = oracle.geglu_quantize(bits(w13_out).reshape(routes, W13_OUT), hw["in_scale_q2"], plan)
+    assert (fused_codes.cpu().numpy().reshape(routes, -1) == want_inter).all()
+    groups = INTER // 16
+    got = fused_sf.cpu().numpy()
+    for expert in np.unique(ids):
+        rows = int((plan["sorted_experts"] == expert).sum())
+        base = plan["scale_rows"][expert] * groups
+        r = np.arange(rows)[:, None]
+        g = np.arange(groups)[None, :]
+        off = base + (r // 128) * (128 * groups) + (g // 4) * 512 + (r % 32) * 16 + ((r // 32) % 4) * 4 + g % 4
+        assert (got[off] == want_inter_sf[off]).all(), int(expert)
+
+
+def test_distinct_expert_scales_whole_layer(gm, oracle, varied_weights, cuda_device):
+    w, hw = varied_weights
+    tokens = 24
+    x = hashgen.activations(tokens, HIDDEN, 43, "cpu")
+    ids = torch.from_numpy(random_ids(tokens, 31)).to(cuda_device)
+    rw = torch.tensor([0.24, 0.19, 0.15, 0.12, 0.10, 0.08, 0.07, 0.05], device=cuda_device).repeat(tokens, 1)
+    runner = gm.Nvfp4ExpertRunner(w, tokens)
+    out = torch.empty((tokens, HIDDEN), dtype=torch.bfloat16, device=cuda_device)
+    runner.launch_batch(x.to(cuda_device), ids, rw, out, tokens)
+    runner.check()
+    want = oracle.moe_layer(bits(x), ids.cpu().numpy(), rw.cpu().numpy(), hw)
+    assert rel_l2(bf16_to_f32(bits(out)), bf16_to_f32(want)) < REL_L2
 
 
 def test_against_committed_golden_vectors(gm, packed, weights, cuda_device):

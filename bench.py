@@ -31,6 +31,10 @@ NOMINAL_FP4_TFLOPS = 9000.0
 W13_ALGORITHMIC_BYTES = 128 * (1982464 + 247808) + 32768 * (1408 + 176) + 32768 * (352 + 44)
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch (ncu capture summarised under profiles/)
 W13_DRAM_TRAFFIC_BYTES = 392952832 + 18171136
+# DRAM bytes of one layer step at 4096 tokens: the two GEMMs as measured by ncu (profiles/), the
+# quantiser (23 MB read + 52 MB written) and the reduce (185 MB read + 23 MB written) by their
+# algorithmic bytes, which their kernels move once
+LAYER_DRAM_BYTES = (392952832 + 18171136) + (156116992 + 138975744) + 75000000 + 207600000
 WORKLOAD = "prefill_4096_tokens_router_bias_N(0,0.5)"
 
 
@@ -465,6 +469,14 @@ def run_gpu(args):
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }
+        if world == 1:
+            step_seconds = elapsed_ms / args.steps * 1e-3
+            line["layer_hbm"] = {
+                "bytes_per_step": LAYER_DRAM_BYTES, "achieved_gbs": LAYER_DRAM_BYTES / step_seconds / 1e9,
+                "peak_gbs": float(peaks["hbm_gbs"]),
+                "frac": LAYER_DRAM_BYTES / step_seconds / 1e9 / float(peaks["hbm_gbs"]),
+                "note": "whole layer step against the measured copy bandwidth: at 4096 tokens the layer "
+                        "moves about 1 GB for 390 GFLOP, below the machine balance of the FP4 tensor pipe"}
         if world == 1 and not args.no_library_compare:
             library = library_nvfp4_gemm_tflops(device)
             if library:

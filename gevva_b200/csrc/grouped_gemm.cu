@@ -357,12 +357,11 @@ __device__ __forceinline__ uint32_t geglu_block(const uint32_t (&up)[16], const 
   return quantize_block16(values, multiplier, codes_lo, codes_hi);
 }
 
-// Work distribution.  Items are numbered with the expensive ones first (in the fused wide
-// form the half-filled last item of every row tile comes after all full ones) and dealt to
-// the persistent CTAs in snake order: round r goes to CTA b as item r*G + b for even r and
-// r*G + (G-1-b) for odd r.  With equal-cost items this is plain round-robin; with the cheap
-// items at the end it is the longest-first rule, which is what balances a decode-sized
-// launch (768 items of two sizes over 148 CTAs).
+// Work distribution.  Items are dealt to the persistent CTAs in snake order: round r goes to
+// CTA b as item r*G + b for even r and r*G + (G-1-b) for odd r.  In a short launch of the fused
+// wide form (at most eight rounds) the items are numbered with the expensive ones first, the
+// half-filled last item of every row tile after all full ones: that is the longest-first
+// rule, which is what balances a decode-sized launch (768 items of two sizes over 148 CTAs).
 struct WorkItem {
   int m_tile;
   int n_tile;
@@ -375,7 +374,9 @@ __device__ __forceinline__ bool work_item(int round, int total_items, int m_tile
   const int slot = (round & 1) ? grid - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
   const int index = round * grid + slot;
   if (index >= total_items) return false;
-  if (kMode == kGeglu && kN == 256) {
+  // Cost order only where balance decides (a few rounds); a long launch keeps the items of a
+  // row tile together so that its activation tile is still in L2 for the last one.
+  if (kMode == kGeglu && kN == 256 && total_items <= 8 * grid) {
     const int full = m_tiles * (n_tiles - 1);
     if (index < full) {
       item.m_tile = index / (n_tiles - 1);

@@ -30,11 +30,11 @@ NOMINAL_FP4_TFLOPS = 9000.0
 # fused w13 launch at 4096 tokens: weights + weight scales + operand codes/scales + output codes/scales
 W13_ALGORITHMIC_BYTES = 128 * (1982464 + 247808) + 32768 * (1408 + 176) + 32768 * (352 + 44)
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch (ncu capture summarised under profiles/)
-W13_DRAM_TRAFFIC_BYTES = 392952832 + 18171136
+W13_DRAM_TRAFFIC_BYTES = 342586368 + 12649216
 # DRAM bytes of one layer step at 4096 tokens: the two GEMMs as measured by ncu (profiles/), the
 # quantiser (23 MB read + 52 MB written) and the reduce (185 MB read + 23 MB written) by their
 # algorithmic bytes, which their kernels move once
-LAYER_DRAM_BYTES = (392952832 + 18171136) + (156116992 + 138975744) + 75000000 + 207600000
+LAYER_DRAM_BYTES = (342586368 + 12649216) + (156119808 + 134346240) + 75000000 + 207600000
 WORKLOAD = "prefill_4096_tokens_router_bias_N(0,0.5)"
 
 

@@ -529,11 +529,12 @@ def test_bounded_wait_times_out_and_context_survives(gm, weights, cuda_device):
     assert torch.isfinite(out.float()).all()
 
 
-def test_full_size_properties(gm, weights, cuda_device):
-    """4096 tokens (the prefill configuration's size): properties that need no oracle."""
+@pytest.mark.parametrize("tokens", [4096, 16384, 20000])
+def test_full_size_properties(gm, weights, cuda_device, tokens):
+    """4096 and 16384 tokens (the prefill configurations' sizes) and 20000 (more route chunks
+    than SMs, so the route sort takes its three-launch form): properties that need no oracle."""
     from gevva_b200 import runtime as rt
     w, _ = weights
-    tokens = 4096
     x = hashgen.activations(tokens, HIDDEN, 51, cuda_device)
     router_w = (hashgen.hash_uniform(EXPERTS * HIDDEN, 5, cuda_device) * 0.0346).view(EXPERTS, HIDDEN)
     bias = hashgen.hash_uniform(EXPERTS, 6, cuda_device) * 0.9

@@ -439,7 +439,7 @@ def run_gpu(args):
         # our kernels per step.  Single GPU: route, sort, quantise, w13 (+GeGLU), w2, reduce.
         # Expert parallel: route, sort, publish counts, 3 barriers, send bases, dispatch, receive
         # plan, scale swizzle, row destinations, w13, w2, reduce.
-        launches_per_step = 6 if world == 1 else 15
+        launches_per_step = 6 if world == 1 else 14
         line = {
             "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),

@@ -321,9 +321,17 @@ def run_gpu(args):
             print(json.dumps({"profile_decode_tokens": args.profile_decode, "steps": 6}), flush=True)
         return
     if world > 1:
-        from gevva_b200.expert_parallel import ExpertParallelRunner, local_expert_weights
-        layer.ep = ExpertParallelRunner(local_expert_weights(layer.weights, rank, world),
-                                        layer.weights.in_scale_q1, TOKENS)
+        from gevva_b200.expert_parallel import (ExpertParallelRunner, balanced_placement,
+                                                local_expert_weights)
+        # Experts are placed by load observed on a calibration batch (other tokens than the timed
+        # ones, same router): most loaded first, each to the least loaded rank with a free slot.
+        calibration = layer.inputs(TOKENS, seed=2000 + rank)
+        _, calibration_ids = gevva_b200.route_128_top8(layer.logits(calibration), layer.expert_scale)
+        counts = torch.bincount(calibration_ids.reshape(-1).long(), minlength=EXPERTS)
+        dist.all_reduce(counts)
+        placement = balanced_placement(counts.tolist(), world)
+        layer.ep = ExpertParallelRunner(local_expert_weights(layer.weights, rank, world, placement),
+                                        layer.weights.in_scale_q1, TOKENS, placement=placement)
     out = torch.empty_like(x)
     weights = torch.empty((TOKENS, TOP_K), dtype=torch.float32, device=device)
     ids = torch.empty((TOKENS, TOP_K), dtype=torch.int32, device=device)
@@ -449,7 +457,8 @@ def run_gpu(args):
             "config": {"workload": WORKLOAD, "tokens_per_gpu": TOKENS, "experts": EXPERTS,
                        "top_k": TOP_K, "hidden": HIDDEN, "expert_width": INTER,
                        "parallelism": "single GPU" if world == 1 else
-                       f"expert parallel x{world}: 128/{world} experts per GPU, tokens data-parallel, "
+                       f"expert parallel x{world}: 128/{world} experts per GPU placed by the load of a "
+                       "calibration batch, tokens data-parallel, "
                        "dispatch/combine by stores into peer memory over NVLink",
                        "l2": "inputs larger than L2: 428 MB of expert weights stream every step"},
             "layer_tflops": FLOP_PER_TOKEN * TOKENS / (elapsed_ms / args.steps * 1e-3) / 1e12,

@@ -420,6 +420,18 @@ int gevva_moe_ep_create(gevva_moe_ep** out, const gevva_moe_weights* local_weigh
   int* remap = carve(kExperts);
   int host_remap[kExperts];
   for (int x = 0; x < kExperts; ++x) host_remap[x] = (x % world) * el + x / world;
+  if (config->placement) {
+    bool taken[kExperts] = {};
+    for (int x = 0; x < kExperts; ++x) {
+      const int v = config->placement[x];
+      if (v < 0 || v >= kExperts || taken[v]) {  // not a permutation
+        gevva_moe_ep_destroy(ep);
+        return GEVVA_MOE_BAD_ARGUMENT;
+      }
+      taken[v] = true;
+      host_remap[x] = v;
+    }
+  }
   e = cudaMemcpy(remap, host_remap, sizeof(host_remap), cudaMemcpyHostToDevice);
   ep->dev.remap = remap;
   sp.remap = remap;

@@ -10,8 +10,11 @@ EXPERTS = 128
 TILE = 128
 
 
-def remap(world):
-    """expert id e -> virtual id v: owner e % world, local index e // world."""
+def remap(world, placement=None):
+    """expert id e -> virtual id v = owner * EL + local index: by default owner e % world and
+    local index e // world, else the given placement table."""
+    if placement is not None:
+        return np.asarray(placement, dtype=np.int64)
     e = np.arange(EXPERTS)
     return (e % world) * (EXPERTS // world) + e // world
 

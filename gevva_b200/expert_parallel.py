@@ -19,12 +19,44 @@ class _EpConfig(ctypes.Structure):
                 ("peer_recv_sf", ctypes.POINTER(ctypes.c_void_p)),
                 ("peer_combine", ctypes.POINTER(ctypes.c_void_p)),
                 ("peer_counts", ctypes.POINTER(ctypes.c_void_p)),
-                ("peer_flags", ctypes.POINTER(ctypes.c_void_p))]
+                ("peer_flags", ctypes.POINTER(ctypes.c_void_p)),
+                ("placement", ctypes.POINTER(ctypes.c_int))]
 
 
-def local_expert_weights(full: ExpertWeights, rank: int, world: int) -> ExpertWeights:
-    """This rank's shard: experts rank, rank+world, ... (local index e // world)."""
-    pick = lambda t: t[rank::world].contiguous()
+def strided_placement(world):
+    """placement[e] = owner * (128/world) + local index: expert e on rank e % world at e // world."""
+    el = EXPERTS // world
+    return [(e % world) * el + e // world for e in range(EXPERTS)]
+
+
+def balanced_placement(counts, world):
+    """Placement from observed per-expert route counts (e.g. of a calibration batch): experts in
+    order of decreasing count, each to the least loaded rank that still has a free slot
+    (longest-processing-time rule).  Deterministic, so every rank computes the same table."""
+    el = EXPERTS // world
+    counts = [int(c) for c in counts]
+    assert len(counts) == EXPERTS
+    load = [0] * world
+    members = [[] for _ in range(world)]
+    for e in sorted(range(EXPERTS), key=lambda i: (-counts[i], i)):
+        rank = min((r for r in range(world) if len(members[r]) < el), key=lambda r: (load[r], r))
+        members[rank].append(e)
+        load[rank] += counts[e]
+    placement = [0] * EXPERTS
+    for rank in range(world):
+        for index, e in enumerate(sorted(members[rank])):
+            placement[e] = rank * el + index
+    return placement
+
+
+def local_expert_weights(full: ExpertWeights, rank: int, world: int, placement=None) -> ExpertWeights:
+    """This rank's shard in local-index order: by default experts rank, rank+world, ...;
+    with a placement table the experts e with placement[e] // (128/world) == rank."""
+    el = EXPERTS // world
+    placement = placement or strided_placement(world)
+    order = sorted((e for e in range(EXPERTS) if placement[e] // el == rank), key=lambda e: placement[e])
+    index = torch.tensor(order, dtype=torch.long, device=full.w13.device)
+    pick = lambda t: t.index_select(0, index).contiguous()
     return ExpertWeights(pick(full.w13), pick(full.w13_sf), pick(full.w2), pick(full.w2_sf),
                          pick(full.alpha1), pick(full.alpha2), pick(full.in_scale_q1),
                          pick(full.in_scale_q2))
@@ -32,7 +64,7 @@ def local_expert_weights(full: ExpertWeights, rank: int, world: int) -> ExpertWe
 
 class ExpertParallelRunner:
     def __init__(self, local_weights: ExpertWeights, in_scale_q1_global: torch.Tensor, max_tokens: int,
-                 group=None):
+                 group=None, placement=None):
         import torch.distributed._symmetric_memory as symm_mem
         group = group or dist.group.WORLD
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
@@ -66,7 +98,8 @@ class ExpertParallelRunner:
                            ctypes.cast(arrays[2], ctypes.POINTER(ctypes.c_void_p)),
                            ctypes.cast(arrays[3], ctypes.POINTER(ctypes.c_void_p)),
                            ctypes.cast(arrays[0], ctypes.POINTER(ctypes.c_void_p)),
-                           ctypes.cast(arrays[4], ctypes.POINTER(ctypes.c_void_p)))
+                           ctypes.cast(arrays[4], ctypes.POINTER(ctypes.c_void_p)),
+                           (ctypes.c_int * EXPERTS)(*placement) if placement is not None else None)
         lib = library()
         vp = ctypes.c_void_p
         lib.gevva_moe_ep_create.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(_Weights), vp,

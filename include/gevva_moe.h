@@ -197,6 +197,10 @@ typedef struct {
   void* const* peer_combine;
   int* const* peer_counts;
   int* const* peer_flags; /* i32 [world] per rank, zero-initialised: flags of gevva_moe_ep_barrier */
+  /* Optional HOST array [128], the same on every rank: placement[e] = owner rank * (128/world) +
+   * local index of expert e on its owner (a permutation of 0..127; local_weights then holds the
+   * rank's experts in local-index order).  NULL: expert e on rank e % world at index e / world. */
+  const int* placement;
 } gevva_moe_ep_config;
 
 int gevva_moe_ep_create(gevva_moe_ep** out, const gevva_moe_weights* local_weights,

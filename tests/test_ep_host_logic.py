@@ -78,3 +78,20 @@ def test_dispatch_and_combine_bookkeeping(tmp_path, world, tokens):
     port = 29650 + world
     mp.spawn(_worker, args=(world, port, tokens, str(tmp_path)), nprocs=world, join=True)
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+
+
+def test_balanced_placement_is_a_permutation_and_balances():
+    from gevva_b200 import ep_plan
+    from gevva_b200.expert_parallel import balanced_placement, strided_placement
+    rng = np.random.default_rng(3)
+    counts = (1000 * rng.pareto(1.2, EXPERTS)).astype(np.int64) + 1
+    for world in (1, 2, 4, 8):
+        el = EXPERTS // world
+        placement = balanced_placement(counts.tolist(), world)
+        assert sorted(placement) == list(range(EXPERTS))
+        load = lambda table: max(sum(int(counts[e]) for e in range(EXPERTS) if table[e] // el == r)
+                                 for r in range(world))
+        assert load(placement) <= load(strided_placement(world))
+        assert (ep_plan.remap(world, placement) == np.asarray(placement)).all()
+        assert (ep_plan.remap(world) == np.asarray(strided_placement(world))).all()
+

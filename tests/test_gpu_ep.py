@@ -65,6 +65,19 @@ def _worker(rank, world, port, result_dir):
             assert int(total[0]) == int(total[1]), "rows received != routes sent"
             assert torch.equal(got, want), f"rank {rank} round {round_index}: " \
                 f"{(got != want).sum().item()} of {got.numel()} elements differ"
+        # the same batch with experts placed by observed load instead of e % world
+        from gevva_b200.expert_parallel import balanced_placement
+        counts = torch.bincount(ids.reshape(-1).long(), minlength=EXPERTS)
+        dist.all_reduce(counts)
+        placement = balanced_placement(counts.tolist(), world)
+        assert placement != [(e % world) * (EXPERTS // world) + e // world for e in range(EXPERTS)]
+        placed = ExpertParallelRunner(local_expert_weights(full, rank, world, placement), full.in_scale_q1, 512,
+                                      placement=placement)
+        got = torch.empty_like(x)
+        placed.launch_batch(x, ids, rw, got, tokens)
+        status, rows = placed.status()
+        assert status == 0, status
+        assert torch.equal(got, want), f"rank {rank} balanced placement: {(got != want).sum().item()} differ"
         open(os.path.join(result_dir, f"ok{rank}"), "w").write("ok")
     finally:
         dist.destroy_process_group()

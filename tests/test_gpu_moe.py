@@ -231,7 +231,8 @@ def test_capacity_and_argument_errors(gm, weights, cuda_device):
         gm.Nvfp4ExpertRunner(weights[0], 0)
 
 
-@pytest.mark.parametrize("tokens,kind", [(1, "random"), (16, "random"), (129, "skewed"), (300, "random")])
+@pytest.mark.parametrize("tokens,kind", [(1, "random"), (16, "random"), (128, "skewed"), (129, "skewed"),
+                                         (300, "random")])
 def test_input_quantiser_bit_exact(gm, oracle, weights, big_runner, cuda_device, tokens, kind):
     from gevva_b200 import runtime as rt
     ids = random_ids(tokens, 7 + tokens) if kind == "random" else skewed_ids(tokens)

@@ -2,9 +2,10 @@
 // node, tokens data-parallel, rows exchanged by stores into peer memory over NVLink.
 // The reference is single-GPU and has no counterpart.
 //
-// Placement.  Expert e lives on rank e % world as local expert e / world; the
-// "virtual" id v = (e % world) * EL + e / world (EL = 128 / world) orders experts by
-// owning rank, so a sender's sorted routes are contiguous per destination.
+// Placement.  By default expert e lives on rank e % world as local expert e / world; a
+// caller's table may place experts otherwise (e.g. by observed load).  Either way the
+// "virtual" id v = owner * EL + local index (EL = 128 / world) orders experts by owning
+// rank, so a sender's sorted routes are contiguous per destination.
 //
 // One step, on every rank (the caller places a cross-rank barrier where marked):
 //   1. route_sort   sort local routes by v; store this rank's 128 counts into
@@ -13,9 +14,11 @@
 //                   rank's rows land in the owner's receive buffer; quantise each
 //                   route with its expert's static scale and store codes and scale
 //                   rows straight into the owner's receive buffers
-//                   (1584 B per route instead of 5632 B of bf16)     -- barrier --
-//   3. compute      build the group geometry of the local experts from the same
-//                   matrix; w13 (+GeGLU+requantise) and w2 grouped GEMMs; the w2
+//                   (1584 B per route instead of 5632 B of bf16); then, from the same
+//                   matrix, the group geometry of the local experts and the address
+//                   of every result row                              -- barrier --
+//   3. compute      received scale rows into the MMA layout; w13 (+GeGLU+requantise)
+//                   and w2 grouped GEMMs; the w2
 //                   epilogue stores every result row straight into its source
 //                   rank's combine buffer at the source's own sorted position
 //                                                                    -- barrier --
@@ -497,16 +500,19 @@ int gevva_moe_ep_dispatch(gevva_moe_ep* ep, const void* in, const int* ids, int 
   gv::ep_dispatch_kernel<<<(tokens + gv::kDispatchTokensPerBlock - 1) / gv::kDispatchTokensPerBlock,
                           gv::kDispatchThreads, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(in), ids, ep->in_scale_q1_global, ep->dev, ep->send_plan, tokens);
+  // The receive-side geometry and the combine address table depend on the count matrix only,
+  // so they are computed here, while other ranks' rows are still arriving, rather than after
+  // the barrier that precedes gevva_moe_ep_compute.
+  gv::ep_receive_plan_kernel<<<1, kExperts, 0, stream>>>(ep->dev, ep->receive_plan);
+  gv::ep_row_destinations_kernel<<<ep->sm_count * 2, 256, 0, stream>>>(ep->dev, ep->receive_plan,
+                                                                        ep->row_dest);
   return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;
 }
 
 int gevva_moe_ep_compute(gevva_moe_ep* ep, gevva_stream_t stream) {
   if (!ep) return GEVVA_MOE_BAD_ARGUMENT;
-  gv::ep_receive_plan_kernel<<<1, kExperts, 0, stream>>>(ep->dev, ep->receive_plan);
   gv::ep_swizzle_scales_kernel<<<ep->sm_count * 4, 256, 0, stream>>>(
       ep->dev.peer_scales[ep->dev.rank], ep->dev, ep->receive_plan, ep->input_sf);
-  gv::ep_row_destinations_kernel<<<ep->sm_count * 2, 256, 0, stream>>>(ep->dev, ep->receive_plan,
-                                                                        ep->row_dest);
   gv::launch_grouped_gemm(ep->w13, ep->receive_plan, ep->sm_count, stream);
   gv::launch_grouped_gemm(ep->w2, ep->receive_plan, ep->sm_count, stream);
   return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;

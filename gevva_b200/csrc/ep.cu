@@ -218,7 +218,7 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ input, const int* __restric
 }
 
 // ---- 3a: group geometry of the local experts ---------------------------------------
-__global__ void __launch_bounds__(kExperts) ep_receive_plan_kernel(EpDevice ep, RoutePlan plan) {
+__global__ void __launch_bounds__(kExperts) ep_receive_plan_kernel(EpDevice ep, RoutePlan plan, int* split) {
   __shared__ int scan_scratch[16];
   const int le = threadIdx.x;
   const int el = ep.local_experts;
@@ -235,6 +235,24 @@ __global__ void __launch_bounds__(kExperts) ep_receive_plan_kernel(EpDevice ep, 
     int offset = 0;
     for (int u = 0; u < v; ++u) offset += ep.counts[s * kExperts + u];
     ep.source_offsets[index] = offset;
+  }
+  // Two halves of the tile list, cut at the expert boundary nearest the middle:
+  // split = {first tile, tile count} of each half.
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int total = plan.num_m_tiles[0];
+    int cut = total;
+    for (int e = 1; e < el; ++e) {
+      const int begin = plan.scale_row_offsets[e] / kTileM;
+      if (2 * begin >= total) {
+        cut = begin;
+        break;
+      }
+    }
+    split[0] = 0;
+    split[1] = cut;
+    split[2] = cut;
+    split[3] = total - cut;
   }
 }
 
@@ -327,6 +345,11 @@ struct gevva_moe_ep {
   uint8_t* inter_sf = nullptr;
   unsigned long long* row_dest = nullptr;
   uint8_t* w13_sf_tiled = nullptr;
+  // the compute phase runs the local experts in two halves so that the NVLink-bound w2 of the
+  // first half overlaps the w13 of the second: a side stream and two events order them
+  int* split = nullptr;  // device [4]: first tile and tile count of each half
+  cudaStream_t side = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
 };
 
 extern "C" {
@@ -339,6 +362,9 @@ void gevva_moe_ep_destroy(gevva_moe_ep* ep) {
   cudaFree(ep->inter_sf);
   cudaFree(ep->row_dest);
   cudaFree(ep->w13_sf_tiled);
+  if (ep->side) cudaStreamDestroy(ep->side);
+  if (ep->fork) cudaEventDestroy(ep->fork);
+  if (ep->join) cudaEventDestroy(ep->join);
   delete ep;
 }
 
@@ -359,6 +385,12 @@ int gevva_moe_ep_create(gevva_moe_ep** out, const gevva_moe_weights* local_weigh
   if (!ep) return GEVVA_MOE_CUDA_ERROR;
   const int el = kExperts / world;
   ep->sm_count = prop.multiProcessorCount;
+  if (cudaStreamCreateWithFlags(&ep->side, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreateWithFlags(&ep->fork, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&ep->join, cudaEventDisableTiming) != cudaSuccess) {
+    gevva_moe_ep_destroy(ep);
+    return GEVVA_MOE_CUDA_ERROR;
+  }
   ep->max_tokens = config->max_tokens;
   ep->capacity_rows = config->recv_capacity_rows;
   ep->in_scale_q1_global = in_scale_q1_global;
@@ -410,6 +442,7 @@ int gevva_moe_ep_create(gevva_moe_ep** out, const gevva_moe_weights* local_weigh
   sp.chunk_hist = carve(chunks * kExperts);
   sp.status = carve(1);
   sp.sync = carve(2);  // from the 64 spare ints
+  ep->split = carve(4);
   gv::RoutePlan& rp = ep->receive_plan;
   rp.expert_offsets = carve(kExperts + 1);
   rp.scale_row_offsets = carve(kExperts + 1);
@@ -503,7 +536,7 @@ int gevva_moe_ep_dispatch(gevva_moe_ep* ep, const void* in, const int* ids, int 
   // The receive-side geometry and the combine address table depend on the count matrix only,
   // so they are computed here, while other ranks' rows are still arriving, rather than after
   // the barrier that precedes gevva_moe_ep_compute.
-  gv::ep_receive_plan_kernel<<<1, kExperts, 0, stream>>>(ep->dev, ep->receive_plan);
+  gv::ep_receive_plan_kernel<<<1, kExperts, 0, stream>>>(ep->dev, ep->receive_plan, ep->split);
   gv::ep_row_destinations_kernel<<<ep->sm_count * 2, 256, 0, stream>>>(ep->dev, ep->receive_plan,
                                                                         ep->row_dest);
   return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;
@@ -513,8 +546,26 @@ int gevva_moe_ep_compute(gevva_moe_ep* ep, gevva_stream_t stream) {
   if (!ep) return GEVVA_MOE_BAD_ARGUMENT;
   gv::ep_swizzle_scales_kernel<<<ep->sm_count * 4, 256, 0, stream>>>(
       ep->dev.peer_scales[ep->dev.rank], ep->dev, ep->receive_plan, ep->input_sf);
-  gv::launch_grouped_gemm(ep->w13, ep->receive_plan, ep->sm_count, stream);
-  gv::launch_grouped_gemm(ep->w2, ep->receive_plan, ep->sm_count, stream);
+  // First half: w13 on every SM, then w2 (bound by the NVLink stores of its epilogue) on a
+  // part of the SMs of a side stream while the second half's w13 takes the others.
+  gv::RoutePlan first = ep->receive_plan, second = ep->receive_plan;
+  first.tile_first = ep->split;
+  first.num_m_tiles = ep->split + 1;
+  second.tile_first = ep->split + 2;
+  second.num_m_tiles = ep->split + 3;
+  const int side_sms = ep->sm_count >= 128 ? 64 : ep->sm_count / 2;
+  gv::launch_grouped_gemm(ep->w13, first, ep->sm_count, stream);
+  cudaEventRecord(ep->fork, stream);
+  cudaStreamWaitEvent(ep->side, ep->fork, 0);
+  gv::launch_grouped_gemm(ep->w2, first, side_sms, ep->side);
+  cudaEventRecord(ep->join, ep->side);
+  gv::launch_grouped_gemm(ep->w13, second, ep->sm_count - side_sms, stream);
+  // launched the ordinary way: its CTAs must not take SMs (and wait there) before the second
+  // half's w13 has ended, or the first half's w2 would be left without room
+  gv::GemmOperands last = ep->w2;
+  last.serial_launch = true;
+  gv::launch_grouped_gemm(last, second, ep->sm_count, stream);
+  cudaStreamWaitEvent(stream, ep->join, 0);
   return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;
 }
 

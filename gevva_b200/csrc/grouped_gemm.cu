@@ -138,6 +138,7 @@ struct GemmParams {
   const int* expert_offsets;
   const int* scale_row_offsets;
   const int* num_m_tiles;
+  const int* tile_first;     // optional: first row tile of this launch
   int* status;
   int n_out;
   int n_tiles;      // work items per row tile
@@ -369,7 +370,7 @@ struct WorkItem {
 
 template <int kMode, int kN>
 __device__ __forceinline__ bool work_item(int round, int total_items, int m_tiles, int n_tiles,
-                                          WorkItem& item) {
+                                          int tile_first, WorkItem& item) {
   const int grid = static_cast<int>(gridDim.x);
   const int slot = (round & 1) ? grid - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
   const int index = round * grid + slot;
@@ -389,6 +390,7 @@ __device__ __forceinline__ bool work_item(int round, int total_items, int m_tile
     item.m_tile = index / n_tiles;
     item.n_tile = index - item.m_tile * n_tiles;
   }
+  item.m_tile += tile_first;
   return true;
 }
 
@@ -446,6 +448,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   grid_dependency_wait();
 
   const int m_tiles = p.num_m_tiles[0];
+  const int tile_first = p.tile_first ? p.tile_first[0] : 0;
   const int total_items = m_tiles * p.n_tiles;
   const int rounds = (total_items + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
 
@@ -458,7 +461,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     bool ok = true;
     for (int round = 0; ok && round < rounds; ++round) {
       WorkItem item;
-      if (!work_item<kMode, kN>(round, total_items, m_tiles, p.n_tiles, item)) continue;
+      if (!work_item<kMode, kN>(round, total_items, m_tiles, p.n_tiles, tile_first, item)) continue;
       const int m_tile = item.m_tile;
       const int n_tile = item.n_tile;
       const int expert = p.tile_expert[m_tile];
@@ -579,7 +582,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     const bool leader = elect_one();
     for (int round = 0; round < rounds; ++round) {
       WorkItem item;
-      if (!work_item<kMode, kN>(round, total_items, m_tiles, p.n_tiles, item)) continue;
+      if (!work_item<kMode, kN>(round, total_items, m_tiles, p.n_tiles, tile_first, item)) continue;
       if (!__all_sync(0xffffffffu,
                       wait_or_abort<false>(&smem->acc_empty[acc_stage], acc_phase ^ 1u, smem, p.status)))
         break;
@@ -652,7 +655,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     uint8_t* staging = smem->staging[quarter];
     for (int round = 0; round < rounds; ++round) {
       WorkItem item;
-      if (!work_item<kMode, kN>(round, total_items, m_tiles, p.n_tiles, item)) continue;
+      if (!work_item<kMode, kN>(round, total_items, m_tiles, p.n_tiles, tile_first, item)) continue;
       const int m_tile = item.m_tile;
       const int n_tile = item.n_tile;
       const int expert = p.tile_expert[m_tile];
@@ -796,6 +799,11 @@ template <int kMode, int kAtoms, int kN> cudaError_t raise_smem_limit() {
 
 template <int kMode, int kN>
 void launch_variant(const GemmOperands& op, const GemmParams& p, int sm_count, cudaStream_t stream) {
+  if (op.serial_launch) {
+    grouped_nvfp4_gemm_kernel<kMode, 1, kN><<<sm_count, kGemmThreads, gemm_smem_bytes<kMode, 1, kN>(), stream>>>(
+        op.map_a, op.map_a32, op.map_b, op.map_b64, p);
+    return;
+  }
   launch_chained(grouped_nvfp4_gemm_kernel<kMode, 1, kN>, dim3(sm_count), dim3(kGemmThreads),
                  gemm_smem_bytes<kMode, 1, kN>(), stream, op.map_a, op.map_a32, op.map_b, op.map_b64, p);
 }
@@ -835,6 +843,7 @@ void launch_grouped_gemm(const GemmOperands& op, const RoutePlan& plan, int sm_c
   p.expert_offsets = plan.expert_offsets;
   p.scale_row_offsets = plan.scale_row_offsets;
   p.num_m_tiles = plan.num_m_tiles;
+  p.tile_first = plan.tile_first;
   p.status = plan.status;
   p.n_out = op.n_out;
   const int k_bytes = op.fp8 ? op.k_in : op.k_in / 2;

@@ -18,6 +18,7 @@ struct RoutePlan {
   int* scale_row_offsets;  // [129] first scale-factor row (128-row padded) of each expert
   int* tile_expert;        // [R/128 + 128] expert of each 128-row tile
   int* num_m_tiles;        // [1]
+  const int* tile_first;   // optional [1]: a GEMM launch covers tiles [tile_first, tile_first + num_m_tiles)
   int* chunk_hist;         // [ceil(R/1024) * 128] scratch of the multi-block sort
   int* status;             // [1]   device status word (gv::Status)
   const int* remap;        // optional [128]: sort key = remap[expert id] (expert-parallel placement)
@@ -67,6 +68,7 @@ struct GemmOperands {
   // re-tiled copy made by launch_retile_w13_scales, map_b64 serves the last, half-filled item
   // of each row tile, and the results go to the w2 operand buffers below.
   bool fused_geglu;
+  bool serial_launch;         // launch the ordinary way: no start before the stream's previous kernel ends
   bool fp8;                   // dense E4M3 x E4M3 (no block scales); k_in counts bytes = elements
   uint8_t* next_codes;        // [row capacity, 352]
   uint8_t* next_scales;       // scale regions of the w2 operand

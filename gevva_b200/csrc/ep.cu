@@ -382,6 +382,17 @@ int gevva_moe_ep_create(gevva_moe_ep** out, const gevva_moe_weights* local_weigh
   if (world < 1 || world > gv::kMaxWorld || kExperts % world != 0 || rank < 0 || rank >= world ||
       config->max_tokens < 1)
     return GEVVA_MOE_BAD_ARGUMENT;
+  // Nothing on the device bounds a receive row against the capacity, so the capacity must cover
+  // the case in which every route of every rank lands on this one.
+  if (config->recv_capacity_rows < static_cast<size_t>(world) * kTopK * static_cast<size_t>(config->max_tokens))
+    return GEVVA_MOE_BAD_ARGUMENT;
+  if (!config->peer_recv_codes || !config->peer_recv_sf || !config->peer_combine || !config->peer_counts ||
+      !config->peer_flags)
+    return GEVVA_MOE_BAD_ARGUMENT;
+  for (int d = 0; d < world; ++d)
+    if (!config->peer_recv_codes[d] || !config->peer_recv_sf[d] || !config->peer_combine[d] ||
+        !config->peer_counts[d] || !config->peer_flags[d])
+      return GEVVA_MOE_BAD_ARGUMENT;
   if (gv::prepare_grouped_gemm() != 0) return GEVVA_MOE_CUDA_ERROR;
   cudaDeviceProp prop;
   int device = 0;

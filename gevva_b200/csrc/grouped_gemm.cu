@@ -104,10 +104,6 @@ struct alignas(1024) GemmSmem {
   uint32_t tmem_base;
   volatile int abort;
   alignas(16) float erf_table[GV_ERF_TABLE_FLOATS];
-#if defined(GV_TRACE)
-  unsigned int trace[3][768];
-  int trace_count[3];
-#endif
 };
 
 template <int kMode, int kAtoms, int kN> constexpr size_t gemm_smem_bytes() {
@@ -276,20 +272,6 @@ __device__ __forceinline__ void issue_k_block_fp8(uint32_t tmem_acc, uint32_t a_
 #undef GV_PROLOGUE8
 }
 
-#if defined(GV_TRACE)
-// Debug build only: cycle stamps of CTA 0's roles, kept in shared memory while the kernel
-// runs (a stamp costs one shared store) and copied out at the end; gv_trace_read() reads them.
-constexpr int kTraceDepth = 768;
-__device__ unsigned int g_trace[3][kTraceDepth];
-__device__ int g_trace_count[3];
-#define GV_STAMP(role)                                                              \
-  do {                                                                              \
-    if (blockIdx.x == 0 && smem->trace_count[role] < kTraceDepth)                   \
-      smem->trace[role][smem->trace_count[role]++] = static_cast<unsigned>(clock64()); \
-  } while (0)
-#else
-#define GV_STAMP(role) do {} while (0)
-#endif
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
@@ -424,9 +406,6 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       mbar_init(&smem->acc_empty[s], kEpilogueThreads);
     }
     smem->abort = 0;
-#if defined(GV_TRACE)
-    smem->trace_count[0] = smem->trace_count[1] = smem->trace_count[2] = 0;
-#endif
     fence_barrier_init();
     prefetch_tensor_map(&map_a);
     prefetch_tensor_map(&map_a32);
@@ -493,7 +472,6 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         ok = __all_sync(0xffffffffu, wait_or_abort<true>(&smem->empty[stage], phase ^ 1u, smem, p.status));
         if (!ok) break;
         if (elect_one()) {
-          if (!weight_side) GV_STAMP(0);
           const int atoms = p.k_blocks - kb < kAtoms ? p.k_blocks - kb : kAtoms;
           const bool has_last = kb + atoms == p.k_blocks;
           const uint32_t sf_bytes =
@@ -538,7 +516,6 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                              sf_bytes, &smem->full[stage]);
             }
           }
-          if (!weight_side) GV_STAMP(0);
         }
         __syncwarp();
         ++issued;
@@ -603,7 +580,6 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         const uint32_t sfb_lo = sfb_lo0 + static_cast<uint32_t>(stage) * (kAtoms * Shape::kWeightSfBytes >> 4);
         const uint32_t tmem_sf = tmem_base + kSfColumn + Shape::kSfColumns * kAtoms * stage;
         if (leader) {
-          GV_STAMP(1);
 #pragma unroll
           for (int atom = 0; atom < kAtoms; ++atom) {
             const int k = kb + atom;
@@ -631,7 +607,6 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           }
           tc_commit(&smem->empty[stage]);  // frees the stage once these MMAs have read it
           if (kb + kAtoms >= p.k_blocks) tc_commit(&smem->acc_full[acc_stage]);
-          GV_STAMP(1);
         }
         if (++stage == kStages) {
           stage = 0;
@@ -665,7 +640,6 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       const float alpha = p.alpha[expert];
       if (!wait_or_abort<true>(&smem->acc_full[acc_stage], acc_phase, smem, p.status)) break;
       tc_fence_after_sync();
-      if (threadIdx.x == 64) GV_STAMP(2);
       const int row_local = quarter * 32 + lane;
       const uint32_t tmem_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                 static_cast<uint32_t>(acc_stage * kTileN);
@@ -719,7 +693,6 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
               static_cast<uint16_t>(scale0 | (scale1 << 8));
         }
       }
-      if (threadIdx.x == 64) GV_STAMP(2);
       if (++acc_stage == kAccStages) {
         acc_stage = 0;
         acc_phase ^= 1u;
@@ -729,15 +702,6 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
 
   tc_fence_before_sync();
   __syncthreads();
-#if defined(GV_TRACE)
-  if (blockIdx.x == 0) {
-    for (int role = 0; role < 3; ++role) {
-      for (int i = threadIdx.x; i < smem->trace_count[role]; i += blockDim.x)
-        g_trace[role][i] = smem->trace[role][i];
-      if (threadIdx.x == 0) g_trace_count[role] = smem->trace_count[role];
-    }
-  }
-#endif
   if (warp == 1) {
     tc_fence_after_sync();
     __syncwarp();
@@ -783,12 +747,6 @@ __global__ void retile_w13_scales_kernel(const uint8_t* __restrict__ sidecar,
 
 }  // namespace
 
-#if defined(GV_TRACE)
-extern "C" void gv_trace_read(unsigned int* out, int* counts) {
-  cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace));
-  cudaMemcpyFromSymbol(counts, g_trace_count, sizeof(g_trace_count));
-}
-#endif
 
 namespace {
 template <int kMode, int kAtoms, int kN> cudaError_t raise_smem_limit() {

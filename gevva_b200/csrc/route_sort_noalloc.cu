@@ -19,7 +19,10 @@
 //     race on it.  Nothing in it has to start at zero: each call first writes every
 //     word it later reads;
 //   * the first call on each device looks the array's device address up and caches
-//     it.  Make that first call outside any stream capture.
+//     it.  With lazy module loading that call may also be the one at which the driver
+//     places the library's device code and this array in device memory, so make it at
+//     start-up: before the host's arena takes what memory is left, and outside any
+//     stream capture.
 #include <cuda_runtime.h>
 
 #include <mutex>

@@ -134,13 +134,14 @@ class ExpertParallelRunner:
             library().gevva_moe_ep_destroy(handle)
             self._handle = None
 
-    def _barrier(self):
-        # a stream-ordered collective: no rank's next phase starts before every rank's
-        # previous phase (and its stores into peer memory) has finished
+    def _barrier(self, stream=None):
+        # a collective ordered on the same stream as the phases: no rank's next phase starts
+        # before every rank's previous phase (and its stores into peer memory) has finished
         if self._nccl_barrier:
-            dist.all_reduce(self._flag, group=self.group)
+            with torch.cuda.stream(stream if stream is not None else torch.cuda.current_stream()):
+                dist.all_reduce(self._flag, group=self.group)
         else:
-            self._call("gevva_moe_ep_barrier", _stream_handle(None))
+            self._call("gevva_moe_ep_barrier", _stream_handle(stream))
 
     def _call(self, name, *args):
         with torch.cuda.device(self.device):
@@ -156,11 +157,11 @@ class ExpertParallelRunner:
         _check(output, torch.bfloat16, (tokens, HIDDEN), "output")
         s = _stream_handle(stream)
         self._call("gevva_moe_ep_route_sort", _ptr(expert_ids), tokens, s)
-        self._barrier()
+        self._barrier(stream)
         self._call("gevva_moe_ep_dispatch", _ptr(input), _ptr(expert_ids), tokens, s)
-        self._barrier()
+        self._barrier(stream)
         self._call("gevva_moe_ep_compute", s)
-        self._barrier()
+        self._barrier(stream)
         self._call("gevva_moe_ep_reduce", _ptr(route_weights), _ptr(output), tokens, s)
 
     def timed_step(self, input, expert_ids, route_weights, output, tokens):

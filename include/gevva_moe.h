@@ -161,8 +161,11 @@ int gevva_moe_buffer(const gevva_moe* runner, int buffer_id, void** device_ptr, 
  *   status   i32 [1], zeroed by the caller; set to 1 if an id is outside [0,128)
  * Limits: 1 <= tokens <= 16384, else GEVVA_MOE_TOO_LARGE.  All calls on a device share
  * the array, so calls that may overlap on the GPU race; order them on one stream.
- * The first call on each device resolves the array's address: make it before any
- * stream capture.  Calls no allocating routine. */
+ * The first call on each device resolves the array's address, and with lazy module
+ * loading it is also the moment the driver loads the library's device code, the array
+ * included, into device memory: make that call at start-up, before the host's arena
+ * claims the remaining memory and before any stream capture.  After it, no call
+ * allocates or calls an allocating routine. */
 int gevva_moe_route_sort_noalloc(const int* expert_ids, int tokens, int* sorted_experts,
                                  int* sorted_routes, int* inverse_routes, int* expert_offsets,
                                  int* scale_row_offsets, int* status, gevva_stream_t stream);
@@ -182,7 +185,9 @@ int gevva_moe_route_sort_noalloc(const int* expert_ids, int tokens, int* sorted_
  *   peer_recv_codes  u8  [recv_capacity_rows, 1408]
  *   peer_recv_sf     u8  [recv_capacity_rows, 176]   (row-major scale bytes as received)
  *   peer_combine     bf16 [8*max_tokens, 2816]
- * recv_capacity_rows >= world * 8 * max_tokens covers the worst case.  local_weights holds
+ * recv_capacity_rows must be at least world * 8 * max_tokens (every route of every rank on one
+ * owner; smaller values are refused with GEVVA_MOE_BAD_ARGUMENT because no kernel bounds a
+ * receive row against the capacity).  local_weights holds
  * this rank's 128/world experts in the sidecar layout with [128/world] scale vectors;
  * in_scale_q1_global is g1.input_scale_quant of all 128 experts (the sender quantises). */
 typedef struct gevva_moe_ep gevva_moe_ep;

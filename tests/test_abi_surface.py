@@ -53,6 +53,30 @@ def test_null_arguments_are_rejected_without_cuda(lib):
     lib.gevva_moe_destroy(None)  # no-op
 
 
+def test_expert_parallel_receive_capacity_below_worst_case_is_refused(lib):
+    """A receive buffer smaller than world * 8 * max_tokens rows could be overrun by a skewed
+    batch (stores into another GPU's memory); creation refuses it before any CUDA call."""
+    from gevva_b200.expert_parallel import _EpConfig
+    from gevva_b200.runtime import _Weights
+    vp = ctypes.c_void_p
+    world, max_tokens = 2, 64
+    fake = (vp * world)(0x1000, 0x2000)   # never dereferenced: the size check comes first
+    cast = lambda a: ctypes.cast(a, ctypes.POINTER(vp))
+    weights = _Weights(*([0x1000] * 8))
+    scale = vp(0x1000)
+    lib.gevva_moe_ep_create.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(_Weights), vp, ctypes.POINTER(_EpConfig)]
+    handle = vp()
+    for capacity in (0, world * 8 * max_tokens - 1):
+        config = _EpConfig(0, world, max_tokens, capacity, cast(fake), cast(fake), cast(fake), cast(fake),
+                           cast(fake), None)
+        assert lib.gevva_moe_ep_create(ctypes.byref(handle), ctypes.byref(weights), scale,
+                                       ctypes.byref(config)) == -3
+    # a null peer table is refused too
+    config = _EpConfig(0, world, max_tokens, world * 8 * max_tokens, None, cast(fake), cast(fake), cast(fake),
+                       cast(fake), None)
+    assert lib.gevva_moe_ep_create(ctypes.byref(handle), ctypes.byref(weights), scale, ctypes.byref(config)) == -3
+
+
 def test_python_mirror_fails_loudly_without_library(monkeypatch, tmp_path):
     from gevva_b200 import runtime
     monkeypatch.setattr(runtime, "_lib", None)

@@ -78,6 +78,16 @@ def _worker(rank, world, port, result_dir):
         status, rows = placed.status()
         assert status == 0, status
         assert torch.equal(got, want), f"rank {rank} balanced placement: {(got != want).sum().item()} differ"
+        # the same step enqueued on a stream that is not the current one: phases and barriers
+        # must all be ordered on that stream
+        other = torch.cuda.Stream(device=device)
+        got = torch.zeros_like(x)
+        other.wait_stream(torch.cuda.current_stream())
+        placed.launch_batch(x, ids, rw, got, tokens, stream=other)
+        torch.cuda.current_stream().wait_stream(other)
+        status, rows = placed.status()
+        assert status == 0, status
+        assert torch.equal(got, want), f"rank {rank} explicit stream: {(got != want).sum().item()} differ"
         open(os.path.join(result_dir, f"ok{rank}"), "w").write("ok")
     finally:
         dist.destroy_process_group()

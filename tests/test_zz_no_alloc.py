@@ -64,6 +64,24 @@ def test_noalloc_sort_single_block_path_and_bad_id(cuda_device):
     assert int(got["status"][0]) == 1
 
 
+def test_noalloc_sort_at_its_maximum_size(cuda_device):
+    """16384 tokens = 128 chunks of 1024 routes: every histogram row of the fixed array is in use."""
+    from gevva_b200 import runtime as rt
+    ids = _ids(16384, 4)
+    got = rt.route_sort_noalloc(torch.from_numpy(ids).to(cuda_device))
+    assert int(got["status"][0]) == 0
+    flat = ids.reshape(-1)
+    order = np.argsort(flat, kind="stable")
+    assert (got["sorted_routes"].cpu().numpy() == order).all()
+    assert (got["sorted_experts"].cpu().numpy() == flat[order]).all()
+    inverse = np.empty_like(order)
+    inverse[order] = np.arange(order.size)
+    assert (got["inverse_routes"].cpu().numpy() == inverse).all()
+    counts = np.bincount(flat, minlength=EXPERTS)
+    assert (got["expert_offsets"].cpu().numpy() == np.r_[0, np.cumsum(counts)]).all()
+    assert (got["scale_row_offsets"].cpu().numpy() == np.r_[0, np.cumsum((counts + 127) // 128 * 128)]).all()
+
+
 def test_noalloc_sort_rejects_sizes_beyond_its_fixed_array(cuda_device):
     import gevva_b200 as gm
     from gevva_b200 import runtime as rt

@@ -461,6 +461,70 @@ int gevva_sidecar_layer_weights(const gevva_sidecar* s, int layer, gevva_moe_wei
   });
 }
 
+// Checkpoint -> sidecar packing of one layer, on the host.  Follows
+// tools/pack_trtllm_experts.py:88-148: stack the experts, w13 rows = [up; gate] (:110-113),
+// weights copied as they are, each expert's row-major E4M3 block scales put into the 128-row x
+// 4-group interleave (:51-65; offset formula src/nvfp4_cutlass.cu:321-323), and the five derived
+// vectors (:141-147) computed in fp32 exactly as the script's tensor arithmetic does.
+int gevva_moe_pack_checkpoint_layer(const gevva_checkpoint_expert* experts, int expert_count, int hidden,
+                                    int intermediate, gevva_sidecar_layer* out) {
+  if (!experts || !out || expert_count < 1 || hidden < 64 || intermediate < 64) return GEVVA_MOE_BAD_ARGUMENT;
+  return guarded([&]() {
+    // rows of a projection fill whole 128-row scale blocks, K whole groups of 4 block scales
+    if (hidden % 128 != 0 || intermediate % 64 != 0 || (2 * intermediate) % 128 != 0)
+      fail("hidden must be a multiple of 128 and intermediate a multiple of 64");
+    void* const outputs[] = {out->w13_weight, out->w13_weight_scale, out->w2_weight, out->w2_weight_scale,
+                             out->w13_input_scale, out->w2_input_scale, out->w13_weight_scale_2,
+                             out->w2_weight_scale_2, out->g1_alpha, out->g1_alpha_up, out->g2_alpha,
+                             out->g1_input_scale_quant, out->g2_input_scale_quant};
+    for (void* pointer : outputs)
+      if (!pointer) fail("an output tensor pointer is null");
+    const size_t in_row = static_cast<size_t>(hidden) / 2, in_groups = static_cast<size_t>(hidden) / 16;
+    const size_t mid_row = static_cast<size_t>(intermediate) / 2, mid_groups = static_cast<size_t>(intermediate) / 16;
+    auto interleave = [](const uint8_t* row_major, int rows, size_t groups, uint8_t* dst) {
+      for (int r = 0; r < rows; ++r)
+        for (size_t g = 0; g < groups; ++g)
+          dst[static_cast<size_t>(r >> 7) * (128 * groups) + (g >> 2) * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 +
+              (g & 3)] = row_major[static_cast<size_t>(r) * groups + g];
+    };
+    for (int e = 0; e < expert_count; ++e) {
+      const gevva_checkpoint_expert& x = experts[e];
+      const gevva_checkpoint_projection* parts[3] = {&x.gate_proj, &x.up_proj, &x.down_proj};
+      for (const gevva_checkpoint_projection* part : parts)
+        if (!part->weight || !part->weight_scale) fail("expert " + std::to_string(e) + ": null checkpoint tensor");
+      // "gate/up activation scales differ" (tools/pack_trtllm_experts.py:127-128)
+      if (memcmp(&x.gate_proj.input_scale, &x.up_proj.input_scale, sizeof(float)) != 0)
+        fail("expert " + std::to_string(e) + ": gate/up activation scales differ");
+      uint8_t* w13 = static_cast<uint8_t*>(out->w13_weight) + static_cast<size_t>(e) * 2 * intermediate * in_row;
+      memcpy(w13, x.up_proj.weight, static_cast<size_t>(intermediate) * in_row);
+      memcpy(w13 + static_cast<size_t>(intermediate) * in_row, x.gate_proj.weight,
+             static_cast<size_t>(intermediate) * in_row);
+      std::vector<uint8_t> stacked(static_cast<size_t>(2) * intermediate * in_groups);
+      memcpy(stacked.data(), x.up_proj.weight_scale, static_cast<size_t>(intermediate) * in_groups);
+      memcpy(stacked.data() + static_cast<size_t>(intermediate) * in_groups, x.gate_proj.weight_scale,
+             static_cast<size_t>(intermediate) * in_groups);
+      interleave(stacked.data(), 2 * intermediate, in_groups,
+                 static_cast<uint8_t*>(out->w13_weight_scale) + static_cast<size_t>(e) * 2 * intermediate * in_groups);
+      memcpy(static_cast<uint8_t*>(out->w2_weight) + static_cast<size_t>(e) * hidden * mid_row, x.down_proj.weight,
+             static_cast<size_t>(hidden) * mid_row);
+      interleave(static_cast<const uint8_t*>(x.down_proj.weight_scale), hidden, mid_groups,
+                 static_cast<uint8_t*>(out->w2_weight_scale) + static_cast<size_t>(e) * hidden * mid_groups);
+      const float gate_input = x.gate_proj.input_scale, down_input = x.down_proj.input_scale;
+      out->w13_input_scale[e] = gate_input;
+      out->w2_input_scale[e] = down_input;
+      out->w13_weight_scale_2[2 * e] = x.gate_proj.weight_scale_2;
+      out->w13_weight_scale_2[2 * e + 1] = x.up_proj.weight_scale_2;
+      out->w2_weight_scale_2[e] = x.down_proj.weight_scale_2;
+      out->g1_alpha[e] = gate_input * x.gate_proj.weight_scale_2;
+      out->g1_alpha_up[e] = x.up_proj.input_scale * x.up_proj.weight_scale_2;
+      out->g2_alpha[e] = down_input * x.down_proj.weight_scale_2;
+      out->g1_input_scale_quant[e] = 1.0f / gate_input;
+      out->g2_input_scale_quant[e] = 1.0f / down_input;
+    }
+    return static_cast<int>(GEVVA_MOE_OK);
+  });
+}
+
 const char* gevva_sidecar_error(void) { return g_sidecar_error.c_str(); }
 
 }  // extern "C"

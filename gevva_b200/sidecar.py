@@ -173,6 +173,108 @@ def write_sidecar(path, layers):
             out.write(blob.tobytes())
 
 
+class _Projection(ctypes.Structure):
+    _fields_ = [("weight", ctypes.c_void_p), ("weight_scale", ctypes.c_void_p),
+                ("weight_scale_2", ctypes.c_float), ("input_scale", ctypes.c_float)]
+
+
+class _CheckpointExpert(ctypes.Structure):
+    _fields_ = [("gate_proj", _Projection), ("up_proj", _Projection), ("down_proj", _Projection)]
+
+
+class _SidecarLayer(ctypes.Structure):
+    _fields_ = [(name, ctypes.c_void_p) for name in
+                ("w13_weight", "w13_weight_scale", "w2_weight", "w2_weight_scale", "w13_input_scale",
+                 "w2_input_scale", "w13_weight_scale_2", "w2_weight_scale_2", "g1_alpha", "g1_alpha_up",
+                 "g2_alpha", "g1_input_scale_quant", "g2_input_scale_quant")]
+
+
+def pack_checkpoint_layer(get, layer, experts=EXPERTS, hidden=2816, intermediate=704):
+    """The thirteen sidecar tensors of one layer from checkpoint tensors, as
+    tools/pack_trtllm_experts.py:88-148 makes them.  `get(name)` returns the checkpoint tensor
+    `name` as a numpy array (what safetensors' get_tensor gives): per expert E and projection P in
+    gate_proj / up_proj / down_proj,
+        model.language_model.layers.{layer}.experts.{E}.{P}.weight          u8 [rows, k/2]
+        ...weight_scale  E4M3 bytes [rows, k/16]   ...weight_scale_2, ...input_scale  f32 scalars.
+    The work is done by gevva_moe_pack_checkpoint_layer on the host; the result is a dict keyed by
+    the suffixes of LAYER_TENSORS, ready for write_sidecar."""
+    lib = _bind(library())
+    lib.gevva_moe_pack_checkpoint_layer.argtypes = [ctypes.POINTER(_CheckpointExpert), ctypes.c_int, ctypes.c_int,
+                                                    ctypes.c_int, ctypes.POINTER(_SidecarLayer)]
+    lib.gevva_moe_pack_checkpoint_layer.restype = ctypes.c_int
+    keep = []
+
+    def projection(expert, name, rows, k):
+        prefix = f"model.language_model.layers.{layer}.experts.{expert}.{name}."
+        weight = np.ascontiguousarray(get(prefix + "weight")).view(np.uint8)
+        scale = np.ascontiguousarray(get(prefix + "weight_scale")).view(np.uint8)
+        if weight.shape != (rows, k // 2) or scale.shape != (rows, k // 16):
+            raise ValueError(f"{prefix}: weight {weight.shape}, weight_scale {scale.shape}; expected "
+                             f"{(rows, k // 2)} and {(rows, k // 16)}")
+        keep.extend((weight, scale))
+        return _Projection(weight.ctypes.data, scale.ctypes.data,
+                           float(np.asarray(get(prefix + "weight_scale_2"), dtype=np.float32).reshape(())),
+                           float(np.asarray(get(prefix + "input_scale"), dtype=np.float32).reshape(())))
+
+    table = (_CheckpointExpert * experts)()
+    for e in range(experts):
+        table[e] = _CheckpointExpert(projection(e, "gate_proj", intermediate, hidden),
+                                     projection(e, "up_proj", intermediate, hidden),
+                                     projection(e, "down_proj", hidden, intermediate))
+    out = {
+        "w13.weight": np.empty((experts, 2 * intermediate, hidden // 2), np.uint8),
+        "w13.weight_scale": np.empty((experts, 2 * intermediate, hidden // 16), np.uint8),
+        "w2.weight": np.empty((experts, hidden, intermediate // 2), np.uint8),
+        "w2.weight_scale": np.empty((experts, hidden, intermediate // 16), np.uint8),
+        "w13.input_scale": np.empty(experts, np.float32), "w2.input_scale": np.empty(experts, np.float32),
+        "w13.weight_scale_2": np.empty((experts, 2), np.float32), "w2.weight_scale_2": np.empty(experts, np.float32),
+        "g1.alpha": np.empty(experts, np.float32), "g1.alpha_up": np.empty(experts, np.float32),
+        "g2.alpha": np.empty(experts, np.float32), "g1.input_scale_quant": np.empty(experts, np.float32),
+        "g2.input_scale_quant": np.empty(experts, np.float32),
+    }
+    order = ("w13.weight", "w13.weight_scale", "w2.weight", "w2.weight_scale", "w13.input_scale",
+             "w2.input_scale", "w13.weight_scale_2", "w2.weight_scale_2", "g1.alpha", "g1.alpha_up", "g2.alpha",
+             "g1.input_scale_quant", "g2.input_scale_quant")
+    target = _SidecarLayer(*[out[name].ctypes.data for name in order])
+    status = lib.gevva_moe_pack_checkpoint_layer(table, experts, hidden, intermediate, ctypes.byref(target))
+    if status != 0:
+        _raise(lib, status, "gevva_moe_pack_checkpoint_layer")
+    return out
+
+
+def deinterleave_scales(interleaved):
+    """Inverse of the 128-row x 4-group block-scale interleave: sidecar layout [rows, groups] (as
+    stored) -> row-major [rows, groups] (as a checkpoint stores weight_scale)."""
+    rows, groups = interleaved.shape
+    blocks = interleaved.reshape(rows // 128, groups // 4, 32, 4, 4)     # [row block, k block, r%32, (r/32)%4, g%4]
+    return np.ascontiguousarray(blocks.transpose(0, 3, 2, 1, 4)).reshape(rows, groups)
+
+
+def synthetic_checkpoint(packed, s1, s2, layer=0):
+    """A checkpoint-format view of `make_packed_experts` output: per-expert gate/up/down tensors
+    with row-major block scales, under the checkpoint's tensor names.  Returns get(name)."""
+    w13, w13_sf = packed["w13"].cpu().numpy(), packed["w13_sf"].cpu().numpy()
+    w2, w2_sf = packed["w2"].cpu().numpy(), packed["w2_sf"].cpu().numpy()
+    g13, g2 = packed["g13"].cpu().numpy(), packed["g2"].cpu().numpy()
+    inter = w13.shape[1] // 2
+
+    def get(name):
+        parts = name.split(".")
+        expert, projection, suffix = int(parts[5]), parts[6], parts[7]
+        assert int(parts[3]) == layer
+        if projection == "down_proj":
+            table = {"weight": lambda: w2[expert], "weight_scale": lambda: deinterleave_scales(w2_sf[expert]),
+                     "weight_scale_2": lambda: np.float32(g2[expert]), "input_scale": lambda: np.float32(s2)}
+        else:
+            rows = slice(0, inter) if projection == "up_proj" else slice(inter, 2 * inter)   # w13 = [up; gate]
+            table = {"weight": lambda: w13[expert][rows],
+                     "weight_scale": lambda: deinterleave_scales(w13_sf[expert])[rows],
+                     "weight_scale_2": lambda: np.float32(g13[expert]), "input_scale": lambda: np.float32(s1)}
+        return table[suffix]()
+
+    return get
+
+
 def synthetic_layer_tensors(packed, weights, s1, s2):
     """The thirteen tensors of one layer from `make_packed_experts` output, the runner's
     `ExpertWeights` (whose alpha and input_scale_quant vectors are stored as they are) and the

@@ -308,6 +308,46 @@ int gevva_sidecar_check_layers(const gevva_sidecar* sidecar, int layers);
 int gevva_sidecar_layer_weights(const gevva_sidecar* sidecar, int layer, gevva_moe_weights* host_views);
 const char* gevva_sidecar_error(void);
 
+/* Checkpoint -> sidecar packer for one layer (host only, no CUDA call).  Replaces the per-layer
+ * body of tools/pack_trtllm_experts.py:88-148: takes the checkpoint's already quantised
+ * per-expert tensors (model.language_model.layers.L.experts.E.{gate,up,down}_proj.{weight,
+ * weight_scale,weight_scale_2,input_scale}), stacks the experts, orders w13 rows [up; gate],
+ * puts every expert's row-major E4M3 block scales into the 128-row x 4-group interleave the GEMM
+ * reads (the job of flashinfer's nvfp4_block_scale_interleave there) and derives
+ *   g1.alpha = gate input_scale * gate weight_scale_2,  g1.alpha_up likewise for up,
+ *   g2.alpha = down input_scale * down weight_scale_2,  g*.input_scale_quant = 1 / input_scale.
+ * All pointers are HOST pointers; the outputs are the thirteen tensors of the layer schema
+ * (src/runtime.cpp:233-252) with the caller's sizes: hidden 2816 and intermediate 704 for
+ * Gemma-4 26B-A4B.  Gate and up input scales that differ are an error, as in the script. */
+typedef struct {
+  const void* weight;       /* u8  [rows, k/2]   E2M1 pairs */
+  const void* weight_scale; /* u8  [rows, k/16]  E4M3, row-major */
+  float weight_scale_2;     /* per-tensor global scale */
+  float input_scale;        /* static activation scale */
+} gevva_checkpoint_projection;
+typedef struct {
+  gevva_checkpoint_projection gate_proj; /* rows = intermediate, k = hidden */
+  gevva_checkpoint_projection up_proj;   /* rows = intermediate, k = hidden */
+  gevva_checkpoint_projection down_proj; /* rows = hidden, k = intermediate */
+} gevva_checkpoint_expert;
+typedef struct {
+  void* w13_weight;             /* u8 [E, 2*intermediate, hidden/2] */
+  void* w13_weight_scale;       /* u8 [E, 2*intermediate, hidden/16], interleaved */
+  void* w2_weight;              /* u8 [E, hidden, intermediate/2] */
+  void* w2_weight_scale;        /* u8 [E, hidden, intermediate/16], interleaved */
+  float* w13_input_scale;       /* [E] */
+  float* w2_input_scale;        /* [E] */
+  float* w13_weight_scale_2;    /* [E,2]: gate, up */
+  float* w2_weight_scale_2;     /* [E] */
+  float* g1_alpha;              /* [E] */
+  float* g1_alpha_up;           /* [E] */
+  float* g2_alpha;              /* [E] */
+  float* g1_input_scale_quant;  /* [E] */
+  float* g2_input_scale_quant;  /* [E] */
+} gevva_sidecar_layer;
+int gevva_moe_pack_checkpoint_layer(const gevva_checkpoint_expert* experts, int expert_count, int hidden,
+                                    int intermediate, gevva_sidecar_layer* out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -33,3 +33,43 @@ def test_sidecar_round_trip_runs_the_layer(tmp_path):
     runner.launch_batch(x, ids, route_weights, out, tokens)
     runner.check()
     assert torch.equal(out, expected)
+
+
+def test_checkpoint_to_sidecar_to_runner(tmp_path):
+    """A synthetic layer presented in the checkpoint's format (per-expert gate/up/down tensors,
+    row-major block scales, weight_scale_2, input_scale) goes through the checkpoint packer, the
+    sidecar writer and reader and the schema check, and drives the runner to the same output bits
+    as the in-memory weights (tools/pack_trtllm_experts.py:88-148 is the step replaced)."""
+    import gevva_b200
+    from gevva_b200.runtime import Nvfp4ExpertRunner
+    from gevva_b200.sidecar import ExpertSidecar, pack_checkpoint_layer, synthetic_checkpoint, write_sidecar
+    from gevva_b200.synthetic import SyntheticLayer
+
+    tokens = 200
+    layer = SyntheticLayer(seed=4, max_tokens=tokens, bias_std=0.5)
+    layer.set_scales(0.002, 0.006)
+    x = layer.inputs(tokens, seed=12)
+    expected = layer.forward(x)
+    torch.cuda.synchronize()
+
+    tensors = pack_checkpoint_layer(synthetic_checkpoint(layer.packed, layer.s1, layer.s2), 0)
+    path = tmp_path / "experts-00.safetensors"
+    write_sidecar(path, [tensors])
+    with ExpertSidecar(path) as sidecar:
+        sidecar.check_layers(1)
+        weights = sidecar.layer_weights(0, device=x.device)
+    for name in ("w13", "w13_sf", "w2", "w2_sf"):
+        assert torch.equal(getattr(weights, name), getattr(layer.weights, name)), name
+    for name in ("alpha1", "alpha2", "in_scale_q1", "in_scale_q2"):   # same fp32 products and quotients
+        assert torch.allclose(getattr(weights, name), getattr(layer.weights, name), rtol=2e-7, atol=0), name
+    runner = Nvfp4ExpertRunner(weights, tokens)
+    route_weights, ids = gevva_b200.route_128_top8(layer.logits(x), layer.expert_scale)
+    out = torch.empty_like(x)
+    runner.launch_batch(x, ids, route_weights, out, tokens)
+    runner.check()
+    if all(torch.equal(getattr(weights, n), getattr(layer.weights, n))
+           for n in ("alpha1", "alpha2", "in_scale_q1", "in_scale_q2")):
+        assert torch.equal(out, expected)
+    else:   # a last-bit difference in a scale vector (python float vs fp32 arithmetic in set_scales)
+        err = (out.float() - expected.float()).norm() / expected.float().norm()
+        assert err < 2e-2

@@ -28,6 +28,7 @@ struct gevva_dense {
   uint8_t* prod_fp8 = nullptr;    // [T, 2112]
   float* prod_scales = nullptr;   // [T]
   float* ones = nullptr;          // [128]
+  float* down_scale = nullptr;    // [1]: weights.down_scale on the device, for gevva_ff_finalize
   int* ints = nullptr;
 };
 
@@ -41,6 +42,7 @@ void gevva_dense_destroy(gevva_dense* d) {
   cudaFree(d->prod_fp8);
   cudaFree(d->prod_scales);
   cudaFree(d->ones);
+  cudaFree(d->down_scale);
   cudaFree(d->ints);
   delete d;
 }
@@ -68,6 +70,9 @@ int gevva_dense_create(gevva_dense** out, const gevva_dense_weights* weights, in
   if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&d->prod_fp8), t * kDense);
   if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&d->prod_scales), t * sizeof(float));
   if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&d->ones), gv::kExperts * sizeof(float));
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&d->down_scale), sizeof(float));
+  if (e == cudaSuccess)
+    e = cudaMemcpy(d->down_scale, &weights->down_scale, sizeof(float), cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&d->ints), int_count * sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(d->ints, 0, int_count * sizeof(int));
   if (e == cudaSuccess) {
@@ -126,6 +131,8 @@ int gevva_dense_launch(gevva_dense* d, const void* in, void* out_unscaled, int t
 
 const float* gevva_dense_output_scales(const gevva_dense* d) { return d ? d->prod_scales : nullptr; }
 
+const float* gevva_dense_projection_scale(const gevva_dense* d) { return d ? d->down_scale : nullptr; }
+
 int gevva_dense_buffer(const gevva_dense* d, int which, void** ptr, size_t* bytes) {
   if (!d || !ptr || !bytes) return GEVVA_MOE_BAD_ARGUMENT;
   const size_t t = static_cast<size_t>(d->max_tokens);
@@ -156,9 +163,10 @@ int gevva_ff_finalize(const void* dense, const void* dense_weight, const void* e
                       const float* route_weights, const int* inverse_routes, const void* expert_weight,
                       const void* combined_weight, const void* residual, const void* layer_scalar,
                       void* output, int rows, const float* dense_activation_scales,
-                      float dense_projection_scale, gevva_stream_t stream) {
+                      const float* dense_projection_scale, gevva_stream_t stream) {
   if (!dense || !dense_weight || !expert_routes || !route_weights || !expert_weight || !combined_weight ||
-      !residual || !layer_scalar || !output || rows < 0)
+      !residual || !layer_scalar || !output || rows < 0 ||
+      (dense_activation_scales != nullptr && dense_projection_scale == nullptr))
     return GEVVA_MOE_BAD_ARGUMENT;
   if (rows == 0) return GEVVA_MOE_OK;
   gv::launch_ff_finalize(dense, dense_weight, expert_routes, route_weights, inverse_routes, expert_weight,

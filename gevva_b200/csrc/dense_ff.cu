@@ -184,14 +184,15 @@ ff_finalize_kernel(const __nv_bfloat16* __restrict__ dense, const __nv_bfloat16*
                    const __nv_bfloat16* __restrict__ combined_weight,
                    const __nv_bfloat16* __restrict__ residual,
                    const __nv_bfloat16* __restrict__ layer_scalar, __nv_bfloat16* __restrict__ output,
-                   const float* __restrict__ dense_activation_scales, float dense_projection_scale) {
+                   const float* __restrict__ dense_activation_scales,
+                   const float* __restrict__ dense_projection_scale) {
   __shared__ float scratch[kRowThreads / 32 + 1];
   const int row = blockIdx.x;
   const size_t base = static_cast<size_t>(row) * kHidden;
   float d[8], e[8], w[8];
   unpack8(__ldg(reinterpret_cast<const uint4*>(dense + base) + threadIdx.x), d);
   if (dense_activation_scales) {
-    const float scale = __fmul_rn(dense_activation_scales[row], dense_projection_scale);
+    const float scale = __fmul_rn(dense_activation_scales[row], dense_projection_scale[0]);
 #pragma unroll
     for (int i = 0; i < 8; ++i) d[i] = bf16_round(__fmul_rn(d[i], scale));
   }
@@ -291,7 +292,7 @@ void launch_ff_finalize(const void* dense, const void* dense_weight, const void*
                         const float* route_weights, const int* inverse_routes, const void* expert_weight,
                         const void* combined_weight, const void* residual, const void* layer_scalar,
                         void* output, int rows, const float* dense_activation_scales,
-                        float dense_projection_scale, cudaStream_t stream) {
+                        const float* dense_projection_scale, cudaStream_t stream) {
   using B = __nv_bfloat16;
   ff_finalize_kernel<<<rows, kRowThreads, 0, stream>>>(
       static_cast<const B*>(dense), static_cast<const B*>(dense_weight), static_cast<const B*>(expert_routes),

@@ -110,7 +110,7 @@ void launch_ff_finalize(const void* dense, const void* dense_weight, const void*
                         const float* route_weights, const int* inverse_routes, const void* expert_weight,
                         const void* combined_weight, const void* residual, const void* layer_scalar,
                         void* output, int rows, const float* dense_activation_scales,
-                        float dense_projection_scale, cudaStream_t stream);
+                        const float* dense_projection_scale, cudaStream_t stream);
 void launch_dense_plan(int rows, const RoutePlan& plan, cudaStream_t stream);
 void launch_pack_fp8(const float* w, size_t count, uint8_t* out, float* scale_out, cudaStream_t stream);
 

@@ -23,13 +23,15 @@ def _lib():
         return lib
     vp, i32, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
     lib.gevva_ff_prepare.argtypes = [vp] * 7 + [i32, vp]
-    lib.gevva_ff_finalize.argtypes = [vp] * 10 + [i32, vp, f32, vp]
+    lib.gevva_ff_finalize.argtypes = [vp] * 10 + [i32, vp, vp, vp]
     lib.gevva_dense_create.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(_DenseWeights), i32]
     lib.gevva_dense_destroy.argtypes = [vp]
     lib.gevva_dense_destroy.restype = None
     lib.gevva_dense_launch.argtypes = [vp, vp, vp, i32, vp]
     lib.gevva_dense_output_scales.argtypes = [vp]
     lib.gevva_dense_output_scales.restype = vp
+    lib.gevva_dense_projection_scale.argtypes = [vp]
+    lib.gevva_dense_projection_scale.restype = vp
     lib.gevva_dense_buffer.argtypes = [vp, i32, ctypes.POINTER(vp), ctypes.POINTER(ctypes.c_size_t)]
     lib.gevva_pack_fp8.argtypes = [vp, ctypes.c_size_t, vp, vp, vp]
     lib._gv_ff_ready = True
@@ -65,14 +67,16 @@ def ff_prepare(x, dense_weight, expert_weight, router_scale):
 
 def ff_finalize(dense, dense_weight, expert_routes, route_weights, inverse_routes, expert_weight,
                 combined_weight, residual, layer_scalar, dense_activation_scales=None,
-                dense_projection_scale=1.0):
+                dense_projection_scale=None):
+    """dense_activation_scales f32 [rows] and dense_projection_scale f32 [1] are CUDA tensors (or both
+    None), as the reference kernel takes them."""
     rows = dense.shape[0]
     out = torch.empty_like(residual)
     with torch.cuda.device(dense.device):
         _status(_lib().gevva_ff_finalize(
             _ptr(dense), _ptr(dense_weight), _ptr(expert_routes), _ptr(route_weights), _ptr(inverse_routes),
             _ptr(expert_weight), _ptr(combined_weight), _ptr(residual), _ptr(layer_scalar), _ptr(out), rows,
-            _ptr(dense_activation_scales), float(dense_projection_scale), _stream_handle(None)), "ff_finalize")
+            _ptr(dense_activation_scales), _ptr(dense_projection_scale), _stream_handle(None)), "ff_finalize")
     return out
 
 
@@ -91,6 +95,9 @@ class DenseMlp:
         with torch.cuda.device(self.device):
             _status(_lib().gevva_dense_create(ctypes.byref(handle), ctypes.byref(w), max_tokens), "DenseMlp")
         self._handle = handle
+        # f32 [1] on the device, owned by the runner: what ff_finalize takes beside the row scales
+        self.projection_scale = _view(_lib().gevva_dense_projection_scale(self._handle), (1,), torch.int32,
+                                      self.device).view(torch.float32)
 
     def __del__(self):
         if getattr(self, "_handle", None):
@@ -151,4 +158,4 @@ class FeedForwardLayer:
             main.wait_stream(aux_stream)
         return ff_finalize(dense_out, self.dense_post, self.experts.routed_output(), weights,
                            self.experts.inverse_routes(), self.expert_post, self.combined_post, hidden,
-                           self.layer_scalar, dense_scales, self.dense.down_scale)
+                           self.layer_scalar, dense_scales, self.dense.projection_scale)

@@ -235,8 +235,9 @@ int gevva_moe_ep_status(gevva_moe_ep* ep, int* received_rows);
  * gevva_ff_finalize replaces finalize_feedforward_routes_2816_kernel (normalization.cuh:249-377,
  * launched at prefill.cuh:1238-1245): weighted reduce of the eight routed rows (read through
  * inverse_routes from gevva_moe_routed_output), RMSNorm of the dense and expert branches, their
- * sum, a third RMSNorm, residual add and the layer scalar.  dense_activation_scales /
- * dense_projection_scale rescale an unscaled FP8 GEMM output (NULL / unused otherwise). */
+ * sum, a third RMSNorm, residual add and the layer scalar.  dense_activation_scales f32 [rows] and
+ * dense_projection_scale f32 [1], both on the DEVICE as in the reference kernel's signature
+ * (normalization.cuh:249-262), rescale an unscaled FP8 GEMM output; both NULL otherwise. */
 int gevva_ff_prepare(const void* input, const void* dense_weight, const void* expert_weight,
                      const void* router_scale, void* dense_out, void* expert_out, void* router_out,
                      int rows, gevva_stream_t stream);
@@ -244,7 +245,7 @@ int gevva_ff_finalize(const void* dense, const void* dense_weight, const void* e
                       const float* route_weights, const int* inverse_routes, const void* expert_weight,
                       const void* combined_weight, const void* residual, const void* layer_scalar,
                       void* output, int rows, const float* dense_activation_scales,
-                      float dense_projection_scale, gevva_stream_t stream);
+                      const float* dense_projection_scale, gevva_stream_t stream);
 
 /* Dense GeGLU MLP of width 2112 in FP8 E4M3 with per-tensor weight scales
  * (tools/pack_fp8_dense.py:52-71) and per-row dynamic activation scales.  Replaces the
@@ -265,6 +266,8 @@ void gevva_dense_destroy(gevva_dense* dense);
 int gevva_dense_launch(gevva_dense* dense, const void* in, void* out_unscaled, int tokens,
                        gevva_stream_t stream);
 const float* gevva_dense_output_scales(const gevva_dense* dense);
+/* f32 [1] on the device: weights->down_scale, in the form gevva_ff_finalize takes it */
+const float* gevva_dense_projection_scale(const gevva_dense* dense);
 /* stage buffers for parity tests: 0 input e4m3, 1 input scales, 2 gate|up bf16 unscaled,
  * 3 product e4m3, 4 product scales */
 int gevva_dense_buffer(const gevva_dense* dense, int which, void** device_ptr, size_t* bytes);

@@ -99,10 +99,11 @@ def test_ff_finalize_bit_exact(dense_oracle, cuda_device):
     dw, ew, cw = norm_weight(4, cuda_device), norm_weight(5, cuda_device), norm_weight(6, cuda_device)
     scalar = torch.tensor([0.75], dtype=torch.bfloat16, device=cuda_device)
     for scales, proj in ((act_scales, 0.013), (None, 1.0)):
-        got = ff.ff_finalize(dense, dw, routes, rw, inverse, ew, cw, residual, scalar, scales, proj)
+        proj_dev = None if scales is None else torch.tensor([proj], dtype=torch.float32, device=cuda_device)
+        got = ff.ff_finalize(dense, dw, routes, rw, inverse, ew, cw, residual, scalar, scales, proj_dev)
         want = dense_oracle.finalize(bits(dense), bits(dw), bits(routes), rw.cpu().numpy(),
                                      inverse.cpu().numpy(), bits(ew), bits(cw), bits(residual),
-                                     bits(scalar)[0], None if scales is None else scales.cpu().numpy(), proj)
+                                     bits(scalar)[0], None if scales is None else scales.cpu().numpy(), float(np.float32(proj)))
         assert (bits(got) == want).all()
 
 
@@ -160,3 +161,36 @@ def test_ffn_stack_runs_at_configured_size(cuda_device):
     torch.cuda.synchronize()
     assert torch.isfinite(a.float()).all() and a.float().abs().max() > 0
     assert torch.equal(a, b) and torch.equal(a, c)
+
+
+def test_thirty_layers_captured_into_one_graph_at_verifier_size(cuda_device):
+    """The decode-side caller of the path: rows = sessions x (drafts + 1) <= 40, the whole
+    30-layer enqueue (prepare -> router -> route -> experts unreduced beside the dense MLP on a
+    second stream -> finalize) captured once and replayed (src/cuda/runtime/verifier.cuh:960-1042,
+    capture :1058-1078).  Replays must reproduce the eager pass bit for bit, also after the input
+    buffer has been refilled."""
+    from gevva_b200.synthetic import SyntheticStack
+    rows = 40
+    stack = SyntheticStack(30, rows, cuda_device, distinct_experts=False)
+    first = hashgen.activations(rows, HIDDEN, 11, cuda_device)
+    second = hashgen.activations(rows, HIDDEN, 12, cuda_device)
+    want_first = stack.forward(first, concurrent=False).clone()
+    want_second = stack.forward(second, concurrent=False).clone()
+    torch.cuda.synchronize()
+    assert not torch.equal(want_first, want_second)
+    static_in = first.clone()
+    stack.forward(static_in)            # warm-up outside the capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        static_out = stack.forward(static_in)
+    for _ in range(2):
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(static_out, want_first)
+    static_in.copy_(second)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(static_out, want_second)
+    for layer in stack.layers:
+        layer.experts.check()

@@ -14,6 +14,7 @@ from .runtime import (  # noqa: F401
     library,
     pack_experts,
     route_128_top8,
+    route_project,
 )
 
 __all__ = [
@@ -23,4 +24,5 @@ __all__ = [
     "library",
     "pack_experts",
     "route_128_top8",
+    "route_project",
 ]

@@ -143,33 +143,6 @@ struct GemmParams {
   int last_mmas;    // MMAs (K = 64 each) in the last K block, 1..4
 };
 
-// Bounded wait on an mbarrier.  The time limit is kept with the SM's cycle counter (a
-// cheap register read); it is consulted only every 1024 failed polls so that a short
-// stall costs nothing but the polls themselves.
-constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s at 2 GHz
-
-// kBackoff: sleep between polls.  Warps that wait with slack (producers, epilogue) must not
-// spin, because a spinning warp takes issue slots from the MMA warp on the same scheduler and
-// every instruction of the main loop then costs several times its latency.
-template <bool kBackoff, class Smem>
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Smem* smem,
-                                              int* status) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long start = clock64();
-  for (uint32_t spin = 1;; ++spin) {
-    if (kBackoff) __nanosleep(spin < 8 ? 32 : 128);
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & (kBackoff ? 63u : 1023u)) == 0) {
-      if (smem->abort) return false;
-      if (clock64() - start > kWaitLimitCycles) {
-        smem->abort = 1;
-        atomicExch(status, static_cast<int>(kWaitTimeout));
-        return false;
-      }
-    }
-  }
-}
-
 // One K block's worth of tensor-core work issued as a single instruction sequence:
 // kMmas scale-factor atom copies per operand (shared -> tensor memory) followed by kMmas
 // MMAs of K = 64.  Everything is derived from four 32-bit descriptor bases with immediate

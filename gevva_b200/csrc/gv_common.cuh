@@ -204,6 +204,33 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   }
 }
 
+// Bounded wait on an mbarrier.  The time limit is kept with the SM's cycle counter (a
+// cheap register read); it is consulted only every 1024 failed polls so that a short
+// stall costs nothing but the polls themselves.
+constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s at 2 GHz
+
+// kBackoff: sleep between polls.  Warps that wait with slack (producers, epilogue) must not
+// spin, because a spinning warp takes issue slots from the MMA warp on the same scheduler and
+// every instruction of the main loop then costs several times its latency.
+template <bool kBackoff, class Smem>
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Smem* smem,
+                                              int* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  for (uint32_t spin = 1;; ++spin) {
+    if (kBackoff) __nanosleep(spin < 8 ? 32 : 128);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & (kBackoff ? 63u : 1023u)) == 0) {
+      if (smem->abort) return false;
+      if (clock64() - start > kWaitLimitCycles) {
+        smem->abort = 1;
+        if (status) atomicExch(status, static_cast<int>(kWaitTimeout));
+        return false;
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
@@ -234,6 +261,36 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_sr
 
 __device__ __forceinline__ void prefetch_tensor_map(const void* tensor_map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tensor_map) : "memory");
+}
+
+// ---- thread-block clusters ---------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  return rank;
+}
+
+// Barrier over every thread of the cluster; writes to (distributed) shared memory made before
+// the arrive are visible to every thread after its wait.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Address, in the cluster's shared window, of the byte that `local_address` names in the CTA of
+// rank `cta_rank`.
+__device__ __forceinline__ uint32_t cluster_map_shared(uint32_t local_address, uint32_t cta_rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(cta_rank));
+  return remote;
+}
+
+__device__ __forceinline__ float4 cluster_load_float4(uint32_t cluster_address) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_address)
+               : "memory");
+  return v;
 }
 
 // ---- tensor memory ---------------------------------------------------------

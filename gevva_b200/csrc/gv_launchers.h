@@ -29,6 +29,13 @@ void launch_route(const void* logits_bf16, int ld, const void* expert_scale_bf16
                   int* ids, int tokens, const float* activation_scales,
                   const float* projection_weight_scale, cudaStream_t stream);
 
+// Router projection fused with routing: x [tokens, 2816] (bf16, or E4M3 with per-row scales) times
+// router_w [128, 2816]^T, optional f32 bias, bf16 rounding, top-8 + softmax.  Returns a cudaError_t value.
+int launch_route_project(const void* x, const void* router_w, bool fp8, const float* bias,
+                         const void* expert_scale_bf16, float* weights, int* ids, void* logits_out,
+                         const float* activation_scales, const float* weight_scale, int tokens, int* status,
+                         cudaStream_t stream);
+
 void launch_route_sort(const int* expert_ids, int routes, const RoutePlan& plan,
                        cudaStream_t stream);
 

@@ -303,6 +303,42 @@ int gevva_moe_route(const void* logits_bf16, int ld, const void* expert_scale_bf
   return GEVVA_MOE_OK;
 }
 
+int gevva_moe_route_project(const void* router_input_bf16, const void* router_weight_bf16, const float* bias,
+                            const void* expert_scale_bf16, float* weights, int* ids, void* logits_out,
+                            int tokens, int* device_status, gevva_stream_t stream) {
+  if (!router_input_bf16 || !router_weight_bf16 || !expert_scale_bf16 || !weights || !ids || tokens < 0 ||
+      (reinterpret_cast<uintptr_t>(router_input_bf16) & 15) || (reinterpret_cast<uintptr_t>(router_weight_bf16) & 15) ||
+      (reinterpret_cast<uintptr_t>(bias) & 15))
+    return GEVVA_MOE_BAD_ARGUMENT;
+  if (tokens == 0) return GEVVA_MOE_OK;
+  if (!encode_tiled()) return GEVVA_MOE_NO_DEVICE;
+  GV_CUDA(static_cast<cudaError_t>(gv::launch_route_project(router_input_bf16, router_weight_bf16, false, bias,
+                                                            expert_scale_bf16, weights, ids, logits_out, nullptr,
+                                                            nullptr, tokens, device_status, stream)),
+          "route_project");
+  return GEVVA_MOE_OK;
+}
+
+int gevva_moe_route_project_fp8(const void* router_input_e4m3, const float* activation_scales,
+                                const void* router_weight_e4m3, const float* weight_scale,
+                                const void* expert_scale_bf16, float* weights, int* ids, void* logits_out,
+                                int tokens, int* device_status, gevva_stream_t stream) {
+  if (!router_input_e4m3 || !activation_scales || !router_weight_e4m3 || !weight_scale || !expert_scale_bf16 ||
+      !weights || !ids || tokens < 0 || (reinterpret_cast<uintptr_t>(router_input_e4m3) & 15) ||
+      (reinterpret_cast<uintptr_t>(router_weight_e4m3) & 15))
+    return GEVVA_MOE_BAD_ARGUMENT;
+  if (tokens == 0) return GEVVA_MOE_OK;
+  if (!encode_tiled()) return GEVVA_MOE_NO_DEVICE;
+  GV_CUDA(static_cast<cudaError_t>(gv::launch_route_project(router_input_e4m3, router_weight_e4m3, true, nullptr,
+                                                            expert_scale_bf16, weights, ids, logits_out,
+                                                            activation_scales, weight_scale, tokens, device_status,
+                                                            stream)),
+          "route_project_fp8");
+  return GEVVA_MOE_OK;
+}
+
+int* gevva_moe_status_word(gevva_moe* runner) { return runner ? runner->scratch->plan.status : nullptr; }
+
 int gevva_moe_launch_stages(gevva_moe* runner, const void* in, const int* ids,
                             const float* route_weights, void* out, int tokens, unsigned stages,
                             gevva_stream_t stream) {

@@ -7,6 +7,7 @@
 #include "gv_common.cuh"
 #include "gv_launchers.h"
 #include "gv_plan.cuh"
+#include "gv_route.cuh"
 
 namespace gv {
 
@@ -16,12 +17,6 @@ namespace gv {
 // (a 128-thread CTA and a full CUB radix sort per token).  Here one warp owns one
 // token: four logits per lane, eight rounds of redux.sync arg-max.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t radix_key(float value) {
-  uint32_t bits = __float_as_uint(value);
-  if (bits == 0x80000000u) bits = 0;  // -0 sorts as +0
-  return (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
-}
-
 __global__ void __launch_bounds__(128)
 route_128_top8_kernel(const __nv_bfloat16* __restrict__ logits, int ld,
                       const __nv_bfloat16* __restrict__ expert_scale, float* __restrict__ weights,
@@ -33,7 +28,6 @@ route_128_top8_kernel(const __nv_bfloat16* __restrict__ logits, int ld,
   const uint16_t* src =
       reinterpret_cast<const uint16_t*>(logits) + static_cast<size_t>(row) * ld + 4 * lane;
   float value[4];
-  uint32_t key[4];
   float rescale = 1.0f;
   if (activation_scales) rescale = __fmul_rn(activation_scales[row], projection_weight_scale[0]);
 #pragma unroll
@@ -41,53 +35,9 @@ route_128_top8_kernel(const __nv_bfloat16* __restrict__ logits, int ld,
     float v = bf16_bits_to_float(src[j]);
     if (activation_scales) v = __bfloat162float(__float2bfloat16_rn(__fmul_rn(v, rescale)));
     value[j] = v;
-    key[j] = radix_key(v);
   }
-  uint32_t taken = 0;
-  int my_id = 0;
-  float my_key = 0.0f;
-#pragma unroll 1
-  for (int round = 0; round < kTopK; ++round) {
-    uint32_t best_key = 0;
-    uint32_t best_index = 0xffffffffu;
-#pragma unroll
-    for (int j = 3; j >= 0; --j) {
-      if (!((taken >> j) & 1u) && key[j] >= best_key) {  // descending j: ties keep the lower index
-        best_key = key[j];
-        best_index = 4u * lane + j;
-      }
-    }
-    const uint32_t top_key = __reduce_max_sync(0xffffffffu, best_key);
-    const uint32_t candidate = (best_index != 0xffffffffu && best_key == top_key) ? best_index
-                                                                                  : 0xffffffffu;
-    const uint32_t winner = __reduce_min_sync(0xffffffffu, candidate);
-    const int owner = static_cast<int>(winner >> 2);
-    const int slot = static_cast<int>(winner & 3u);
-    float v = value[0];
-    v = slot == 1 ? value[1] : v;
-    v = slot == 2 ? value[2] : v;
-    v = slot == 3 ? value[3] : v;
-    v = __shfl_sync(0xffffffffu, v, owner);
-    if (lane == owner) taken |= 1u << slot;
-    if (lane == round) {
-      my_id = static_cast<int>(winner);
-      my_key = v;
-    }
-  }
-  const float maximum = __shfl_sync(0xffffffffu, my_key, 0);
-  const float e = lane < kTopK ? gv_expf(__fsub_rn(my_key, maximum)) : 0.0f;
-  float ek[kTopK];
-#pragma unroll
-  for (int k = 0; k < kTopK; ++k) ek[k] = __shfl_sync(0xffffffffu, e, k);
-  // Same association as the reference's shuffle-down tree over lanes 0..7.
-  const float denominator =
-      __fadd_rn(__fadd_rn(__fadd_rn(ek[0], ek[4]), __fadd_rn(ek[2], ek[6])),
-                __fadd_rn(__fadd_rn(ek[1], ek[5]), __fadd_rn(ek[3], ek[7])));
-  if (lane < kTopK) {
-    ids[row * kTopK + lane] = my_id;
-    weights[row * kTopK + lane] =
-        __fmul_rn(__fdiv_rn(e, denominator), __bfloat162float(expert_scale[my_id]));
-  }
+  route_top8_of_row(value, lane, expert_scale, weights + static_cast<size_t>(row) * kTopK,
+                    ids + static_cast<size_t>(row) * kTopK);
 }
 
 void launch_route(const void* logits_bf16, int ld, const void* expert_scale_bf16, float* weights,

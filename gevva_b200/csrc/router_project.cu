@@ -1,0 +1,351 @@
+// Router projection fused with top-8 routing, for sm_100a.
+//
+// The reference computes the router logits with a library GEMM and then routes
+// (src/cuda/runtime/prefill.cuh:414-422, :1203-1210: cublasGemmEx / cuBLASLt FP8
+// [tokens,2816] x [128,2816]^T -> bf16 [tokens,128], followed by
+// route_128_top8_kernel<<<tokens,128>>>).  Here both are one kernel and the logits never
+// reach HBM: tokens sit on MMA-M (128 per tile), the 128 experts on MMA-N, K = 2816.
+//
+// A tile's K range is split over a cluster of four CTAs, so a 4096-token batch runs on 128 SMs
+// and a decode-sized batch streams the router matrix through four SMs instead of one.  Each
+// CTA accumulates its K slice in tensor memory (tcgen05.mma kind::f16 for bf16 operands,
+// kind::f8f6f4 for E4M3), copies the 128 x 128 fp32 partial sums to its shared memory, and
+// after a cluster barrier CTA q sums the four partials of rows [32q, 32q+32) in rank order
+// through distributed shared memory (a fixed order: results do not depend on timing), adds the
+// optional per-expert bias, rounds to bf16 as the GEMM would have stored it, and runs the
+// warp-per-token top-8 + softmax of gv_route.cuh.
+//
+// Roles per CTA: warp 0 TMA producer, warp 1 MMA issuer and owner of tensor memory, warps
+// 2..5 epilogue (thread = accumulator row).  Every mbarrier wait is bounded (status word
+// kWaitTimeout); the two cluster barriers are reached by every thread whatever happened before.
+#include "gv_common.cuh"
+#include "gv_launchers.h"
+#include "gv_route.cuh"
+
+namespace gv {
+
+namespace {
+
+constexpr int kRpSplit = 4;      // CTAs per cluster = K slices per token tile
+constexpr int kRpStages = 4;
+constexpr int kRpThreads = 192;
+constexpr int kRpTileBytes = kTileM * kTileKBytes;  // 16 KiB: 128 rows of one 128-byte K block
+constexpr int kRpLogitStride = kExperts + 8;        // bf16 elements per staged logits row
+
+struct alignas(1024) RouterSmem {
+  uint8_t a[kRpStages][kRpTileBytes];
+  uint8_t b[kRpStages][kRpTileBytes];
+  // This CTA's partial sums: row r, 16-byte chunk c (four columns) at chunk position c ^ (r & 31),
+  // which keeps both the row-wise writes and the reduce's reads free of bank conflicts.
+  float partial[kTileM * kExperts];
+  alignas(16) uint16_t logits[32][kRpLogitStride];
+  uint64_t full[kRpStages];
+  uint64_t empty[kRpStages];
+  uint64_t acc_full;
+  uint32_t tmem_base;
+  volatile int abort;
+};
+
+constexpr size_t kRpSmemBytes = sizeof(RouterSmem) + 1024;
+static_assert(kRpSmemBytes <= 232448, "shared memory budget of one sm_100 CTA");
+
+struct RouterParams {
+  const float* bias;                   // optional f32 [128], added before the bf16 rounding
+  const __nv_bfloat16* expert_scale;   // bf16 [128]
+  float* weights;                      // f32 [tokens, 8]
+  int* ids;                            // i32 [tokens, 8]
+  __nv_bfloat16* logits_out;           // optional bf16 [tokens, 128]
+  const float* activation_scales;      // E4M3 form: f32 [tokens]
+  const float* weight_scale;           // E4M3 form: f32 [1]
+  int* status;                         // optional device status word
+  int tokens;
+  int k_blocks;                        // 128-byte K blocks per row
+};
+
+// Instruction descriptors: fp32 accumulate (bit 4), both operands K-major, N at [17,23) in units
+// of 8, M at [24,29) in units of 16; operand formats at [7,10) and [10,13): BF16 = 1 in
+// kind::f16, E4M3 = 0 in kind::f8f6f4.
+constexpr uint32_t kIdescBase = (1u << 4) | (static_cast<uint32_t>(kExperts >> 3) << 17) |
+                                (static_cast<uint32_t>(kTileM >> 4) << 24);
+constexpr uint32_t kIdescBf16 = kIdescBase | (1u << 7) | (1u << 10);
+constexpr uint32_t kIdescE4m3 = kIdescBase;
+
+// The four MMAs of one 128-byte K block (K = 16 bf16 or 32 E4M3 values each, 32 bytes apart).
+template <bool kFp8>
+__device__ __forceinline__ void issue_router_k_block(uint32_t tmem_acc, uint32_t a_lo, uint32_t b_lo,
+                                                     uint32_t accumulate) {
+  constexpr uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // 8 rows x 128 B groups, 128B swizzle
+#define GV_RP_MMA(kind, j, pred)                                     \
+  "add.u32 lo, %1, " #j "*2;\n\t"                                    \
+  "mov.b64 d0, {lo, %3};\n\t"                                        \
+  "add.u32 lo, %2, " #j "*2;\n\t"                                    \
+  "mov.b64 d1, {lo, %3};\n\t"                                        \
+  "tcgen05.mma.cta_group::1.kind::" kind " [%0], d0, d1, %4, " pred ";\n\t"
+#define GV_RP_BLOCK(kind)                                                                            \
+  asm volatile("{\n\t.reg .pred p, pt;\n\t.reg .b32 lo;\n\t.reg .b64 d0, d1;\n\t"                     \
+               "setp.ne.b32 p, %5, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"                                   \
+               GV_RP_MMA(kind, 0, "p") GV_RP_MMA(kind, 1, "pt") GV_RP_MMA(kind, 2, "pt")              \
+               GV_RP_MMA(kind, 3, "pt") "}"                                                           \
+               ::"r"(tmem_acc), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(kFp8 ? kIdescE4m3 : kIdescBf16),    \
+                 "r"(accumulate)                                                                      \
+               : "memory")
+  if constexpr (kFp8) {
+    GV_RP_BLOCK("f8f6f4");
+  } else {
+    GV_RP_BLOCK("f16");
+  }
+#undef GV_RP_BLOCK
+#undef GV_RP_MMA
+}
+
+template <bool kFp8>
+__global__ void __launch_bounds__(kRpThreads, 1)
+route_project_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                     const RouterParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  RouterSmem* smem = reinterpret_cast<RouterSmem*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();
+  const int m_tile = static_cast<int>(blockIdx.x) / kRpSplit;
+  const int kb_begin = static_cast<int>(rank) * p.k_blocks / kRpSplit;
+  const int kb_end = (static_cast<int>(rank) + 1) * p.k_blocks / kRpSplit;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kRpStages; ++s) {
+      mbar_init(&smem->full[s], 1);
+      mbar_init(&smem->empty[s], 1);
+    }
+    mbar_init(&smem->acc_full, 1);
+    smem->abort = 0;
+    fence_barrier_init();
+    prefetch_tensor_map(&map_x);
+    prefetch_tensor_map(&map_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(&smem->tmem_base, kExperts);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = smem->tmem_base;
+  grid_dependency_wait();  // a no-op unless launched behind a predecessor with programmatic serialization
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    int stage = 0;
+    uint32_t phase = 0;
+    int issued = 0;
+    bool ok = true;
+    for (int kb = kb_begin; kb < kb_end; ++kb) {
+      ok = __all_sync(0xffffffffu, wait_or_abort<true>(&smem->empty[stage], phase ^ 1u, smem, p.status));
+      if (!ok) break;
+      if (elect_one()) {
+        mbar_arrive_expect_tx(&smem->full[stage], 2u * kRpTileBytes);
+        tma_load_2d(smem->a[stage], &map_x, &smem->full[stage], kb * kTileKBytes, m_tile * kTileM);
+        tma_load_2d(smem->b[stage], &map_w, &smem->full[stage], kb * kTileKBytes, 0);
+      }
+      __syncwarp();
+      ++issued;
+      if (++stage == kRpStages) {
+        stage = 0;
+        phase ^= 1u;
+      }
+    }
+    if (!ok && lane == 0) {
+      // let the copies already issued land before shared memory is given up
+      const int pending = issued < kRpStages ? issued : kRpStages;
+      int s = stage;
+      uint32_t ph = phase;
+      for (int i = 0; i < pending; ++i) {
+        if (--s < 0) {
+          s = kRpStages - 1;
+          ph ^= 1u;
+        }
+        mbar_wait_bounded(&smem->full[s], ph, 40000000ll);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    int stage = 0;
+    uint32_t phase = 0;
+    const uint32_t a_lo0 = (smem_u32(smem->a[0]) & 0x3ffffu) >> 4;
+    const uint32_t b_lo0 = (smem_u32(smem->b[0]) & 0x3ffffu) >> 4;
+    const bool leader = elect_one();
+    for (int kb = kb_begin; kb < kb_end; ++kb) {
+      if (!wait_or_abort<false>(&smem->full[stage], phase, smem, p.status)) break;
+      if (leader) {
+        issue_router_k_block<kFp8>(tmem_base, a_lo0 + static_cast<uint32_t>(stage) * (kRpTileBytes >> 4),
+                                   b_lo0 + static_cast<uint32_t>(stage) * (kRpTileBytes >> 4),
+                                   kb != kb_begin ? 1u : 0u);
+        tc_commit(&smem->empty[stage]);
+        if (kb + 1 == kb_end) tc_commit(&smem->acc_full);
+      }
+      if (++stage == kRpStages) {
+        stage = 0;
+        phase ^= 1u;
+      }
+    }
+  } else {
+    // ---------------- epilogue, part 1: partial sums to shared memory ----------------
+    const int quarter = warp & 3;  // the tensor-memory lanes this warp may read
+    const int row = quarter * 32 + lane;
+    if (wait_or_abort<true>(&smem->acc_full, 0, smem, p.status)) {
+      tc_fence_after_sync();
+      float* row_base = smem->partial + row * kExperts;
+#pragma unroll 1
+      for (int part = 0; part < 4; ++part) {
+        uint32_t r[32];
+        tmem_load_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + part * 32, r);
+        tmem_load_wait();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int chunk = part * 8 + i;
+          *reinterpret_cast<uint4*>(row_base + ((chunk ^ lane) << 2)) =
+              make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+        }
+      }
+      tc_fence_before_sync();
+    }
+  }
+
+  // Every thread of every CTA of the cluster arrives here, also after a failed wait.
+  cluster_sync_all();
+
+  if (warp >= 2 && !smem->abort) {
+    // ---------------- epilogue, part 2: reduce rows [32*rank, 32*rank+32) and route ----------------
+    const int t = threadIdx.x - 64;
+    const int row_local = t >> 2;
+    const int column_quarter = t & 3;
+    const int row = static_cast<int>(rank) * 32 + row_local;
+    const uint32_t local_row = smem_u32(smem->partial + row * kExperts);
+    float4 acc[8];
+#pragma unroll
+    for (int source = 0; source < kRpSplit; ++source) {
+      const uint32_t remote_row = cluster_map_shared(local_row, static_cast<uint32_t>(source));
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int chunk = column_quarter * 8 + i;
+        const float4 v = cluster_load_float4(remote_row + (static_cast<uint32_t>(chunk ^ row_local) << 4));
+        if (source == 0) {
+          acc[i] = v;
+        } else {
+          acc[i].x = __fadd_rn(acc[i].x, v.x);
+          acc[i].y = __fadd_rn(acc[i].y, v.y);
+          acc[i].z = __fadd_rn(acc[i].z, v.z);
+          acc[i].w = __fadd_rn(acc[i].w, v.w);
+        }
+      }
+    }
+    uint32_t packed[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float4 v = acc[i];
+      if (p.bias) {
+        const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias) + column_quarter * 8 + i);
+        v.x = __fadd_rn(v.x, b.x);
+        v.y = __fadd_rn(v.y, b.y);
+        v.z = __fadd_rn(v.z, b.z);
+        v.w = __fadd_rn(v.w, b.w);
+      }
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y);
+      const __nv_bfloat162 hi = __floats2bfloat162_rn(v.z, v.w);
+      packed[2 * i] = *reinterpret_cast<const uint32_t*>(&lo);
+      packed[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+    }
+    uint4* staged = reinterpret_cast<uint4*>(&smem->logits[row_local][column_quarter * 32]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      staged[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+    named_barrier(1, 128);
+    // one warp per token: this warp's eight rows
+    const int first = (warp - 2) * 8;
+#pragma unroll 1
+    for (int i = 0; i < 8; ++i) {
+      const int token = m_tile * kTileM + static_cast<int>(rank) * 32 + first + i;
+      if (token >= p.tokens) break;
+      const uint2 raw = *reinterpret_cast<const uint2*>(&smem->logits[first + i][4 * lane]);
+      if (p.logits_out)
+        *reinterpret_cast<uint2*>(p.logits_out + static_cast<size_t>(token) * kExperts + 4 * lane) = raw;
+      float value[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                        __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u)};
+      if (kFp8) {
+        // the reference's rescale of an unscaled FP8 GEMM output (routing_sampling.cuh:408-411)
+        const float rescale = __fmul_rn(p.activation_scales[token], p.weight_scale[0]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) value[j] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(value[j], rescale)));
+      }
+      route_top8_of_row(value, lane, p.expert_scale, p.weights + static_cast<size_t>(token) * kTopK,
+                        p.ids + static_cast<size_t>(token) * kTopK);
+    }
+  }
+
+  // No CTA may leave while a peer still reads its partial sums.
+  tc_fence_before_sync();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    __syncwarp();
+    tmem_dealloc(tmem_base, kExperts);
+  }
+}
+
+template <bool kFp8>
+cudaError_t launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_w, const RouterParams& p,
+                           cudaStream_t stream) {
+  static bool prepared[64] = {};
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return e;
+  if (device >= 0 && device < 64 && !prepared[device]) {
+    e = cudaFuncSetAttribute(route_project_kernel<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(kRpSmemBytes));
+    if (e != cudaSuccess) return e;
+    prepared[device] = true;
+  }
+  const int m_tiles = (p.tokens + kTileM - 1) / kTileM;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(static_cast<unsigned>(m_tiles * kRpSplit));
+  config.blockDim = dim3(kRpThreads);
+  config.dynamicSmemBytes = kRpSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = kRpSplit;
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, route_project_kernel<kFp8>, map_x, map_w, p);
+}
+
+}  // namespace
+
+int launch_route_project(const void* x, const void* router_w, bool fp8, const float* bias,
+                         const void* expert_scale_bf16, float* weights, int* ids, void* logits_out,
+                         const float* activation_scales, const float* weight_scale, int tokens, int* status,
+                         cudaStream_t stream) {
+  const uint64_t row_bytes = fp8 ? kHidden : 2 * kHidden;
+  CUtensorMap map_x, map_w;
+  if (!make_operand_tensor_map(&map_x, x, static_cast<uint64_t>(tokens), row_bytes, kTileM) ||
+      !make_operand_tensor_map(&map_w, router_w, kExperts, row_bytes, kTileM))
+    return static_cast<int>(cudaErrorInvalidValue);
+  RouterParams p{};
+  p.bias = bias;
+  p.expert_scale = static_cast<const __nv_bfloat16*>(expert_scale_bf16);
+  p.weights = weights;
+  p.ids = ids;
+  p.logits_out = static_cast<__nv_bfloat16*>(logits_out);
+  p.activation_scales = activation_scales;
+  p.weight_scale = weight_scale;
+  p.status = status;
+  p.tokens = tokens;
+  p.k_blocks = static_cast<int>(row_bytes / kTileKBytes);
+  const cudaError_t e = fp8 ? launch_variant<true>(map_x, map_w, p, stream)
+                            : launch_variant<false>(map_x, map_w, p, stream);
+  return static_cast<int>(e);
+}
+
+}  // namespace gv

@@ -255,6 +255,49 @@ def route_128_top8(logits, expert_scale, activation_scales=None, projection_weig
     return weights, ids
 
 
+def route_project(router_input, router_weight, expert_scale, bias=None, want_logits=False, status_of=None,
+                  activation_scales=None, weight_scale=None, weights=None, ids=None, stream=None):
+    """Router projection and routing in one kernel (gevva_moe_route_project): what the reference
+    does with a library GEMM followed by route_128_top8_kernel (src/cuda/runtime/prefill.cuh:414-422).
+
+    router_input bf16 [rows, 2816] and router_weight bf16 [128, 2816]; or, with activation_scales
+    f32 [rows] and weight_scale f32 [1], both as E4M3 bytes (uint8) for the FP8 sidecar's router.
+    bias: optional f32 [128].  status_of: a runner whose status word receives a wait timeout.
+    Returns (weights f32 [rows,8], ids int32 [rows,8]) and, with want_logits, the bf16 logits."""
+    rows = router_input.shape[0]
+    fp8 = activation_scales is not None
+    dtype = torch.uint8 if fp8 else torch.bfloat16
+    _check(router_input, dtype, (rows, HIDDEN), "router_input")
+    _check(router_weight, dtype, (EXPERTS, HIDDEN), "router_weight")
+    _check(expert_scale, torch.bfloat16, (EXPERTS,), "expert_scale")
+    device = router_input.device
+    if weights is None:
+        weights = torch.empty((rows, TOP_K), dtype=torch.float32, device=device)
+    if ids is None:
+        ids = torch.empty((rows, TOP_K), dtype=torch.int32, device=device)
+    logits = torch.empty((rows, EXPERTS), dtype=torch.bfloat16, device=device) if want_logits else None
+    lib = library()
+    vp, i32 = ctypes.c_void_p, ctypes.c_int
+    lib.gevva_moe_route_project.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, vp, vp]
+    lib.gevva_moe_route_project_fp8.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp]
+    lib.gevva_moe_status_word.argtypes = [vp]
+    lib.gevva_moe_status_word.restype = vp
+    status_word = vp(lib.gevva_moe_status_word(status_of._handle)) if status_of is not None else vp(0)
+    with torch.cuda.device(device):
+        if fp8:
+            status = lib.gevva_moe_route_project_fp8(
+                _ptr(router_input), _ptr(activation_scales), _ptr(router_weight), _ptr(weight_scale),
+                _ptr(expert_scale), _ptr(weights), _ptr(ids), _ptr(logits), rows, status_word,
+                _stream_handle(stream))
+        else:
+            status = lib.gevva_moe_route_project(
+                _ptr(router_input), _ptr(router_weight), _ptr(bias), _ptr(expert_scale), _ptr(weights),
+                _ptr(ids), _ptr(logits), rows, status_word, _stream_handle(stream))
+    if status != 0:
+        raise GevvaMoeError(status, "route_project")
+    return (weights, ids, logits) if want_logits else (weights, ids)
+
+
 def pack_experts(weights_fp32, stream=None):
     """fp32 [experts, N, K] -> (codes u8 [E,N,K/2], scales u8 [E,N,K/16], global f32 [E])."""
     experts, n_out, k_in = weights_fp32.shape

@@ -81,6 +81,34 @@ int gevva_moe_route(const void* logits_bf16, int ld, const void* expert_scale_bf
                     int* ids, int tokens, const float* act_scales, const float* w_scale,
                     gevva_stream_t stream);
 
+/* Replaces the pair "router projection GEMM, then route_128_top8_kernel"
+ * (src/cuda/runtime/prefill.cuh:414-422, :1203-1210: cublasGemmEx bf16 with fp32 compute, output
+ * bf16 [tokens,128], src/cuda/runtime/prefill.cuh:196-200) by one kernel; the logits stay on chip.
+ *   router_input bf16 [tokens,2816], router_weight bf16 [128,2816] (both 16-byte aligned),
+ *   bias optional f32 [128] (added in fp32 before the bf16 rounding; the reference has none, the
+ *   benchmark's skewed-load configurations use it), expert_scale bf16 [128],
+ *   weights f32 [tokens,8], ids i32 [tokens,8], logits_out optional bf16 [tokens,128].
+ * logit = bf16(sum_k x*w + bias) with fp32 accumulation over four K slices summed in a fixed order,
+ * so results are repeatable; against an fp32 dot product in another order a logit may differ by
+ * one bf16 ulp, as between any two GEMM implementations.  device_status: optional device status
+ * word (e.g. gevva_moe_status_word) that receives GEVVA_MOE_WAIT_TIMEOUT if a bounded wait expires. */
+int gevva_moe_route_project(const void* router_input_bf16, const void* router_weight_bf16, const float* bias,
+                            const void* expert_scale_bf16, float* weights, int* ids, void* logits_out,
+                            int tokens, int* device_status, gevva_stream_t stream);
+
+/* The same for the FP8 sidecar's router (Fp8LinearRunner::launch_unscaled with unit scales, then the
+ * router kernel's rescale: src/cuda/runtime/fp8_linear.cuh:215-473, routing_sampling.cuh:405-411):
+ * router_input e4m3 [tokens,2816] with activation_scales f32 [tokens], router_weight e4m3 [128,2816]
+ * with weight_scale f32 [1]; logits_out receives the UNSCALED bf16 logits. */
+int gevva_moe_route_project_fp8(const void* router_input_e4m3, const float* activation_scales,
+                                const void* router_weight_e4m3, const float* weight_scale,
+                                const void* expert_scale_bf16, float* weights, int* ids, void* logits_out,
+                                int tokens, int* device_status, gevva_stream_t stream);
+
+/* Device pointer of the runner's status word, for kernels launched outside the runner that should
+ * report into it (read and cleared by gevva_moe_last_status). */
+int* gevva_moe_status_word(gevva_moe* runner);
+
 /* Replaces Nvfp4ExpertRunner::launch / launch_batch / launch_batch_unreduced
  * (src/nvfp4_cutlass.cu:1893-1913 -> Impl::launch :1827-1886).
  * in bf16 [tokens,2816]; ids i32 [tokens,8]; route_weights f32 [tokens,8];

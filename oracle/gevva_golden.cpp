@@ -177,6 +177,36 @@ float gvo_expf(float v) { return gv_expf(v); }
 float gvo_gelu(float v) { return gv_gelu_erf(v, &gv_erf_table_host[0][0]); }
 size_t gvo_sf_offset(int row, int group, int groups) { return sf_offset(row, group, groups); }
 
+// ---- a1: router projection, src/cuda/runtime/prefill.cuh:196-200 (cublasGemmEx, bf16 operands,
+// fp32 compute, bf16 output [tokens,128]) and its call at :414-419.  The dot product is taken in
+// double and rounded once to fp32, so this is the value every fp32-accumulating GEMM approximates;
+// `bias` (optional, f32 [128]) is the benchmark's per-expert load skew, added before the bf16
+// rounding.  With e4m3 != 0 the operands are E4M3 bytes and the result is the unscaled logit
+// (Fp8LinearRunner::launch_unscaled, src/cuda/runtime/fp8_linear.cuh:215-473).
+void gvo_router_logits(const void* input, const void* router, const float* bias, int tokens, int width,
+                       int e4m3, uint16_t* logits) {
+#pragma omp parallel for schedule(static)
+  for (int row = 0; row < tokens; ++row) {
+    for (int expert = 0; expert < kExperts; ++expert) {
+      double sum = 0.0;
+      for (int k = 0; k < width; ++k) {
+        float a, b;
+        if (e4m3) {
+          a = decode_e4m3(static_cast<const uint8_t*>(input)[static_cast<size_t>(row) * width + k]);
+          b = decode_e4m3(static_cast<const uint8_t*>(router)[static_cast<size_t>(expert) * width + k]);
+        } else {
+          a = bf16_to_float(static_cast<const uint16_t*>(input)[static_cast<size_t>(row) * width + k]);
+          b = bf16_to_float(static_cast<const uint16_t*>(router)[static_cast<size_t>(expert) * width + k]);
+        }
+        sum += static_cast<double>(a) * static_cast<double>(b);
+      }
+      float value = static_cast<float>(sum);
+      if (bias) value += bias[expert];
+      logits[static_cast<size_t>(row) * kExperts + expert] = float_to_bf16(value);
+    }
+  }
+}
+
 // ---- a2: router, src/cuda/kernels/routing_sampling.cuh:396-431 ---------------
 // logits bf16 [tokens, ld>=128]; expert_scale bf16 [128]; optional FP8 rescale.
 void gvo_route(const uint16_t* logits, int ld, const uint16_t* expert_scale, float* weights,

@@ -63,6 +63,17 @@ class Oracle:
                            _p(weights), _p(ids), ctypes.c_int(tokens), _p(act_scales), _p(w_scale))
         return weights, ids
 
+    def router_logits(self, x, router, bias=None, e4m3=False):
+        """x [tokens, 2816] and router [128, 2816] as bf16 bit patterns (uint16) or, with e4m3,
+        as E4M3 bytes; returns bf16 logits [tokens, 128] as bit patterns."""
+        tokens, width = x.shape
+        logits = np.zeros((tokens, EXPERTS), np.uint16)
+        bias = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+        self.lib.gvo_router_logits(_p(np.ascontiguousarray(x)), _p(np.ascontiguousarray(router)), _p(bias),
+                                   ctypes.c_int(tokens), ctypes.c_int(width), ctypes.c_int(1 if e4m3 else 0),
+                                   _p(logits))
+        return logits
+
     def sort(self, ids):
         flat = np.ascontiguousarray(ids, dtype=np.int32).reshape(-1)
         routes = flat.size

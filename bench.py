@@ -104,7 +104,6 @@ def build_layer(device, rank):
     from gevva_b200.synthetic import SyntheticLayer
     layer = SyntheticLayer(seed=0, max_tokens=TOKENS, device=device, bias_std=0.5)
     layer.calibrate(layer.inputs(TOKENS, seed=1000))
-    layer.bias_row = layer.bias.to(torch.bfloat16)
     return layer, layer.inputs(TOKENS, seed=1000 + rank)
 
 
@@ -137,8 +136,7 @@ def layer_step(layer, x, out, weights, ids):
     than one GPU the experts are sharded and `layer.ep` exchanges rows over NVLink."""
     import torch
     import gevva_b200
-    logits = torch.addmm(layer.bias_row, x, layer.router_w.t())
-    gevva_b200.route_128_top8(logits, layer.expert_scale, weights=weights, ids=ids)
+    layer.route(x, weights=weights, ids=ids)
     runner = layer.ep if getattr(layer, "ep", None) is not None else layer.runner
     runner.launch_batch(x, ids, weights, out, x.shape[0])
 
@@ -161,8 +159,8 @@ def decode_sweep(layer, device, steps):
         distinct = []
 
         def step(x):
-            logits = torch.matmul(x, layer.router_w.t())
-            gevva_b200.route_128_top8(logits, layer.expert_scale, weights=weights, ids=ids)
+            gevva_b200.route_project(x, layer.router_w, layer.expert_scale, weights=weights, ids=ids,
+                                     status_of=runner)
             runner.launch_batch(x, ids, weights, out, tokens)
 
         graphs = []
@@ -212,8 +210,7 @@ def decode_eager(layer, device, tokens, steps):
     ids = torch.empty((tokens, TOP_K), dtype=torch.int32, device=device)
     for i in range(steps):
         x = layer.inputs(tokens, seed=7000 + i)
-        logits = torch.matmul(x, layer.router_w.t())
-        gevva_b200.route_128_top8(logits, layer.expert_scale, weights=weights, ids=ids)
+        gevva_b200.route_project(x, layer.router_w, layer.expert_scale, weights=weights, ids=ids, status_of=runner)
         runner.launch_batch(x, ids, weights, out, tokens)
     torch.cuda.synchronize()
     runner.check()
@@ -326,7 +323,7 @@ def run_gpu(args):
         # Experts are placed by load observed on a calibration batch (other tokens than the timed
         # ones, same router): most loaded first, each to the least loaded rank with a free slot.
         calibration = layer.inputs(TOKENS, seed=2000 + rank)
-        _, calibration_ids = gevva_b200.route_128_top8(layer.logits(calibration), layer.expert_scale)
+        _, calibration_ids = layer.route(calibration)
         counts = torch.bincount(calibration_ids.reshape(-1).long(), minlength=EXPERTS)
         dist.all_reduce(counts)
         placement = balanced_placement(counts.tolist(), world)
@@ -414,8 +411,7 @@ def run_gpu(args):
     h1 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     runner = layer.runner
     for i in range(args.steps):
-        logits = torch.addmm(layer.bias_row, x, layer.router_w.t())
-        gevva_b200.route_128_top8(logits, layer.expert_scale, weights=weights, ids=ids)
+        layer.route(x, weights=weights, ids=ids)
         runner.launch_stages(rt.STAGE_SORT | rt.STAGE_QUANTIZE, TOKENS, input=x, expert_ids=ids)
         g0[i].record()
         runner.launch_stages(rt.STAGE_W13 | rt.STAGE_GEGLU, TOKENS)  # one kernel: GeGLU in the epilogue

@@ -7,7 +7,7 @@ from dataclasses import dataclass
 import torch
 
 from .runtime import (EXPERTS, HIDDEN, TOP_K, GevvaMoeError, Nvfp4ExpertRunner, _check, _ptr,
-                      _stream_handle, _view, library, route_128_top8)
+                      _stream_handle, _view, library, route_project)
 
 DENSE = 2112
 
@@ -144,8 +144,7 @@ class FeedForwardLayer:
     def forward(self, hidden, aux_stream=None):
         tokens = hidden.shape[0]
         dense_in, expert_in, router_in = ff_prepare(hidden, self.dense_pre, self.expert_pre, self.router_scale)
-        logits = torch.matmul(router_in, self.router_w.t())
-        weights, ids = route_128_top8(logits, self.expert_scale)
+        weights, ids = route_project(router_in, self.router_w, self.expert_scale, status_of=self.experts)
         main = torch.cuda.current_stream()
         if aux_stream is not None:
             aux_stream.wait_stream(main)

@@ -15,7 +15,7 @@ import torch
 
 from .runtime import (EXPERTS, HIDDEN, INTER, STAGE_QUANTIZE, STAGE_SORT, STAGE_W13, TOP_K,
                       W13_OUT, BUF_W13_OUT, ExpertWeights, Nvfp4ExpertRunner, pack_experts,
-                      route_128_top8)
+                      route_128_top8, route_project)
 
 
 def _randn(shape, std, generator, device):
@@ -84,10 +84,16 @@ class SyntheticLayer:
         return torch.randn((tokens, HIDDEN), generator=gen, device=self.device,
                            dtype=torch.float32).to(torch.bfloat16)
 
+    def route(self, x, weights=None, ids=None, want_logits=False, runner=None):
+        """Router projection, per-expert bias (the model of uneven expert load), top-8 and
+        softmax in one kernel of the library (gevva_moe_route_project)."""
+        return route_project(x, self.router_w, self.expert_scale, bias=self.bias, want_logits=want_logits,
+                             status_of=runner if runner is not None else self.runner, weights=weights, ids=ids)
+
     def logits(self, x):
-        """Router projection: a plain library GEMM, as in the reference
-        (src/cuda/runtime/prefill.cuh:414-419); the optional per-expert bias models
-        uneven expert load."""
+        """Router logits by a plain library GEMM, as the reference computes them
+        (src/cuda/runtime/prefill.cuh:414-419), for tests that hand identical logits to the
+        library and to the oracle; the optional per-expert bias models uneven expert load."""
         out = torch.matmul(x, self.router_w.t())
         if self.bias is not None:
             out = (out.float() + self.bias).to(torch.bfloat16)
@@ -129,7 +135,7 @@ class SyntheticLayer:
     def forward(self, x, out=None):
         """Router projection -> route -> experts; returns bf16 [tokens, 2816]."""
         tokens = x.shape[0]
-        weights, ids = route_128_top8(self.logits(x), self.expert_scale)
+        weights, ids = self.route(x)
         if out is None:
             out = torch.empty_like(x)
         self.runner.launch_batch(x, ids, weights, out, tokens)

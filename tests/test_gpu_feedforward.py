@@ -134,8 +134,10 @@ def test_layer_wiring_against_oracle(oracle, dense_oracle, dense_weights, cuda_d
     torch.cuda.synchronize()
     # CPU chain
     dense_in, expert_in, router_in = dense_oracle.ff_prepare(bits(hidden), bits(dw), bits(ew), bits(rs))
-    logits = torch.matmul(torch.from_numpy(router_in.view(np.int16)).to(cuda_device).view(torch.bfloat16),
-                          router_w.t())
+    # the library's own logits (fused projection, deterministic), so that both sides route alike
+    _, _, logits = gm.route_project(torch.from_numpy(router_in.view(np.int16)).to(cuda_device).view(torch.bfloat16),
+                                    router_w, torch.ones(EXPERTS, dtype=torch.bfloat16, device=cuda_device),
+                                    want_logits=True)
     rw, ids = oracle.route(bits(logits), bits(torch.ones(EXPERTS, dtype=torch.bfloat16)))
     hw = dict(w13=p["w13"].cpu().numpy(), w13_sf=p["w13_sf"].cpu().numpy(), w2=p["w2"].cpu().numpy(),
               w2_sf=p["w2_sf"].cpu().numpy(), alpha1=w.alpha1.cpu().numpy(), alpha2=w.alpha2.cpu().numpy(),

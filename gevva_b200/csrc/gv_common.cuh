@@ -284,6 +284,14 @@ __device__ __forceinline__ uint32_t cluster_map_shared(uint32_t local_address, u
   return remote;
 }
 
+// Posted store into the shared memory of a CTA of the cluster; visible to that CTA after the next
+// cluster barrier.
+__device__ __forceinline__ void cluster_store_uint4(uint32_t cluster_address, uint4 v) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_address), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
 __device__ __forceinline__ float4 cluster_load_float4(uint32_t cluster_address) {
   float4 v;
   asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"

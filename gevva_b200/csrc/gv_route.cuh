@@ -1,71 +1,98 @@
 // Top-8 of a token's 128 router logits, softmax over the eight, per-expert scale: the body of
 // the router kernel, shared by the stand-alone launch and by the fused projection kernel.
 // Reference: route_128_top8_kernel, src/cuda/kernels/routing_sampling.cuh:396-431 (a 128-thread
-// CTA and a CUB radix sort per token).  Here one warp owns one token: lane l holds the logits of
-// experts 4l..4l+3, and eight rounds of redux.sync pick the maxima in the order a stable
-// descending radix sort would (ties keep the lower expert index, -0 sorts as +0).
+// CTA and a CUB radix sort per token).
+//
+// Here four adjacent lanes (a quad) own one token, 32 logits each.  A lane keeps the eight
+// largest of its 32 in registers (a branch-free insertion network), then the quad merges its four
+// sorted lists in eight rounds of two shuffles.  Order is that of a stable descending radix sort
+// on the float keys: every logit is a bf16 value, so its order is carried by 16 bits, and the
+// composite (key16 << 7 | 127 - expert) makes ties fall to the lower expert index and all
+// composites distinct; -0 sorts as +0.  (A warp-wide redux.sync arg-max per round, the earlier
+// form, cost about 200 cycles per round and token.)
 #pragma once
 
 #include "gv_common.cuh"
 
 namespace gv {
 
-__device__ __forceinline__ uint32_t radix_key(float value) {
-  uint32_t bits = __float_as_uint(value);
-  if (bits == 0x80000000u) bits = 0;  // -0 sorts as +0
-  return (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+// Order-preserving 16-bit key of a bf16 bit pattern (larger value -> larger key).
+__device__ __forceinline__ uint32_t route_key16(uint32_t bf16_bits) {
+  if (bf16_bits == 0x8000u) bf16_bits = 0;  // -0 sorts as +0
+  return (bf16_bits & 0x8000u) ? (~bf16_bits & 0xffffu) : (bf16_bits | 0x8000u);
 }
 
-// All 32 lanes of a warp call this with the same row; lanes 0..7 write the row's results.
-__device__ __forceinline__ void route_top8_of_row(const float (&value)[4], int lane,
-                                                  const __nv_bfloat16* __restrict__ expert_scale,
-                                                  float* __restrict__ weights_row, int* __restrict__ ids_row) {
-  uint32_t key[4];
+__device__ __forceinline__ float route_value_of_key16(uint32_t key16) {
+  const uint32_t bf16_bits = (key16 & 0x8000u) ? (key16 & 0x7fffu) : (~key16 & 0xffffu);
+  return __uint_as_float(bf16_bits << 16);
+}
+
+// The four lanes of a quad (lanes 4q..4q+3 of a warp, `part` = lane & 3) call this together.
+// `packed` holds this lane's 32 logits as bf16 pairs: experts 32*part + 2i (low half) and
+// 32*part + 2i + 1 (high half) in packed[i].  With `rescale` the key of a logit is
+// bf16(logit * rescale) (the FP8 router's per-row scale, routing_sampling.cuh:405-411).
+// Every lane must call (shuffles use the full mask); a quad whose token does not exist passes
+// valid = false and writes nothing.  Lane `part` writes results 2*part and 2*part + 1.
+__device__ __forceinline__ void route_top8_quad(const uint32_t (&packed)[16], int part, bool use_rescale,
+                                                float rescale, bool valid,
+                                                const __nv_bfloat16* __restrict__ expert_scale,
+                                                float* __restrict__ weights_row, int* __restrict__ ids_row) {
+  uint32_t top[kTopK];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) key[j] = radix_key(value[j]);
-  uint32_t taken = 0;
-  int my_id = 0;
-  float my_key = 0.0f;
-#pragma unroll 1
-  for (int round = 0; round < kTopK; ++round) {
-    uint32_t best_key = 0;
-    uint32_t best_index = 0xffffffffu;
+  for (int k = 0; k < kTopK; ++k) top[k] = 0;  // the empty marker: below every real composite (those are >= 1)
 #pragma unroll
-    for (int j = 3; j >= 0; --j) {
-      if (!((taken >> j) & 1u) && key[j] >= best_key) {  // descending j: ties keep the lower index
-        best_key = key[j];
-        best_index = 4u * lane + j;
-      }
+  for (int i = 0; i < 32; ++i) {
+    uint32_t bits = (i & 1) ? (packed[i >> 1] >> 16) : (packed[i >> 1] & 0xffffu);
+    if (use_rescale) {
+      const float scaled = __fmul_rn(__uint_as_float(bits << 16), rescale);
+      bits = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(scaled)));
     }
-    const uint32_t top_key = __reduce_max_sync(0xffffffffu, best_key);
-    const uint32_t candidate = (best_index != 0xffffffffu && best_key == top_key) ? best_index
-                                                                                  : 0xffffffffu;
-    const uint32_t winner = __reduce_min_sync(0xffffffffu, candidate);
-    const int owner = static_cast<int>(winner >> 2);
-    const int slot = static_cast<int>(winner & 3u);
-    float v = value[0];
-    v = slot == 1 ? value[1] : v;
-    v = slot == 2 ? value[2] : v;
-    v = slot == 3 ? value[3] : v;
-    v = __shfl_sync(0xffffffffu, v, owner);
-    if (lane == owner) taken |= 1u << slot;
-    if (lane == round) {
-      my_id = static_cast<int>(winner);
-      my_key = v;
+    // +1 keeps every real composite above the empty marker 0
+    uint32_t c = ((route_key16(bits) << 7) | static_cast<uint32_t>(127 - (32 * part + i))) + 1u;
+    // insert into the descending list: after the pass top[] holds the eight largest so far
+#pragma unroll
+    for (int k = 0; k < kTopK; ++k) {
+      const uint32_t hi = max(top[k], c);
+      c = min(top[k], c);
+      top[k] = hi;
     }
   }
-  const float maximum = __shfl_sync(0xffffffffu, my_key, 0);
-  const float e = lane < kTopK ? gv_expf(__fsub_rn(my_key, maximum)) : 0.0f;
-  float ek[kTopK];
+  // merge the four sorted lists: in every round the largest head wins and its list advances
+  uint32_t winner[kTopK];
 #pragma unroll
-  for (int k = 0; k < kTopK; ++k) ek[k] = __shfl_sync(0xffffffffu, e, k);
+  for (int round = 0; round < kTopK; ++round) {
+    const uint32_t head = top[0];
+    uint32_t best = max(head, __shfl_xor_sync(0xffffffffu, head, 1));
+    best = max(best, __shfl_xor_sync(0xffffffffu, best, 2));
+    winner[round] = best;
+    if (head == best) {
+#pragma unroll
+      for (int k = 0; k + 1 < kTopK; ++k) top[k] = top[k + 1];
+      top[kTopK - 1] = 0;
+    }
+  }
+  float value[kTopK];
+  int id[kTopK];
+#pragma unroll
+  for (int k = 0; k < kTopK; ++k) {
+    const uint32_t c = winner[k] - 1u;
+    id[k] = 127 - static_cast<int>(c & 127u);
+    value[k] = route_value_of_key16(c >> 7);
+  }
+  float e[kTopK];
+#pragma unroll
+  for (int k = 0; k < kTopK; ++k) e[k] = gv_expf(__fsub_rn(value[k], value[0]));
   // Same association as the reference's shuffle-down tree over lanes 0..7.
-  const float denominator =
-      __fadd_rn(__fadd_rn(__fadd_rn(ek[0], ek[4]), __fadd_rn(ek[2], ek[6])),
-                __fadd_rn(__fadd_rn(ek[1], ek[5]), __fadd_rn(ek[3], ek[7])));
-  if (lane < kTopK) {
-    ids_row[lane] = my_id;
-    weights_row[lane] = __fmul_rn(__fdiv_rn(e, denominator), __bfloat162float(expert_scale[my_id]));
+  const float denominator = __fadd_rn(__fadd_rn(__fadd_rn(e[0], e[4]), __fadd_rn(e[2], e[6])),
+                                      __fadd_rn(__fadd_rn(e[1], e[5]), __fadd_rn(e[3], e[7])));
+  if (valid) {
+#pragma unroll
+    for (int k = 0; k < kTopK; ++k) {
+      if ((k >> 1) == part) {
+        ids_row[k] = id[k];
+        weights_row[k] = __fmul_rn(__fdiv_rn(e[k], denominator), __bfloat162float(expert_scale[id[k]]));
+      }
+    }
   }
 }
 

@@ -14,36 +14,44 @@ namespace gv {
 // ---------------------------------------------------------------------------
 // Router: top-8 of 128 logits + softmax over the eight + per-expert scale.
 // Reference: route_128_top8_kernel, src/cuda/kernels/routing_sampling.cuh:396-431
-// (a 128-thread CTA and a full CUB radix sort per token).  Here one warp owns one
-// token: four logits per lane, eight rounds of redux.sync arg-max.
+// (a 128-thread CTA and a full CUB radix sort per token).  Here four lanes own one
+// token (gv_route.cuh): 32 tokens per CTA of 128 threads.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(128)
 route_128_top8_kernel(const __nv_bfloat16* __restrict__ logits, int ld,
                       const __nv_bfloat16* __restrict__ expert_scale, float* __restrict__ weights,
                       int* __restrict__ ids, int rows, const float* __restrict__ activation_scales,
                       const float* __restrict__ projection_weight_scale) {
-  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const int lane = threadIdx.x & 31;
-  const uint16_t* src =
-      reinterpret_cast<const uint16_t*>(logits) + static_cast<size_t>(row) * ld + 4 * lane;
-  float value[4];
-  float rescale = 1.0f;
-  if (activation_scales) rescale = __fmul_rn(activation_scales[row], projection_weight_scale[0]);
+  const int row = blockIdx.x * 32 + (threadIdx.x >> 2);
+  const int part = threadIdx.x & 3;
+  const bool valid = row < rows;
+  const int safe_row = valid ? row : 0;
+  const uint16_t* src = reinterpret_cast<const uint16_t*>(logits) + static_cast<size_t>(safe_row) * ld + 32 * part;
+  uint32_t packed[16];
+  if ((reinterpret_cast<uintptr_t>(logits) & 15) == 0 && (ld & 7) == 0) {
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    float v = bf16_bits_to_float(src[j]);
-    if (activation_scales) v = __bfloat162float(__float2bfloat16_rn(__fmul_rn(v, rescale)));
-    value[j] = v;
+    for (int i = 0; i < 4; ++i) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(src) + i);
+      packed[4 * i] = v.x;
+      packed[4 * i + 1] = v.y;
+      packed[4 * i + 2] = v.z;
+      packed[4 * i + 3] = v.w;
+    }
+  } else {  // a view whose rows are not 16-byte aligned
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      packed[i] = static_cast<uint32_t>(src[2 * i]) | (static_cast<uint32_t>(src[2 * i + 1]) << 16);
   }
-  route_top8_of_row(value, lane, expert_scale, weights + static_cast<size_t>(row) * kTopK,
-                    ids + static_cast<size_t>(row) * kTopK);
+  float rescale = 1.0f;
+  if (activation_scales) rescale = __fmul_rn(activation_scales[safe_row], projection_weight_scale[0]);
+  route_top8_quad(packed, part, activation_scales != nullptr, rescale, valid, expert_scale,
+                  weights + static_cast<size_t>(safe_row) * kTopK, ids + static_cast<size_t>(safe_row) * kTopK);
 }
 
 void launch_route(const void* logits_bf16, int ld, const void* expert_scale_bf16, float* weights,
                   int* ids, int tokens, const float* activation_scales,
                   const float* projection_weight_scale, cudaStream_t stream) {
-  route_128_top8_kernel<<<(tokens + 3) / 4, 128, 0, stream>>>(
+  route_128_top8_kernel<<<(tokens + 31) / 32, 128, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(logits_bf16), ld,
       static_cast<const __nv_bfloat16*>(expert_scale_bf16), weights, ids, tokens, activation_scales,
       projection_weight_scale);

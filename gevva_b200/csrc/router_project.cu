@@ -9,15 +9,16 @@
 // A tile's K range is split over a cluster of four CTAs, so a 4096-token batch runs on 128 SMs
 // and a decode-sized batch streams the router matrix through four SMs instead of one.  Each
 // CTA accumulates its K slice in tensor memory (tcgen05.mma kind::f16 for bf16 operands,
-// kind::f8f6f4 for E4M3), copies the 128 x 128 fp32 partial sums to its shared memory, and
-// after a cluster barrier CTA q sums the four partials of rows [32q, 32q+32) in rank order
-// through distributed shared memory (a fixed order: results do not depend on timing), adds the
-// optional per-expert bias, rounds to bf16 as the GEMM would have stored it, and runs the
-// warp-per-token top-8 + softmax of gv_route.cuh.
+// kind::f8f6f4 for E4M3).  Tile row r belongs to CTA r % 4 of the cluster: every CTA stores its
+// 128 x 128 fp32 partial sums row by row straight into the owners' shared memory (posted
+// st.shared::cluster stores), and after one cluster barrier each owner sums the four partials of
+// its 32 rows in rank order (a fixed order: results do not depend on timing), adds the optional
+// per-expert bias, rounds to bf16 as the GEMM would have stored it, and routes its rows with four
+// lanes per token (gv_route.cuh).
 //
 // Roles per CTA: warp 0 TMA producer, warp 1 MMA issuer and owner of tensor memory, warps
 // 2..5 epilogue (thread = accumulator row).  Every mbarrier wait is bounded (status word
-// kWaitTimeout); the two cluster barriers are reached by every thread whatever happened before.
+// kWaitTimeout); the cluster barrier is reached by every thread whatever happened before.
 #include "gv_common.cuh"
 #include "gv_launchers.h"
 #include "gv_route.cuh"
@@ -30,21 +31,29 @@ constexpr int kRpSplit = 4;      // CTAs per cluster = K slices per token tile
 constexpr int kRpStages = 4;
 constexpr int kRpThreads = 192;
 constexpr int kRpTileBytes = kTileM * kTileKBytes;  // 16 KiB: 128 rows of one 128-byte K block
-constexpr int kRpLogitStride = kExperts + 8;        // bf16 elements per staged logits row
 
 struct alignas(1024) RouterSmem {
   uint8_t a[kRpStages][kRpTileBytes];
   uint8_t b[kRpStages][kRpTileBytes];
-  // This CTA's partial sums: row r, 16-byte chunk c (four columns) at chunk position c ^ (r & 31),
-  // which keeps both the row-wise writes and the reduce's reads free of bank conflicts.
-  float partial[kTileM * kExperts];
-  alignas(16) uint16_t logits[32][kRpLogitStride];
+  // Partial sums of this CTA's 32 rows as received from the four CTAs of the cluster (its own
+  // included): [source][local row][128 floats]; the 16-byte chunks of a row are permuted
+  // (received_chunk_position) so that neither the row-wise stores nor the reduce's reads, where
+  // four lanes share a row, meet in a bank.
+  float received[kRpSplit][32][kExperts];
   uint64_t full[kRpStages];
   uint64_t empty[kRpStages];
   uint64_t acc_full;
   uint32_t tmem_base;
   volatile int abort;
 };
+
+// Position of 16-byte chunk `chunk` (0..31) inside local row `row`: the chunk's low three bits are
+// XORed with (row + 2 * (chunk / 8)) % 8.  For a fixed chunk, eight consecutive rows fall into eight
+// different bank groups (the stores); for a fixed chunk % 8, two consecutive rows times the four
+// column quarters do too (the loads of a quarter-warp).
+__device__ __forceinline__ int received_chunk_position(int chunk, int row) {
+  return chunk ^ ((row + 2 * (chunk >> 3)) & 7);
+}
 
 constexpr size_t kRpSmemBytes = sizeof(RouterSmem) + 1024;
 static_assert(kRpSmemBytes <= 232448, "shared memory budget of one sm_100 CTA");
@@ -189,12 +198,15 @@ route_project_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
       }
     }
   } else {
-    // ---------------- epilogue, part 1: partial sums to shared memory ----------------
+    // ---------------- epilogue, part 1: partial sums to the rows' owners ----------------
     const int quarter = warp & 3;  // the tensor-memory lanes this warp may read
     const int row = quarter * 32 + lane;
+    const int owner = row & (kRpSplit - 1);
+    const int owner_row = row >> 2;
     if (wait_or_abort<true>(&smem->acc_full, 0, smem, p.status)) {
       tc_fence_after_sync();
-      float* row_base = smem->partial + row * kExperts;
+      const uint32_t remote_row =
+          cluster_map_shared(smem_u32(&smem->received[rank][owner_row][0]), static_cast<uint32_t>(owner));
 #pragma unroll 1
       for (int part = 0; part < 4; ++part) {
         uint32_t r[32];
@@ -203,32 +215,33 @@ route_project_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int chunk = part * 8 + i;
-          *reinterpret_cast<uint4*>(row_base + ((chunk ^ lane) << 2)) =
-              make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+          cluster_store_uint4(remote_row + (static_cast<uint32_t>(received_chunk_position(chunk, owner_row)) << 4),
+                              make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]));
         }
       }
       tc_fence_before_sync();
     }
   }
 
-  // Every thread of every CTA of the cluster arrives here, also after a failed wait.
+  // Every thread of every CTA of the cluster arrives here, also after a failed wait.  The barrier
+  // orders the posted stores above before the owners' reads below; after it no CTA touches another
+  // CTA's shared memory, so a CTA may finish while its peers still work.
   cluster_sync_all();
 
   if (warp >= 2 && !smem->abort) {
-    // ---------------- epilogue, part 2: reduce rows [32*rank, 32*rank+32) and route ----------------
+    // ---------------- epilogue, part 2: reduce this CTA's 32 rows and route them ----------------
     const int t = threadIdx.x - 64;
-    const int row_local = t >> 2;
-    const int column_quarter = t & 3;
-    const int row = static_cast<int>(rank) * 32 + row_local;
-    const uint32_t local_row = smem_u32(smem->partial + row * kExperts);
+    const int row_local = t >> 2;   // tile row 4 * row_local + rank
+    const int part = t & 3;         // columns [32 * part, 32 * part + 32)
+    const int token = m_tile * kTileM + row_local * kRpSplit + static_cast<int>(rank);
+    const bool valid = token < p.tokens;
     float4 acc[8];
 #pragma unroll
     for (int source = 0; source < kRpSplit; ++source) {
-      const uint32_t remote_row = cluster_map_shared(local_row, static_cast<uint32_t>(source));
+      const float4* source_row = reinterpret_cast<const float4*>(&smem->received[source][row_local][0]);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const int chunk = column_quarter * 8 + i;
-        const float4 v = cluster_load_float4(remote_row + (static_cast<uint32_t>(chunk ^ row_local) << 4));
+        const float4 v = source_row[received_chunk_position(part * 8 + i, row_local)];
         if (source == 0) {
           acc[i] = v;
         } else {
@@ -244,7 +257,7 @@ route_project_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     for (int i = 0; i < 8; ++i) {
       float4 v = acc[i];
       if (p.bias) {
-        const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias) + column_quarter * 8 + i);
+        const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias) + part * 8 + i);
         v.x = __fadd_rn(v.x, b.x);
         v.y = __fadd_rn(v.y, b.y);
         v.z = __fadd_rn(v.z, b.z);
@@ -255,36 +268,21 @@ route_project_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
       packed[2 * i] = *reinterpret_cast<const uint32_t*>(&lo);
       packed[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&hi);
     }
-    uint4* staged = reinterpret_cast<uint4*>(&smem->logits[row_local][column_quarter * 32]);
+    const size_t safe_token = valid ? static_cast<size_t>(token) : 0;
+    if (p.logits_out && valid) {
+      uint4* out = reinterpret_cast<uint4*>(p.logits_out + safe_token * kExperts + 32 * part);
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-      staged[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
-    named_barrier(1, 128);
-    // one warp per token: this warp's eight rows
-    const int first = (warp - 2) * 8;
-#pragma unroll 1
-    for (int i = 0; i < 8; ++i) {
-      const int token = m_tile * kTileM + static_cast<int>(rank) * 32 + first + i;
-      if (token >= p.tokens) break;
-      const uint2 raw = *reinterpret_cast<const uint2*>(&smem->logits[first + i][4 * lane]);
-      if (p.logits_out)
-        *reinterpret_cast<uint2*>(p.logits_out + static_cast<size_t>(token) * kExperts + 4 * lane) = raw;
-      float value[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
-                        __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u)};
-      if (kFp8) {
-        // the reference's rescale of an unscaled FP8 GEMM output (routing_sampling.cuh:408-411)
-        const float rescale = __fmul_rn(p.activation_scales[token], p.weight_scale[0]);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) value[j] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(value[j], rescale)));
-      }
-      route_top8_of_row(value, lane, p.expert_scale, p.weights + static_cast<size_t>(token) * kTopK,
-                        p.ids + static_cast<size_t>(token) * kTopK);
+      for (int i = 0; i < 4; ++i)
+        out[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
     }
+    // the reference's rescale of an unscaled FP8 GEMM output (routing_sampling.cuh:405-411)
+    const float rescale = kFp8 ? __fmul_rn(p.activation_scales[safe_token], p.weight_scale[0]) : 1.0f;
+    route_top8_quad(packed, part, kFp8, rescale, valid, p.expert_scale, p.weights + safe_token * kTopK,
+                    p.ids + safe_token * kTopK);
   }
 
-  // No CTA may leave while a peer still reads its partial sums.
   tc_fence_before_sync();
-  cluster_sync_all();
+  __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
     __syncwarp();

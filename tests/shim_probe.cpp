@@ -107,9 +107,9 @@ int gpu_checks() {
   cudaMemcpy(ids, host_ids.data(), host_ids.size() * sizeof(int), cudaMemcpyHostToDevice);
   cudaStream_t stream;
   cudaStreamCreate(&stream);
+  runner.launch(in, ids, weights, out, stream);   // one token
   runner.launch_batch(in, ids, weights, out, kTokens, stream);
-  second.launch_batch_unreduced(in, ids, kTokens, stream);
-  runner.launch(in, ids, weights, out, stream);
+  second.launch_batch_unreduced(in, ids, kTokens, stream);   // last: its plan is what is read back below
   try {
     runner.launch_batch(in, ids, weights, out, kTokens + 1, stream);
     return fail("a batch beyond the capacity was accepted");

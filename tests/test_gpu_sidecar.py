@@ -28,7 +28,7 @@ def test_sidecar_round_trip_runs_the_layer(tmp_path):
         assert torch.equal(getattr(weights, name), getattr(layer.weights, name)), name
 
     runner = Nvfp4ExpertRunner(weights, tokens)
-    route_weights, ids = gevva_b200.route_128_top8(layer.logits(x), layer.expert_scale)
+    route_weights, ids = layer.route(x)
     out = torch.empty_like(x)
     runner.launch_batch(x, ids, route_weights, out, tokens)
     runner.check()
@@ -63,7 +63,7 @@ def test_checkpoint_to_sidecar_to_runner(tmp_path):
     for name in ("alpha1", "alpha2", "in_scale_q1", "in_scale_q2"):   # same fp32 products and quotients
         assert torch.allclose(getattr(weights, name), getattr(layer.weights, name), rtol=2e-7, atol=0), name
     runner = Nvfp4ExpertRunner(weights, tokens)
-    route_weights, ids = gevva_b200.route_128_top8(layer.logits(x), layer.expert_scale)
+    route_weights, ids = layer.route(x)
     out = torch.empty_like(x)
     runner.launch_batch(x, ids, route_weights, out, tokens)
     runner.check()

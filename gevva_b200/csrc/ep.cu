@@ -317,6 +317,18 @@ ep_row_destinations_kernel(EpDevice ep, RoutePlan plan, unsigned long long* __re
   }
 }
 
+// Measurement aid: the same table with every destination inside this rank's own combine buffer
+// (rows wrap around its 8 * max_tokens rows), so the compute phase can be timed with no byte
+// crossing NVLink.
+__global__ void __launch_bounds__(256)
+ep_row_destinations_local_kernel(EpDevice ep, RoutePlan plan, unsigned long long* __restrict__ row_dest,
+                                 int combine_rows) {
+  const int total = plan.expert_offsets[kExperts];
+  for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < total; row += gridDim.x * blockDim.x)
+    row_dest[row] = reinterpret_cast<unsigned long long>(ep.peer_combine[ep.rank] +
+                                                         static_cast<size_t>(row % combine_rows) * kHidden);
+}
+
 }  // namespace
 
 }  // namespace gv
@@ -350,6 +362,7 @@ struct gevva_moe_ep {
   uint8_t* inter_codes = nullptr;
   uint8_t* inter_sf = nullptr;
   unsigned long long* row_dest = nullptr;
+  unsigned long long* row_dest_local = nullptr;  // measurement aid, allocated on first use
   uint8_t* w13_sf_tiled = nullptr;
   // the compute phase runs the local experts in two halves so that the NVLink-bound w2 of the
   // first half overlaps the w13 of the second: a side stream and two events order them
@@ -368,6 +381,7 @@ void gevva_moe_ep_destroy(gevva_moe_ep* ep) {
   cudaFree(ep->inter_codes);
   cudaFree(ep->inter_sf);
   cudaFree(ep->row_dest);
+  cudaFree(ep->row_dest_local);
   cudaFree(ep->w13_sf_tiled);
   if (ep->side) cudaStreamDestroy(ep->side);
   if (ep->fork) cudaEventDestroy(ep->fork);
@@ -563,8 +577,46 @@ int gevva_moe_ep_dispatch(gevva_moe_ep* ep, const void* in, const int* ids, int 
   return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;
 }
 
+namespace {
+int run_compute(gevva_moe_ep* ep, const unsigned long long* row_dest, cudaStream_t stream);
+}
+
 int gevva_moe_ep_compute(gevva_moe_ep* ep, gevva_stream_t stream) {
   if (!ep) return GEVVA_MOE_BAD_ARGUMENT;
+  return run_compute(ep, ep->row_dest, stream);
+}
+
+int gevva_moe_ep_compute_local(gevva_moe_ep* ep, gevva_stream_t stream) {
+  if (!ep) return GEVVA_MOE_BAD_ARGUMENT;
+  if (!ep->row_dest_local &&
+      cudaMalloc(reinterpret_cast<void**>(&ep->row_dest_local), ep->capacity_rows * sizeof(unsigned long long)) !=
+          cudaSuccess)
+    return GEVVA_MOE_CUDA_ERROR;
+  gv::ep_row_destinations_local_kernel<<<ep->sm_count * 2, 256, 0, stream>>>(
+      ep->dev, ep->receive_plan, ep->row_dest_local, ep->max_tokens * kTopK);
+  return run_compute(ep, ep->row_dest_local, stream);
+}
+
+int gevva_moe_ep_dispatch_local(gevva_moe_ep* ep, const void* in, const int* ids, int tokens,
+                                gevva_stream_t stream) {
+  if (!ep || !in || !ids || tokens < 1 || tokens > ep->max_tokens) return GEVVA_MOE_BAD_ARGUMENT;
+  gv::EpDevice local = ep->dev;
+  for (int d = 0; d < local.world; ++d) {
+    local.peer_codes[d] = ep->dev.peer_codes[ep->dev.rank];
+    local.peer_scales[d] = ep->dev.peer_scales[ep->dev.rank];
+  }
+  gv::ep_dispatch_kernel<<<(tokens + gv::kDispatchTokensPerBlock - 1) / gv::kDispatchTokensPerBlock,
+                          gv::kDispatchThreads, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(in), ids, ep->in_scale_q1_global, local, ep->send_plan, tokens);
+  return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;
+}
+
+}  // extern "C"
+
+namespace {
+int run_compute(gevva_moe_ep* ep, const unsigned long long* row_dest, cudaStream_t stream) {
+  gv::GemmOperands w2 = ep->w2;
+  w2.row_dest = row_dest;
   gv::ep_swizzle_scales_kernel<<<ep->sm_count * 4, 256, 0, stream>>>(
       ep->dev.peer_scales[ep->dev.rank], ep->dev, ep->receive_plan, ep->input_sf);
   // The local experts are processed in `chunks` parts of about equal rows.  A part's w2
@@ -581,11 +633,11 @@ int gevva_moe_ep_compute(gevva_moe_ep* ep, gevva_stream_t stream) {
     if (!last) {
       cudaEventRecord(ep->fork, stream);
       cudaStreamWaitEvent(ep->side, ep->fork, 0);
-      gv::launch_grouped_gemm(ep->w2, plan, side_sms, ep->side);
+      gv::launch_grouped_gemm(w2, plan, side_sms, ep->side);
     } else {
       // launched the ordinary way: its CTAs must not take SMs (and wait there) before this
       // part's w13 has ended, or the previous part's w2 would be left without room
-      gv::GemmOperands serial = ep->w2;
+      gv::GemmOperands serial = w2;
       serial.serial_launch = true;
       gv::launch_grouped_gemm(serial, plan, ep->sm_count, stream);
     }
@@ -594,6 +646,9 @@ int gevva_moe_ep_compute(gevva_moe_ep* ep, gevva_stream_t stream) {
   cudaStreamWaitEvent(stream, ep->join, 0);
   return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;
 }
+}  // namespace
+
+extern "C" {
 
 int gevva_moe_ep_reduce(gevva_moe_ep* ep, const float* route_weights, void* out, int tokens,
                         gevva_stream_t stream) {

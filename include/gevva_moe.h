@@ -249,6 +249,15 @@ int gevva_moe_ep_dispatch(gevva_moe_ep* ep, const void* in, const int* ids, int 
 int gevva_moe_ep_compute(gevva_moe_ep* ep, gevva_stream_t stream);
 int gevva_moe_ep_reduce(gevva_moe_ep* ep, const float* route_weights, void* out, int tokens,
                         gevva_stream_t stream);
+/* Measurement aids: the dispatch and compute phases of the last step again with every store kept
+ * on this GPU (rows go to this rank's own buffers, whose contents become meaningless).  An
+ * expert-parallel step minus the same work timed this way is the step's exposed communication. */
+int gevva_moe_ep_dispatch_local(gevva_moe_ep* ep, const void* in, const int* ids, int tokens,
+                                gevva_stream_t stream);
+int gevva_moe_ep_compute_local(gevva_moe_ep* ep, gevva_stream_t stream);
+/* gevva_moe_ep_compute runs part of its work on a non-blocking side stream owned by the object
+ * (forked from and joined to `stream` by events), so that one group's NVLink-bound down projection
+ * overlaps the next group's up projection; a caller that captures `stream` captures it too. */
 /* Synchronises; returns and clears the device status word; optionally reports how many rows
  * this rank received in the last step. */
 int gevva_moe_ep_status(gevva_moe_ep* ep, int* received_rows);

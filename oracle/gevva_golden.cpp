@@ -641,6 +641,10 @@ float gvo_pack_fp8_weight(const float* w, size_t count, uint8_t* out) {
 #if defined(_OPENMP)
 #include <omp.h>
 extern "C" int gvo_threads(void) { return omp_get_max_threads(); }
+// A launcher may have exported OMP_NUM_THREADS=1 (torchrun does); the timed CPU leg sets the
+// thread count it wants explicitly.
+extern "C" void gvo_set_threads(int threads) { if (threads > 0) omp_set_num_threads(threads); }
 #else
 extern "C" int gvo_threads(void) { return 1; }
+extern "C" void gvo_set_threads(int) {}
 #endif

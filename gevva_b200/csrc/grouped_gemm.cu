@@ -53,10 +53,15 @@ namespace {
 constexpr int kEpilogueWarpsPerQuarter = 4;  // each takes a quarter of a tile's columns
 constexpr int kEpilogueThreads = 4 * kEpilogueWarpsPerQuarter * 32;
 // Warp roles: 0 = producer of the activation side (A + its scales), 1 = MMA issuer,
-// 2..17 = epilogue, 18 = producer of the weight side (B + its scales).  Two producers
-// because one thread cannot issue a K block's copies in the time its MMAs take.
+// 2..17 = epilogue, 18 = producer of the weight side (B + its scales), 19 = scale-factor
+// copier.  Two producers because one thread cannot issue a K block's copies in the time its
+// MMAs take; a copier of its own because a thread needs about 34 cycles per tcgen05
+// instruction: the twelve shared -> tensor memory scale copies of a K block plus its four
+// MMAs in one thread take longer than the 528 cycles the tensor pipe needs for them, whereas
+// four MMAs in one thread and twelve copies in another both fit.
 constexpr int kWeightProducerWarp = 2 + 4 * kEpilogueWarpsPerQuarter;
-constexpr int kGemmThreads = (kWeightProducerWarp + 1) * 32;
+constexpr int kScaleCopyWarp = kWeightProducerWarp + 1;
+constexpr int kGemmThreads = (kScaleCopyWarp + 1) * 32;
 constexpr uint32_t kTmemColumns = 512;
 // Accumulators take tensor-memory columns [0, 256) in every configuration (2 x 128 or
 // 1 x 256); scale factors follow, per pipeline stage and K block: a copy for the next K
@@ -99,10 +104,12 @@ struct alignas(1024) GemmSmem {
   uint8_t staging[4][kMode != kGeglu ? kStagingBytesPerWarp : 16];  // plain epilogue only
   uint64_t full[kStages];
   uint64_t empty[kStages];
+  uint64_t sf_full[kStages];  // the stage's scale factors have reached tensor memory
   uint64_t acc_full[kAccStages];
   uint64_t acc_empty[kAccStages];
   uint32_t tmem_base;
   volatile int abort;
+  int quarter_left[4];  // plain epilogue: a warp of this quarter gave up waiting
   alignas(16) float erf_table[GV_ERF_TABLE_FLOATS];
 };
 
@@ -143,75 +150,77 @@ struct GemmParams {
   int last_mmas;    // MMAs (K = 64 each) in the last K block, 1..4
 };
 
-// One K block's worth of tensor-core work issued as a single instruction sequence:
-// kMmas scale-factor atom copies per operand (shared -> tensor memory) followed by kMmas
-// MMAs of K = 64.  Everything is derived from four 32-bit descriptor bases with immediate
-// offsets so the issuing thread spends a handful of integer instructions per MMA; that
-// thread's instruction latency is what bounds the main loop otherwise.
+// One K block's worth of tensor-core work, issued by two threads.  The scale copier issues
+// kMmas scale-factor atom copies per operand half (shared -> tensor memory, issue_sf_copies); the
+// MMA thread, once those have landed, issues kMmas MMAs of K = 64 (issue_mmas).  Everything is
+// derived from 32-bit descriptor bases with immediate offsets so that an issuing thread spends
+// a handful of integer instructions per tcgen05 instruction.
 //   a_lo / b_lo     low words of the operand descriptors of this stage (address >> 4)
 //   sfa_lo / sfb_lo low words of the scale-factor descriptors of this stage
 //   hi_ab / hi_sf   high words (stride, version, swizzle) shared by all stages
+// Scale columns of a K block in tensor memory: at N = 128, A of MMA j at +4j and B at +16+4j;
+// at N = 256, A at +16j, B rows 0..127 at +16j+4, B rows 128..255 at +16j+8 (the second half of
+// the weight scales lies 2 KiB = 128 descriptor units after the first in shared memory).
 template <int kMmas, int kN>
-__device__ __forceinline__ void issue_k_block(uint32_t tmem_acc, uint32_t tmem_sf, uint32_t a_lo,
-                                              uint32_t b_lo, uint32_t sfa_lo, uint32_t sfb_lo,
-                                              uint32_t hi_ab, uint32_t hi_sf, uint32_t accumulate) {
+__device__ __forceinline__ void issue_sf_copies(uint32_t tmem_sf, uint32_t sfa_lo, uint32_t sfb_lo, uint32_t hi_sf) {
   static_assert(kMmas >= 1 && kMmas <= 4, "a K block holds one to four MMAs");
-#define GV_OPERANDS                                                                            \
-  ::"r"(tmem_acc), "r"(tmem_sf), "r"(a_lo), "r"(b_lo), "r"(sfa_lo), "r"(sfb_lo), "r"(hi_ab),   \
-    "r"(hi_sf), "r"(kInstrDesc<kN>), "r"(accumulate)                                           \
+#define GV_SF_OPERANDS ::"r"(tmem_sf), "r"(sfa_lo), "r"(sfb_lo), "r"(hi_sf) : "memory"
+#define GV_SF_PROLOGUE "{\n\t.reg .b32 lo, ta;\n\t.reg .b64 d0;\n\t"
+#define GV_SF_ONE(source, source_offset, column)                             \
+  "add.u32 lo, " source ", " source_offset ";\n\t"                           \
+  "mov.b64 d0, {lo, %3};\n\t"                                                \
+  "add.u32 ta, %0, " column ";\n\t"                                          \
+  "tcgen05.cp.cta_group::1.32x128b.warpx4 [ta], d0;\n\t"
+  if constexpr (kN == 128) {
+#define GV_SF_COPY(j) GV_SF_ONE("%1", #j "*32", #j "*4") GV_SF_ONE("%2", #j "*32", "16+" #j "*4")
+    asm volatile(GV_SF_PROLOGUE GV_SF_COPY(0) "}" GV_SF_OPERANDS);
+    if constexpr (kMmas >= 2) asm volatile(GV_SF_PROLOGUE GV_SF_COPY(1) "}" GV_SF_OPERANDS);
+    if constexpr (kMmas >= 3) asm volatile(GV_SF_PROLOGUE GV_SF_COPY(2) "}" GV_SF_OPERANDS);
+    if constexpr (kMmas >= 4) asm volatile(GV_SF_PROLOGUE GV_SF_COPY(3) "}" GV_SF_OPERANDS);
+#undef GV_SF_COPY
+  } else {
+#define GV_SF_COPY(j)                                                        \
+  GV_SF_ONE("%1", #j "*32", #j "*16") GV_SF_ONE("%2", #j "*32", "4+" #j "*16") \
+  GV_SF_ONE("%2", "128+" #j "*32", "8+" #j "*16")
+    asm volatile(GV_SF_PROLOGUE GV_SF_COPY(0) "}" GV_SF_OPERANDS);
+    if constexpr (kMmas >= 2) asm volatile(GV_SF_PROLOGUE GV_SF_COPY(1) "}" GV_SF_OPERANDS);
+    if constexpr (kMmas >= 3) asm volatile(GV_SF_PROLOGUE GV_SF_COPY(2) "}" GV_SF_OPERANDS);
+    if constexpr (kMmas >= 4) asm volatile(GV_SF_PROLOGUE GV_SF_COPY(3) "}" GV_SF_OPERANDS);
+#undef GV_SF_COPY
+  }
+#undef GV_SF_ONE
+#undef GV_SF_PROLOGUE
+#undef GV_SF_OPERANDS
+}
+
+template <int kMmas, int kN>
+__device__ __forceinline__ void issue_mmas(uint32_t tmem_acc, uint32_t tmem_sf, uint32_t a_lo, uint32_t b_lo,
+                                           uint32_t hi_ab, uint32_t accumulate) {
+  static_assert(kMmas >= 1 && kMmas <= 4, "a K block holds one to four MMAs");
+#define GV_OPERANDS                                                                                  \
+  ::"r"(tmem_acc), "r"(tmem_sf), "r"(a_lo), "r"(b_lo), "r"(hi_ab), "r"(kInstrDesc<kN>), "r"(accumulate) \
   : "memory"
 #define GV_PROLOGUE "{\n\t.reg .pred p, pt;\n\t.reg .b32 lo, ta, tb;\n\t.reg .b64 d0, d1;\n\t" \
-                    "setp.ne.b32 p, %9, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
-#define GV_MMA(j, step, pred)                                              \
+                    "setp.ne.b32 p, %6, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+#define GV_MMA(j, step, sfb_column, pred)                                  \
   "add.u32 lo, %2, " #j "*2;\n\t"                                          \
-  "mov.b64 d0, {lo, %6};\n\t"                                              \
+  "mov.b64 d0, {lo, %4};\n\t"                                              \
   "add.u32 lo, %3, " #j "*2;\n\t"                                          \
-  "mov.b64 d1, {lo, %6};\n\t"                                              \
+  "mov.b64 d1, {lo, %4};\n\t"                                              \
   "add.u32 ta, %1, " #j "*" #step ";\n\t"                                  \
-  "add.u32 tb, %1, " #j "*" #step "+" GV_SFB_COLUMN ";\n\t"                \
+  "add.u32 tb, %1, " #j "*" #step "+" #sfb_column ";\n\t"                  \
   "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X"      \
-  " [%0], d0, d1, %8, [ta], [tb], " pred ";\n\t"
+  " [%0], d0, d1, %5, [ta], [tb], " pred ";\n\t"
   if constexpr (kN == 128) {
-    // scale columns of a K block: A of MMA j at +4j, B at +16+4j
-#define GV_SFB_COLUMN "16"
-#define GV_SF_COPY(j)                                                      \
-  "add.u32 lo, %4, " #j "*32;\n\t"                                         \
-  "mov.b64 d0, {lo, %7};\n\t"                                              \
-  "add.u32 ta, %1, " #j "*4;\n\t"                                          \
-  "tcgen05.cp.cta_group::1.32x128b.warpx4 [ta], d0;\n\t"                   \
-  "add.u32 lo, %5, " #j "*32;\n\t"                                         \
-  "mov.b64 d0, {lo, %7};\n\t"                                              \
-  "add.u32 ta, %1, 16+" #j "*4;\n\t"                                       \
-  "tcgen05.cp.cta_group::1.32x128b.warpx4 [ta], d0;\n\t"
-    asm volatile(GV_PROLOGUE GV_SF_COPY(0) GV_MMA(0, 4, "p") "}" GV_OPERANDS);
-    if constexpr (kMmas >= 2) asm volatile(GV_PROLOGUE GV_SF_COPY(1) GV_MMA(1, 4, "pt") "}" GV_OPERANDS);
-    if constexpr (kMmas >= 3) asm volatile(GV_PROLOGUE GV_SF_COPY(2) GV_MMA(2, 4, "pt") "}" GV_OPERANDS);
-    if constexpr (kMmas >= 4) asm volatile(GV_PROLOGUE GV_SF_COPY(3) GV_MMA(3, 4, "pt") "}" GV_OPERANDS);
-#undef GV_SF_COPY
-#undef GV_SFB_COLUMN
+    asm volatile(GV_PROLOGUE GV_MMA(0, 4, 16, "p") "}" GV_OPERANDS);
+    if constexpr (kMmas >= 2) asm volatile(GV_PROLOGUE GV_MMA(1, 4, 16, "pt") "}" GV_OPERANDS);
+    if constexpr (kMmas >= 3) asm volatile(GV_PROLOGUE GV_MMA(2, 4, 16, "pt") "}" GV_OPERANDS);
+    if constexpr (kMmas >= 4) asm volatile(GV_PROLOGUE GV_MMA(3, 4, 16, "pt") "}" GV_OPERANDS);
   } else {
-    // scale columns of MMA j: A at +16j, B rows 0..127 at +16j+4, B rows 128..255 at +16j+8;
-    // the second half of the weight scales lies 2 KiB (128 descriptor units) after the first
-#define GV_SFB_COLUMN "4"
-#define GV_SF_COPY(j)                                                      \
-  "add.u32 lo, %4, " #j "*32;\n\t"                                         \
-  "mov.b64 d0, {lo, %7};\n\t"                                              \
-  "add.u32 ta, %1, " #j "*16;\n\t"                                         \
-  "tcgen05.cp.cta_group::1.32x128b.warpx4 [ta], d0;\n\t"                   \
-  "add.u32 lo, %5, " #j "*32;\n\t"                                         \
-  "mov.b64 d0, {lo, %7};\n\t"                                              \
-  "add.u32 ta, %1, 4+" #j "*16;\n\t"                                       \
-  "tcgen05.cp.cta_group::1.32x128b.warpx4 [ta], d0;\n\t"                   \
-  "add.u32 lo, %5, 128+" #j "*32;\n\t"                                     \
-  "mov.b64 d0, {lo, %7};\n\t"                                              \
-  "add.u32 ta, %1, 8+" #j "*16;\n\t"                                       \
-  "tcgen05.cp.cta_group::1.32x128b.warpx4 [ta], d0;\n\t"
-    asm volatile(GV_PROLOGUE GV_SF_COPY(0) GV_MMA(0, 16, "p") "}" GV_OPERANDS);
-    if constexpr (kMmas >= 2) asm volatile(GV_PROLOGUE GV_SF_COPY(1) GV_MMA(1, 16, "pt") "}" GV_OPERANDS);
-    if constexpr (kMmas >= 3) asm volatile(GV_PROLOGUE GV_SF_COPY(2) GV_MMA(2, 16, "pt") "}" GV_OPERANDS);
-    if constexpr (kMmas >= 4) asm volatile(GV_PROLOGUE GV_SF_COPY(3) GV_MMA(3, 16, "pt") "}" GV_OPERANDS);
-#undef GV_SF_COPY
-#undef GV_SFB_COLUMN
+    asm volatile(GV_PROLOGUE GV_MMA(0, 16, 4, "p") "}" GV_OPERANDS);
+    if constexpr (kMmas >= 2) asm volatile(GV_PROLOGUE GV_MMA(1, 16, 4, "pt") "}" GV_OPERANDS);
+    if constexpr (kMmas >= 3) asm volatile(GV_PROLOGUE GV_MMA(2, 16, 4, "pt") "}" GV_OPERANDS);
+    if constexpr (kMmas >= 4) asm volatile(GV_PROLOGUE GV_MMA(3, 16, 4, "pt") "}" GV_OPERANDS);
   }
 #undef GV_MMA
 #undef GV_OPERANDS
@@ -373,7 +382,9 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&smem->full[s], 2);  // one arrival (with its byte count) per producer warp
       mbar_init(&smem->empty[s], 1);
+      mbar_init(&smem->sf_full[s], 1);
     }
+    for (int s = 0; s < 4; ++s) smem->quarter_left[s] = 0;
     for (int s = 0; s < kAccStages; ++s) {
       mbar_init(&smem->acc_full[s], 1);
       mbar_init(&smem->acc_empty[s], kEpilogueThreads);
@@ -524,10 +535,7 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     // word = stride >> 4 | version 1 at bit 14 | swizzle mode at bits 29..31.
     const uint32_t a_lo0 = (smem_u32(smem->a[0]) & 0x3ffffu) >> 4;
     const uint32_t b_lo0 = (smem_u32(smem->b[0]) & 0x3ffffu) >> 4;
-    const uint32_t sfa_lo0 = (smem_u32(smem->sfa[0]) & 0x3ffffu) >> 4;
-    const uint32_t sfb_lo0 = (smem_u32(smem->sfb[0]) & 0x3ffffu) >> 4;
     constexpr uint32_t hi_ab = (1024u >> 4) | (1u << 14) | (2u << 29);  // 8 rows x 128 B, 128B swizzle
-    constexpr uint32_t hi_sf = (128u >> 4) | (1u << 14);                // 8 rows x 16 B, no swizzle
     const bool full_last = p.last_mmas == 4;
     const bool leader = elect_one();
     for (int round = 0; round < rounds; ++round) {
@@ -543,14 +551,15 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         // All lanes execute the same test on the same barrier, so the result is warp-uniform
         // without a vote.  The operands were written by the async proxy and are read by it;
         // the barrier's transaction count is what orders the two, no tcgen05 fence is needed.
-        ok = wait_or_abort<false>(&smem->full[stage], phase, smem, p.status);
+        // With block scales the stage is ready once the copier's scale copies have landed in
+        // tensor memory (which implies that the operands have landed in shared memory).
+        ok = wait_or_abort<false>(kMode == kFp8 ? &smem->full[stage] : &smem->sf_full[stage], phase, smem, p.status);
         if (!ok) break;
+        if (kMode != kFp8) tc_fence_after_sync();
         // Descriptor low words advance by whole stages and K atoms; the K offset of each MMA
-        // (+32 bytes inside the swizzle row) and each scale atom (+512 bytes) are immediates.
+        // (+32 bytes inside the swizzle row) is an immediate.
         const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * (kAtoms * kOperandStageBytes >> 4);
         const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(stage) * (kAtoms * Shape::kWeightBytes >> 4);
-        const uint32_t sfa_lo = sfa_lo0 + static_cast<uint32_t>(stage) * (kAtoms * kSfStageBytes >> 4);
-        const uint32_t sfb_lo = sfb_lo0 + static_cast<uint32_t>(stage) * (kAtoms * Shape::kWeightSfBytes >> 4);
         const uint32_t tmem_sf = tmem_base + kSfColumn + Shape::kSfColumns * kAtoms * stage;
         if (leader) {
 #pragma unroll
@@ -560,8 +569,6 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
             const uint32_t accumulate = k != 0 ? 1u : 0u;
             const uint32_t aa = a_lo + atom * (kOperandStageBytes >> 4);
             const uint32_t bb = b_lo + atom * (Shape::kWeightBytes >> 4);
-            const uint32_t sa = sfa_lo + atom * (kSfStageBytes >> 4);
-            const uint32_t sb = sfb_lo + atom * (Shape::kWeightSfBytes >> 4);
             const uint32_t ts = tmem_sf + atom * Shape::kSfColumns;
             if (kMode == kFp8) {
               if (k != p.k_blocks - 1 || full_last) issue_k_block_fp8<4>(tmem_acc, aa, bb, hi_ab, accumulate);
@@ -569,13 +576,13 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
               else if (p.last_mmas == 2) issue_k_block_fp8<2>(tmem_acc, aa, bb, hi_ab, accumulate);
               else issue_k_block_fp8<1>(tmem_acc, aa, bb, hi_ab, accumulate);
             } else if (k != p.k_blocks - 1 || full_last) {
-              issue_k_block<4, kN>(tmem_acc, ts, aa, bb, sa, sb, hi_ab, hi_sf, accumulate);
+              issue_mmas<4, kN>(tmem_acc, ts, aa, bb, hi_ab, accumulate);
             } else if (p.last_mmas == 3) {
-              issue_k_block<3, kN>(tmem_acc, ts, aa, bb, sa, sb, hi_ab, hi_sf, accumulate);
+              issue_mmas<3, kN>(tmem_acc, ts, aa, bb, hi_ab, accumulate);
             } else if (p.last_mmas == 2) {
-              issue_k_block<2, kN>(tmem_acc, ts, aa, bb, sa, sb, hi_ab, hi_sf, accumulate);
+              issue_mmas<2, kN>(tmem_acc, ts, aa, bb, hi_ab, accumulate);
             } else {
-              issue_k_block<1, kN>(tmem_acc, ts, aa, bb, sa, sb, hi_ab, hi_sf, accumulate);
+              issue_mmas<1, kN>(tmem_acc, ts, aa, bb, hi_ab, accumulate);
             }
           }
           tc_commit(&smem->empty[stage]);  // frees the stage once these MMAs have read it
@@ -590,6 +597,53 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       if (++acc_stage == kAccStages) {
         acc_stage = 0;
         acc_phase ^= 1u;
+      }
+    }
+  } else if (warp == kScaleCopyWarp) {
+    // ---------------- scale-factor copier ----------------
+    // Walks the same items and K blocks as the MMA warp, one step ahead of it: when a stage's
+    // bytes have landed in shared memory it copies the stage's scale-factor atoms into the
+    // tensor-memory columns of that stage and commits them to sf_full.  The columns of a stage
+    // are free by then: the producers refill a stage only after the MMAs that read it (and its
+    // scale columns) have completed.
+    if (kMode != kFp8) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t sfa_lo0 = (smem_u32(smem->sfa[0]) & 0x3ffffu) >> 4;
+      const uint32_t sfb_lo0 = (smem_u32(smem->sfb[0]) & 0x3ffffu) >> 4;
+      constexpr uint32_t hi_sf = (128u >> 4) | (1u << 14);  // 8 rows x 16 B, no swizzle
+      const bool full_last = p.last_mmas == 4;
+      const bool leader = elect_one();
+      bool ok = true;
+      for (int round = 0; ok && round < rounds; ++round) {
+        WorkItem item;
+        if (!work_item<kMode, kN>(round, total_items, m_tiles, p.n_tiles, tile_first, item)) continue;
+        for (int kb = 0; kb < p.k_blocks; kb += kAtoms) {
+          ok = wait_or_abort<false>(&smem->full[stage], phase, smem, p.status);
+          if (!ok) break;
+          const uint32_t sfa_lo = sfa_lo0 + static_cast<uint32_t>(stage) * (kAtoms * kSfStageBytes >> 4);
+          const uint32_t sfb_lo = sfb_lo0 + static_cast<uint32_t>(stage) * (kAtoms * Shape::kWeightSfBytes >> 4);
+          const uint32_t tmem_sf = tmem_base + kSfColumn + Shape::kSfColumns * kAtoms * stage;
+          if (leader) {
+#pragma unroll
+            for (int atom = 0; atom < kAtoms; ++atom) {
+              const int k = kb + atom;
+              if (k >= p.k_blocks) break;
+              const uint32_t sa = sfa_lo + atom * (kSfStageBytes >> 4);
+              const uint32_t sb = sfb_lo + atom * (Shape::kWeightSfBytes >> 4);
+              const uint32_t ts = tmem_sf + atom * Shape::kSfColumns;
+              if (k != p.k_blocks - 1 || full_last) issue_sf_copies<4, kN>(ts, sa, sb, hi_sf);
+              else if (p.last_mmas == 3) issue_sf_copies<3, kN>(ts, sa, sb, hi_sf);
+              else if (p.last_mmas == 2) issue_sf_copies<2, kN>(ts, sa, sb, hi_sf);
+              else issue_sf_copies<1, kN>(ts, sa, sb, hi_sf);
+            }
+            tc_commit(&smem->sf_full[stage]);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
       }
     }
   } else {
@@ -611,7 +665,17 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       const int row0 = p.expert_offsets[expert] + local0;
       const int rows_valid = p.expert_offsets[expert + 1] - row0;  // may exceed 128
       const float alpha = p.alpha[expert];
-      if (!wait_or_abort<true>(&smem->acc_full[acc_stage], acc_phase, smem, p.status)) break;
+      const bool acc_ready = wait_or_abort<true>(&smem->acc_full[acc_stage], acc_phase, smem, p.status);
+      if constexpr (kMode != kGeglu) {
+        // The four warps of a quarter meet at named barriers while they store, so they must
+        // leave together: a warp whose wait failed says so, and all four read the answer behind
+        // a barrier of their own.
+        if (!acc_ready) smem->quarter_left[quarter] = 1;
+        named_barrier(1 + quarter, kEpilogueWarpsPerQuarter * 32);
+        if (*reinterpret_cast<volatile int*>(&smem->quarter_left[quarter])) break;
+      } else {
+        if (!acc_ready) break;
+      }
       tc_fence_after_sync();
       const int row_local = quarter * 32 + lane;
       const uint32_t tmem_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +

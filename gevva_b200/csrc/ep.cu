@@ -36,6 +36,7 @@
 
 #include "../../include/gevva_moe.h"
 #include "gv_common.cuh"
+#include "gv_ep_protocol.h"
 #include "gv_launchers.h"
 #include "gv_plan.cuh"
 
@@ -66,24 +67,31 @@ struct EpDevice {            // device-visible description, passed to kernels by
 // have reached `epoch`.  The stores of earlier kernels of this stream are complete when this
 // kernel starts; the fence orders the flag behind them at system scope.  The wait is bounded:
 // on expiry the status word gets kWaitTimeout and the kernel returns.
+// Device side of gv_ep_protocol.h: flags in peer-mapped global memory, system-scope release /
+// acquire, the SM cycle counter as the clock (about two seconds).
+struct DeviceFlagPort {
+  const EpDevice& ep;
+  long long start;
+  __device__ void publish(int peer, int slot, int value) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(ep.peer_flags[peer] + slot), "r"(value) : "memory");
+  }
+  __device__ int observe(int slot) {
+    int seen;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(ep.peer_flags[ep.rank] + slot) : "memory");
+    return seen;
+  }
+  __device__ void start_clock() { start = clock64(); }
+  __device__ bool expired() { return clock64() - start > 4000000000ll; }
+  __device__ void pause() { __nanosleep(64); }
+};
+
 __global__ void __launch_bounds__(32) ep_barrier_kernel(EpDevice ep, int epoch, int* status) {
   const int lane = threadIdx.x;
   if (lane < ep.world) {
-    __threadfence_system();
-    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(ep.peer_flags[lane] + ep.rank), "r"(epoch)
-                 : "memory");
-    const int* mine = ep.peer_flags[ep.rank] + lane;
-    const long long start = clock64();
-    for (;;) {
-      int seen;
-      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-      if (seen - epoch >= 0) break;
-      if (clock64() - start > 4000000000ll) {
-        atomicExch(status, static_cast<int>(kWaitTimeout));
-        break;
-      }
-      __nanosleep(64);
-    }
+    DeviceFlagPort port{ep, 0};
+    ep_barrier_announce(port, ep.rank, lane, epoch);
+    if (!ep_barrier_await(port, lane, epoch)) atomicExch(status, static_cast<int>(kWaitTimeout));
   }
 }
 

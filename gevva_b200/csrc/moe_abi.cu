@@ -12,14 +12,31 @@
 #include <new>
 
 #include "../../include/gevva_moe.h"
+#include <nvtx3/nvToolsExt.h>
+
 #include "gv_common.cuh"
 #include "gv_launchers.h"
+#include "gv_scratch.h"
 
 namespace {
 
 using namespace gv;
 
 constexpr int kMaxTokens = 131072;
+
+// The CUDA face of the allocator that gv_scratch.h takes as a parameter.
+struct CudaScratchRuntime {
+  static inline cudaError_t last_error = cudaSuccess;
+  static bool allocate(void** pointer, size_t bytes) {
+    last_error = cudaMalloc(pointer, bytes);
+    return last_error == cudaSuccess;
+  }
+  static bool zero(void* pointer, size_t bytes) {
+    last_error = cudaMemset(pointer, 0, bytes);
+    return last_error == cudaSuccess;
+  }
+  static void release(void* pointer) noexcept { cudaFree(pointer); }
+};
 
 struct Scratch {
   int references = 1;
@@ -32,6 +49,7 @@ struct Scratch {
   uint8_t* inter_sf = nullptr;
   void* w2_out = nullptr;
   int* ints = nullptr;  // one allocation carved into the RoutePlan arrays
+  gv::ScratchMemory<CudaScratchRuntime> memory;
   RoutePlan plan{};
   size_t input_sf_bytes = 0, inter_sf_bytes = 0, tile_capacity = 0;
 };
@@ -84,50 +102,32 @@ int cuda_failure(cudaError_t error, const char* what) {
 
 void free_scratch(Scratch* s) {
   if (!s) return;
-  cudaFree(s->input_codes);
-  cudaFree(s->input_sf);
-  cudaFree(s->w13_out);
-  cudaFree(s->inter_codes);
-  cudaFree(s->inter_sf);
-  cudaFree(s->w2_out);
-  cudaFree(s->ints);
+  s->memory.release();
   delete s;
 }
 
 int make_scratch(int tokens, Scratch** out) {
   Scratch* s = new (std::nothrow) Scratch;
   if (!s) return GEVVA_MOE_CUDA_ERROR;
+  const gv::ScratchSizes sizes = gv::scratch_sizes(tokens);
   s->max_tokens = tokens;
-  s->routes = tokens * kTopK;
-  const size_t routes = static_cast<size_t>(s->routes);
-  // Scale regions are padded to 128 rows per expert (src/nvfp4_cutlass.cu:1699-1706).
-  const size_t padded_rows = routes + static_cast<size_t>(kExperts) * 127;
-  s->input_sf_bytes = padded_rows * (kHidden / 16);
-  s->inter_sf_bytes = padded_rows * (kInter / 16);
-  s->tile_capacity = routes / kTileM + kExperts + 1;
-  const size_t chunks = (routes + 1023) / 1024;
-  const size_t int_count = 3 * routes + 2 * (kExperts + 1) + s->tile_capacity + 1 +
-                           chunks * kExperts + 1 + 64;
-  cudaError_t e = cudaSuccess;
-  auto alloc = [&](void** p, size_t bytes) {
-    if (e == cudaSuccess) e = cudaMalloc(p, bytes);
-  };
-  alloc(reinterpret_cast<void**>(&s->input_codes), routes * (kHidden / 2));
-  alloc(reinterpret_cast<void**>(&s->input_sf), s->input_sf_bytes);
-  alloc(&s->w13_out, routes * kW13Out * 2);
-  alloc(reinterpret_cast<void**>(&s->inter_codes), routes * (kInter / 2));
-  alloc(reinterpret_cast<void**>(&s->inter_sf), s->inter_sf_bytes);
-  alloc(&s->w2_out, routes * kHidden * 2);
-  alloc(reinterpret_cast<void**>(&s->ints), int_count * sizeof(int));
-  if (e == cudaSuccess) e = cudaMemset(s->input_codes, 0, routes * (kHidden / 2));
-  if (e == cudaSuccess) e = cudaMemset(s->input_sf, 0, s->input_sf_bytes);
-  if (e == cudaSuccess) e = cudaMemset(s->inter_codes, 0, routes * (kInter / 2));
-  if (e == cudaSuccess) e = cudaMemset(s->inter_sf, 0, s->inter_sf_bytes);
-  if (e == cudaSuccess) e = cudaMemset(s->ints, 0, int_count * sizeof(int));
-  if (e != cudaSuccess) {
-    free_scratch(s);
-    return cuda_failure(e, "scratch allocation");
+  s->routes = static_cast<int>(sizes.routes);
+  s->input_sf_bytes = sizes.bytes[1];
+  s->inter_sf_bytes = sizes.bytes[4];
+  s->tile_capacity = sizes.tile_capacity;
+  const size_t routes = sizes.routes;
+  const size_t chunks = sizes.chunks;
+  if (!s->memory.acquire(sizes)) {
+    delete s;
+    return cuda_failure(CudaScratchRuntime::last_error, "scratch allocation");
   }
+  s->input_codes = static_cast<uint8_t*>(s->memory.buffers[0]);
+  s->input_sf = static_cast<uint8_t*>(s->memory.buffers[1]);
+  s->w13_out = s->memory.buffers[2];
+  s->inter_codes = static_cast<uint8_t*>(s->memory.buffers[3]);
+  s->inter_sf = static_cast<uint8_t*>(s->memory.buffers[4]);
+  s->w2_out = s->memory.buffers[5];
+  s->ints = static_cast<int*>(s->memory.buffers[6]);
   int* cursor = s->ints;
   auto carve = [&](size_t count) {
     int* p = cursor;
@@ -180,7 +180,22 @@ struct gevva_moe {
   gv::GemmOperands w2{};
   uint8_t* w13_sf_tiled = nullptr;  // runner-owned re-tiling of weights.w13_sf
   int sm_count = 0;
+  bool nvtx = false;                // GEVVA_MOE_OPTION_NVTX: one range per stage around its launches
 };
+
+namespace {
+// A named NVTX range around the launches of one stage, when the runner was created with the
+// option (the ranges cost nothing unless a tool is attached, but are off by default).
+struct StageRange {
+  bool on;
+  StageRange(bool enabled, const char* name) : on(enabled) {
+    if (on) nvtxRangePushA(name);
+  }
+  ~StageRange() {
+    if (on) nvtxRangePop();
+  }
+};
+}  // namespace
 
 extern "C" {
 
@@ -199,7 +214,7 @@ const char* gevva_moe_strerror(int status) {
 
 int gevva_moe_create(gevva_moe** out, const gevva_moe_weights* weights, int max_tokens,
                      gevva_moe* share_scratch_with, const gevva_moe_options* options) {
-  (void)options;
+  if (options && (options->flags & ~static_cast<uint32_t>(GEVVA_MOE_OPTION_NVTX))) return GEVVA_MOE_BAD_ARGUMENT;
   if (!out || !weights || !weights->w13 || !weights->w13_sf || !weights->w2 || !weights->w2_sf ||
       !weights->alpha1 || !weights->alpha2 || !weights->in_scale_q1 || !weights->in_scale_q2)
     return GEVVA_MOE_BAD_ARGUMENT;
@@ -217,6 +232,7 @@ int gevva_moe_create(gevva_moe** out, const gevva_moe_weights* weights, int max_
   gevva_moe* m = new (std::nothrow) gevva_moe;
   if (!m) return GEVVA_MOE_CUDA_ERROR;
   m->weights = *weights;
+  m->nvtx = options && (options->flags & GEVVA_MOE_OPTION_NVTX);
   m->sm_count = prop.multiProcessorCount;
   if (share_scratch_with) {
     m->scratch = share_scratch_with->scratch;
@@ -353,10 +369,15 @@ int gevva_moe_launch_stages(gevva_moe* runner, const void* in, const int* ids,
   const unsigned front = GEVVA_MOE_STAGE_SORT | GEVVA_MOE_STAGE_QUANTIZE;
   if ((stages & front) == front && tokens <= gv::kFusedSortQuantizeMaxTokens) {
     // decode-sized batch: one launch does both
+    StageRange range(runner->nvtx, "gevva_moe.sort+quantize");
     gv::launch_route_sort_quantize_small(in, ids, runner->weights.in_scale_q1, s->plan, tokens, s->input_codes,
                                          s->input_sf, stream);
   } else {
-    if (stages & GEVVA_MOE_STAGE_SORT) gv::launch_route_sort(ids, routes, s->plan, stream);
+    if (stages & GEVVA_MOE_STAGE_SORT) {
+      StageRange range(runner->nvtx, "gevva_moe.sort");
+      gv::launch_route_sort(ids, routes, s->plan, stream);
+    }
+    StageRange range(runner->nvtx && (stages & GEVVA_MOE_STAGE_QUANTIZE), "gevva_moe.quantize");
     if (stages & GEVVA_MOE_STAGE_QUANTIZE)
       gv::launch_quantize_input(in, ids, runner->weights.in_scale_q1, s->plan, tokens, s->input_codes,
                                 s->input_sf, stream);
@@ -364,6 +385,7 @@ int gevva_moe_launch_stages(gevva_moe* runner, const void* in, const int* ids,
   const unsigned both = GEVVA_MOE_STAGE_W13 | GEVVA_MOE_STAGE_GEGLU;
   if ((stages & both) == both && !(stages & GEVVA_MOE_STAGE_UNFUSED)) {
     // production path: GeGLU + requantise inside the w13 epilogue, no bf16 w13 output
+    StageRange range(runner->nvtx, "gevva_moe.w13+geglu");
     gv::launch_grouped_gemm(runner->w13_fused, s->plan, runner->sm_count, stream);
   } else {
     if (stages & GEVVA_MOE_STAGE_W13)
@@ -372,7 +394,11 @@ int gevva_moe_launch_stages(gevva_moe* runner, const void* in, const int* ids,
       gv::launch_geglu_quantize(s->w13_out, runner->weights.in_scale_q2, s->plan, routes,
                                 s->inter_codes, s->inter_sf, stream);
   }
-  if (stages & GEVVA_MOE_STAGE_W2) gv::launch_grouped_gemm(runner->w2, s->plan, runner->sm_count, stream);
+  if (stages & GEVVA_MOE_STAGE_W2) {
+    StageRange range(runner->nvtx, "gevva_moe.w2");
+    gv::launch_grouped_gemm(runner->w2, s->plan, runner->sm_count, stream);
+  }
+  StageRange reduce_range(runner->nvtx && (stages & GEVVA_MOE_STAGE_REDUCE), "gevva_moe.reduce");
   if (stages & GEVVA_MOE_STAGE_REDUCE)
     gv::launch_reduce_routes(s->w2_out, route_weights, s->plan.inverse_routes, tokens, out, stream);
   GV_CUDA(cudaGetLastError(), "moe launch");

@@ -41,6 +41,13 @@ class GevvaMoeError(RuntimeError):
         super().__init__(f"{where}: {text} ({status})")
 
 
+class _Options(ctypes.Structure):
+    _fields_ = [("flags", ctypes.c_uint32), ("reserved", ctypes.c_uint32 * 7)]
+
+
+OPTION_NVTX = 1
+
+
 class _Weights(ctypes.Structure):
     _fields_ = [(n, ctypes.c_void_p) for n in
                 ("w13", "w13_sf", "w2", "w2_sf", "alpha1", "alpha2", "in_scale_q1", "in_scale_q2")]
@@ -143,7 +150,8 @@ class ExpertWeights:
 class Nvfp4ExpertRunner:
     """Mirror of gevva::Nvfp4ExpertRunner (include/gevva/gpu.hpp:217-247)."""
 
-    def __init__(self, experts: ExpertWeights, maximum_tokens: int = 1, shared_scratch=None):
+    def __init__(self, experts: ExpertWeights, maximum_tokens: int = 1, shared_scratch=None, nvtx=False):
+        """nvtx: wrap every stage's launches in a named NVTX range (an addition of this build)."""
         experts.validate()
         self._weights = experts  # keeps the tensors alive, as the DeviceModel arena does
         self._device = experts.w13.device
@@ -155,8 +163,9 @@ class Nvfp4ExpertRunner:
         share = shared_scratch._handle if shared_scratch is not None else None
         self._shared = shared_scratch
         with torch.cuda.device(self._device):
+            options = _Options(OPTION_NVTX if nvtx else 0)
             status = library().gevva_moe_create(ctypes.byref(handle), ctypes.byref(packed),
-                                                self.maximum_tokens, share, None)
+                                                self.maximum_tokens, share, ctypes.byref(options))
         if status != 0:
             raise GevvaMoeError(status, "Nvfp4ExpertRunner")
         self._handle = handle

@@ -59,8 +59,12 @@ typedef struct {
   const float* in_scale_q2;
 } gevva_moe_weights;
 
+/* flags of gevva_moe_options */
+#define GEVVA_MOE_OPTION_NVTX 1u /* one NVTX range per stage around its launches (the reference wraps its
+                                    phases in NVTX ranges too, e.g. src/gpu/weight_arena.cpp:53,
+                                    src/cuda/diagnostics/assistant_prefill_layers.cuh:67-77) */
 typedef struct {
-  uint32_t flags; /* reserved, 0 */
+  uint32_t flags; /* 0 or GEVVA_MOE_OPTION_* */
   uint32_t reserved[7];
 } gevva_moe_options;
 

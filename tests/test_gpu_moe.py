@@ -508,6 +508,32 @@ def test_against_committed_golden_vectors(gm, packed, weights, cuda_device):
     assert rel_l2(bf16_to_f32(bits(out)), bf16_to_f32(golden["layer_out"])) < REL_L2
 
 
+def test_nvtx_ranges_do_not_change_results(gm, weights, cuda_device):
+    """A runner created with the NVTX option marks its stages and computes the same bits; unknown
+    option flags are refused."""
+    import ctypes
+    from gevva_b200 import runtime as rt
+    tokens = 200
+    x = hashgen.activations(tokens, HIDDEN, 44, cuda_device)
+    ids = torch.from_numpy(random_ids(tokens, 9)).to(cuda_device)
+    rw = torch.full((tokens, TOP_K), 0.125, device=cuda_device)
+    outs = []
+    for nvtx in (False, True):
+        runner = gm.Nvfp4ExpertRunner(weights[0], tokens, nvtx=nvtx)
+        out = torch.empty_like(x)
+        runner.launch_batch(x, ids, rw, out, tokens)
+        runner.check()
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    w = weights[0]
+    packed = rt._Weights(*[t.data_ptr() for t in (w.w13, w.w13_sf, w.w2, w.w2_sf, w.alpha1, w.alpha2,
+                                                  w.in_scale_q1, w.in_scale_q2)])
+    handle = ctypes.c_void_p()
+    bad = rt._Options(0x80)
+    assert rt.library().gevva_moe_create(ctypes.byref(handle), ctypes.byref(packed), 16, None,
+                                         ctypes.byref(bad)) == -3
+
+
 def test_bounded_wait_times_out_and_context_survives(gm, weights, cuda_device):
     """A wait that nothing satisfies must end by itself with WAIT_TIMEOUT in the status word
     (about a millisecond here) and leave the device usable: the next layer launch is correct."""

@@ -455,7 +455,7 @@ int gevva_moe_ep_create(gevva_moe_ep** out, const gevva_moe_weights* local_weigh
   const size_t recv_tiles = cap / kTileM + kExperts + 1;
   const size_t chunks = (local_routes + 1023) / 1024;
   const size_t int_count = 3 * local_routes + 2 * (kExperts + 1) + send_tiles + 1 + chunks * kExperts + 1 +
-                           2 * (kExperts + 1) + recv_tiles + 1 + 1 +   // receive plan
+                           2 * (kExperts + 1) + 2 * (recv_tiles + 1) + 1 +   // receive plan
                            4 * kExperts + kExperts + 64;                // tables + remap
   const size_t padded = cap + static_cast<size_t>(kExperts) * 127;
   cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&ep->ints), int_count * sizeof(int));
@@ -491,6 +491,8 @@ int gevva_moe_ep_create(gevva_moe_ep** out, const gevva_moe_weights* local_weigh
   rp.scale_row_offsets = carve(kExperts + 1);
   rp.tile_expert = carve(recv_tiles);
   rp.num_m_tiles = carve(1);
+  rp.pair_tile = carve(recv_tiles);
+  rp.num_pairs = carve(1);
   rp.status = sp.status;
   ep->dev.send_row_base = carve(kExperts);
   ep->dev.send_src_prefix = carve(kExperts);

@@ -18,6 +18,9 @@ struct RoutePlan {
   int* scale_row_offsets;  // [129] first scale-factor row (128-row padded) of each expert
   int* tile_expert;        // [R/128 + 128] expert of each 128-row tile
   int* num_m_tiles;        // [1]
+  int* pair_tile;          // optional [R/128 + 128]: 2 * (first tile of a pair) + (1 if the pair has two
+                           // tiles); a pair = two consecutive 128-row tiles of one expert, or its last odd one
+  int* num_pairs;          // optional [1]
   const int* tile_first;   // optional [1]: a GEMM launch covers tiles [tile_first, tile_first + num_m_tiles)
   int* chunk_hist;         // [ceil(R/1024) * 128] scratch of the multi-block sort
   int* status;             // [1]   device status word (gv::Status)
@@ -76,6 +79,8 @@ struct GemmOperands {
   // of each row tile, and the results go to the w2 operand buffers below.
   bool fused_geglu;
   bool serial_launch;         // launch the ordinary way: no start before the stream's previous kernel ends
+  bool use_pairs;             // NVFP4 forms with 256 weight rows per item: run as CTA pairs (tcgen05 cta_group::2)
+                              // when the plan carries a pair list
   bool fp8;                   // dense E4M3 x E4M3 (no block scales); k_in counts bytes = elements
   uint8_t* next_codes;        // [row capacity, 352]
   uint8_t* next_scales;       // scale regions of the w2 operand
@@ -94,6 +99,10 @@ void launch_retile_w13_scales(const uint8_t* sidecar_scales, uint8_t* tiled, int
 // swizzle; bytes out of range read as zero.  False if the driver entry point is missing.
 bool make_operand_tensor_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
                              int box_rows);
+
+// The CTA-pair form (grouped_gemm_pair.cu): fused w13 (op.fused_geglu) or plain w2 (n_out % 256 == 0).
+void launch_grouped_gemm_pairs(const GemmOperands& op, const RoutePlan& plan, int sm_count, cudaStream_t stream);
+int prepare_grouped_gemm_pairs();
 
 // Must be called once per device before launch_grouped_gemm (sets the dynamic
 // shared-memory limit).  Returns a cudaError_t value.

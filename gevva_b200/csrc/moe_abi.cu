@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -141,6 +142,8 @@ int make_scratch(int tokens, Scratch** out) {
   s->plan.scale_row_offsets = carve(kExperts + 1);
   s->plan.tile_expert = carve(s->tile_capacity);
   s->plan.num_m_tiles = carve(1);
+  s->plan.pair_tile = carve(s->tile_capacity);
+  s->plan.num_pairs = carve(1);
   s->plan.chunk_hist = carve(chunks * kExperts);
   s->plan.status = carve(1);
   s->plan.sync = carve(2);  // taken from the 64 spare ints; zero like everything else here
@@ -180,6 +183,7 @@ struct gevva_moe {
   gv::GemmOperands w2{};
   uint8_t* w13_sf_tiled = nullptr;  // runner-owned re-tiling of weights.w13_sf
   int sm_count = 0;
+  bool pairs = false;               // GEVVA_MOE_OPTION_PAIRS: prefill-sized launches run the expert GEMMs as CTA pairs
   bool nvtx = false;                // GEVVA_MOE_OPTION_NVTX: one range per stage around its launches
 };
 
@@ -214,7 +218,8 @@ const char* gevva_moe_strerror(int status) {
 
 int gevva_moe_create(gevva_moe** out, const gevva_moe_weights* weights, int max_tokens,
                      gevva_moe* share_scratch_with, const gevva_moe_options* options) {
-  if (options && (options->flags & ~static_cast<uint32_t>(GEVVA_MOE_OPTION_NVTX))) return GEVVA_MOE_BAD_ARGUMENT;
+  if (options && (options->flags & ~static_cast<uint32_t>(GEVVA_MOE_OPTION_NVTX | GEVVA_MOE_OPTION_PAIRS)))
+    return GEVVA_MOE_BAD_ARGUMENT;
   if (!out || !weights || !weights->w13 || !weights->w13_sf || !weights->w2 || !weights->w2_sf ||
       !weights->alpha1 || !weights->alpha2 || !weights->in_scale_q1 || !weights->in_scale_q2)
     return GEVVA_MOE_BAD_ARGUMENT;
@@ -233,6 +238,11 @@ int gevva_moe_create(gevva_moe** out, const gevva_moe_weights* weights, int max_
   if (!m) return GEVVA_MOE_CUDA_ERROR;
   m->weights = *weights;
   m->nvtx = options && (options->flags & GEVVA_MOE_OPTION_NVTX);
+  // The CTA-pair form (tcgen05 cta_group::2) is bit-identical but measured slower than one CTA per
+  // tile on this part (175 against 102 us for w13 at 4096 tokens), so it is opt-in: by option, or
+  // for a whole process by GEVVA_MOE_PAIRS=1.
+  const char* pairs_env = std::getenv("GEVVA_MOE_PAIRS");
+  m->pairs = (options && (options->flags & GEVVA_MOE_OPTION_PAIRS)) || (pairs_env && pairs_env[0] == '1');
   m->sm_count = prop.multiProcessorCount;
   if (share_scratch_with) {
     m->scratch = share_scratch_with->scratch;
@@ -366,6 +376,9 @@ int gevva_moe_launch_stages(gevva_moe* runner, const void* in, const int* ids,
   if ((stages & GEVVA_MOE_STAGE_QUANTIZE) && !in) return GEVVA_MOE_BAD_ARGUMENT;
   if ((stages & GEVVA_MOE_STAGE_REDUCE) && (!out || !route_weights)) return GEVVA_MOE_BAD_ARGUMENT;
   const int routes = tokens * kTopK;
+  // Decode-sized batches (at most a few rows per expert) stream weights and gain nothing from
+  // pairing two row tiles of an expert; they keep the one-CTA-per-tile kernel.
+  const bool use_pairs = runner->pairs && tokens > gv::kFusedSortQuantizeMaxTokens;
   const unsigned front = GEVVA_MOE_STAGE_SORT | GEVVA_MOE_STAGE_QUANTIZE;
   if ((stages & front) == front && tokens <= gv::kFusedSortQuantizeMaxTokens) {
     // decode-sized batch: one launch does both
@@ -386,7 +399,9 @@ int gevva_moe_launch_stages(gevva_moe* runner, const void* in, const int* ids,
   if ((stages & both) == both && !(stages & GEVVA_MOE_STAGE_UNFUSED)) {
     // production path: GeGLU + requantise inside the w13 epilogue, no bf16 w13 output
     StageRange range(runner->nvtx, "gevva_moe.w13+geglu");
-    gv::launch_grouped_gemm(runner->w13_fused, s->plan, runner->sm_count, stream);
+    gv::GemmOperands w13 = runner->w13_fused;
+    w13.use_pairs = use_pairs;
+    gv::launch_grouped_gemm(w13, s->plan, runner->sm_count, stream);
   } else {
     if (stages & GEVVA_MOE_STAGE_W13)
       gv::launch_grouped_gemm(runner->w13, s->plan, runner->sm_count, stream);
@@ -396,7 +411,9 @@ int gevva_moe_launch_stages(gevva_moe* runner, const void* in, const int* ids,
   }
   if (stages & GEVVA_MOE_STAGE_W2) {
     StageRange range(runner->nvtx, "gevva_moe.w2");
-    gv::launch_grouped_gemm(runner->w2, s->plan, runner->sm_count, stream);
+    gv::GemmOperands w2 = runner->w2;
+    w2.use_pairs = use_pairs;
+    gv::launch_grouped_gemm(w2, s->plan, runner->sm_count, stream);
   }
   StageRange reduce_range(runner->nvtx && (stages & GEVVA_MOE_STAGE_REDUCE), "gevva_moe.reduce");
   if (stages & GEVVA_MOE_STAGE_REDUCE)

@@ -46,6 +46,7 @@ class _Options(ctypes.Structure):
 
 
 OPTION_NVTX = 1
+OPTION_PAIRS = 2
 
 
 class _Weights(ctypes.Structure):
@@ -150,8 +151,10 @@ class ExpertWeights:
 class Nvfp4ExpertRunner:
     """Mirror of gevva::Nvfp4ExpertRunner (include/gevva/gpu.hpp:217-247)."""
 
-    def __init__(self, experts: ExpertWeights, maximum_tokens: int = 1, shared_scratch=None, nvtx=False):
-        """nvtx: wrap every stage's launches in a named NVTX range (an addition of this build)."""
+    def __init__(self, experts: ExpertWeights, maximum_tokens: int = 1, shared_scratch=None, nvtx=False,
+                 pairs=False):
+        """nvtx: wrap every stage's launches in a named NVTX range; pairs: run the expert GEMMs of
+        batches above 128 tokens as CTA pairs (both additions of this build)."""
         experts.validate()
         self._weights = experts  # keeps the tensors alive, as the DeviceModel arena does
         self._device = experts.w13.device
@@ -163,7 +166,7 @@ class Nvfp4ExpertRunner:
         share = shared_scratch._handle if shared_scratch is not None else None
         self._shared = shared_scratch
         with torch.cuda.device(self._device):
-            options = _Options(OPTION_NVTX if nvtx else 0)
+            options = _Options((OPTION_NVTX if nvtx else 0) | (OPTION_PAIRS if pairs else 0))
             status = library().gevva_moe_create(ctypes.byref(handle), ctypes.byref(packed),
                                                 self.maximum_tokens, share, ctypes.byref(options))
         if status != 0:

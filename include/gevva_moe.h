@@ -63,6 +63,9 @@ typedef struct {
 #define GEVVA_MOE_OPTION_NVTX 1u /* one NVTX range per stage around its launches (the reference wraps its
                                     phases in NVTX ranges too, e.g. src/gpu/weight_arena.cpp:53,
                                     src/cuda/diagnostics/assistant_prefill_layers.cuh:67-77) */
+#define GEVVA_MOE_OPTION_PAIRS 2u /* batches of more than 128 tokens run the two expert GEMMs as CTA pairs
+                                     (tcgen05 cta_group::2, two row tiles of an expert against shared weight
+                                     rows); same bits, measured slower than the default on B200 */
 typedef struct {
   uint32_t flags; /* 0 or GEVVA_MOE_OPTION_* */
   uint32_t reserved[7];

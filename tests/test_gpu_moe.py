@@ -508,6 +508,30 @@ def test_against_committed_golden_vectors(gm, packed, weights, cuda_device):
     assert rel_l2(bf16_to_f32(bits(out)), bf16_to_f32(golden["layer_out"])) < REL_L2
 
 
+@pytest.mark.parametrize("tokens,kind", [(130, "random"), (300, "skewed"), (4096, "random")])
+def test_cta_pair_gemms_equal_the_single_cta_gemms(gm, weights, cuda_device, tokens, kind):
+    """The two expert GEMMs run by CTA pairs (tcgen05 cta_group::2: two row tiles of an expert
+    against shared weight rows, odd last tiles alone in their pair) give the bits of the
+    one-CTA-per-tile kernels: w2 operand codes and scales, routed rows, layer output."""
+    from gevva_b200 import runtime as rt
+    ids = random_ids(tokens, 5) if kind == "random" else skewed_ids(tokens)
+    x = hashgen.activations(tokens, HIDDEN, 71, cuda_device)
+    dev_ids = torch.from_numpy(ids).to(cuda_device)
+    rw = torch.full((tokens, TOP_K), 0.125, device=cuda_device)
+    routes = tokens * TOP_K
+    results = []
+    for pairs in (False, True):
+        runner = gm.Nvfp4ExpertRunner(weights[0], tokens, pairs=pairs)
+        out = torch.empty_like(x)
+        runner.launch_batch(x, dev_ids, rw, out, tokens)
+        runner.check()
+        results.append((out, runner.buffer(rt.BUF_INTER_CODES)[: routes * INTER // 2].clone(),
+                        runner.buffer(rt.BUF_W2_OUT, torch.bfloat16)[: routes * HIDDEN].clone()))
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
+    assert results[0][0].float().abs().max() > 0
+
+
 def test_nvtx_ranges_do_not_change_results(gm, weights, cuda_device):
     """A runner created with the NVTX option marks its stages and computes the same bits; unknown
     option flags are refused."""
@@ -529,7 +553,7 @@ def test_nvtx_ranges_do_not_change_results(gm, weights, cuda_device):
     packed = rt._Weights(*[t.data_ptr() for t in (w.w13, w.w13_sf, w.w2, w.w2_sf, w.alpha1, w.alpha2,
                                                   w.in_scale_q1, w.in_scale_q2)])
     handle = ctypes.c_void_p()
-    bad = rt._Options(0x80)
+    bad = rt._Options(0x80)   # an option bit that does not exist
     assert rt.library().gevva_moe_create(ctypes.byref(handle), ctypes.byref(packed), 16, None,
                                          ctypes.byref(bad)) == -3
 

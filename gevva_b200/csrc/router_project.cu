@@ -203,7 +203,11 @@ route_project_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     const int row = quarter * 32 + lane;
     const int owner = row & (kRpSplit - 1);
     const int owner_row = row >> 2;
-    if (wait_or_abort<true>(&smem->acc_full, 0, smem, p.status)) {
+    // rows past the end of the batch (most rows of a decode-sized batch) are not sent; the
+    // tensor-memory loads are warp-wide, so a warp takes part if any of its 32 rows exists
+    const bool row_exists = m_tile * kTileM + row < p.tokens;
+    const bool warp_has_rows = m_tile * kTileM + quarter * 32 < p.tokens;
+    if (wait_or_abort<true>(&smem->acc_full, 0, smem, p.status) && warp_has_rows) {
       tc_fence_after_sync();
       const uint32_t remote_row =
           cluster_map_shared(smem_u32(&smem->received[rank][owner_row][0]), static_cast<uint32_t>(owner));
@@ -215,7 +219,8 @@ route_project_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int chunk = part * 8 + i;
-          cluster_store_uint4(remote_row + (static_cast<uint32_t>(received_chunk_position(chunk, owner_row)) << 4),
+          if (row_exists)
+            cluster_store_uint4(remote_row + (static_cast<uint32_t>(received_chunk_position(chunk, owner_row)) << 4),
                               make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]));
         }
       }

@@ -6,8 +6,9 @@
 // route_128_top8_kernel<<<tokens,128>>>).  Here both are one kernel and the logits never
 // reach HBM: tokens sit on MMA-M (128 per tile), the 128 experts on MMA-N, K = 2816.
 //
-// A tile's K range is split over a cluster of four CTAs, so a 4096-token batch runs on 128 SMs
-// and a decode-sized batch streams the router matrix through four SMs instead of one.  Each
+// A tile's K range is split over a cluster of four CTAs (two, or one, for batches whose tiles
+// would otherwise not fit one wave of SMs), so a 4096-token batch runs on 128 SMs and a
+// decode-sized batch streams the router matrix through four SMs instead of one.  Each
 // CTA accumulates its K slice in tensor memory (tcgen05.mma kind::f16 for bf16 operands,
 // kind::f8f6f4 for E4M3).  Tile row r belongs to CTA r % 4 of the cluster: every CTA stores its
 // 128 x 128 fp32 partial sums row by row straight into the owners' shared memory (posted
@@ -27,7 +28,8 @@ namespace gv {
 
 namespace {
 
-constexpr int kRpSplit = 4;      // CTAs per cluster = K slices per token tile
+// CTAs per cluster = K slices per token tile: 4, 2 or 1, the largest that keeps the launch within
+// one wave of SMs (a tile's pass is a chain of latencies, so waves cost more than depth)
 constexpr int kRpStages = 4;
 constexpr int kRpThreads = 192;
 constexpr int kRpTileBytes = kTileM * kTileKBytes;  // 16 KiB: 128 rows of one 128-byte K block
@@ -39,7 +41,7 @@ struct alignas(1024) RouterSmem {
   // included): [source][local row][128 floats]; the 16-byte chunks of a row are permuted
   // (received_chunk_position) so that neither the row-wise stores nor the reduce's reads, where
   // four lanes share a row, meet in a bank.
-  float received[kRpSplit][32][kExperts];
+  float received[kTileM * kExperts];   // [kSplit][128 / kSplit rows][128 floats]
   uint64_t full[kRpStages];
   uint64_t empty[kRpStages];
   uint64_t acc_full;
@@ -107,7 +109,7 @@ __device__ __forceinline__ void issue_router_k_block(uint32_t tmem_acc, uint32_t
 #undef GV_RP_MMA
 }
 
-template <bool kFp8>
+template <bool kFp8, int kSplit>
 __global__ void __launch_bounds__(kRpThreads, 1)
 route_project_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                      const RouterParams p) {
@@ -117,9 +119,10 @@ route_project_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();
-  const int m_tile = static_cast<int>(blockIdx.x) / kRpSplit;
-  const int kb_begin = static_cast<int>(rank) * p.k_blocks / kRpSplit;
-  const int kb_end = (static_cast<int>(rank) + 1) * p.k_blocks / kRpSplit;
+  constexpr int kOwnRows = kTileM / kSplit;   // tile rows this CTA reduces and routes
+  const int m_tile = static_cast<int>(blockIdx.x) / kSplit;
+  const int kb_begin = static_cast<int>(rank) * p.k_blocks / kSplit;
+  const int kb_end = (static_cast<int>(rank) + 1) * p.k_blocks / kSplit;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kRpStages; ++s) {
@@ -201,8 +204,8 @@ route_project_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     // ---------------- epilogue, part 1: partial sums to the rows' owners ----------------
     const int quarter = warp & 3;  // the tensor-memory lanes this warp may read
     const int row = quarter * 32 + lane;
-    const int owner = row & (kRpSplit - 1);
-    const int owner_row = row >> 2;
+    const int owner = row % kSplit;
+    const int owner_row = row / kSplit;
     // rows past the end of the batch (most rows of a decode-sized batch) are not sent; the
     // tensor-memory loads are warp-wide, so a warp takes part if any of its 32 rows exists
     const bool row_exists = m_tile * kTileM + row < p.tokens;
@@ -210,7 +213,8 @@ route_project_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     if (wait_or_abort<true>(&smem->acc_full, 0, smem, p.status) && warp_has_rows) {
       tc_fence_after_sync();
       const uint32_t remote_row =
-          cluster_map_shared(smem_u32(&smem->received[rank][owner_row][0]), static_cast<uint32_t>(owner));
+          cluster_map_shared(smem_u32(smem->received + (rank * kOwnRows + owner_row) * kExperts),
+                             static_cast<uint32_t>(owner));
 #pragma unroll 1
       for (int part = 0; part < 4; ++part) {
         uint32_t r[32];
@@ -234,56 +238,61 @@ route_project_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
   cluster_sync_all();
 
   if (warp >= 2 && !smem->abort) {
-    // ---------------- epilogue, part 2: reduce this CTA's 32 rows and route them ----------------
+    // ---------------- epilogue, part 2: reduce this CTA's rows and route them, 32 at a time ----------------
     const int t = threadIdx.x - 64;
-    const int row_local = t >> 2;   // tile row 4 * row_local + rank
     const int part = t & 3;         // columns [32 * part, 32 * part + 32)
-    const int token = m_tile * kTileM + row_local * kRpSplit + static_cast<int>(rank);
-    const bool valid = token < p.tokens;
-    float4 acc[8];
+#pragma unroll 1
+    for (int pass = 0; pass < kOwnRows / 32; ++pass) {
+      if (m_tile * kTileM + pass * 32 * kSplit >= p.tokens) break;   // no row of this pass exists
+      const int row_local = pass * 32 + (t >> 2);   // tile row kSplit * row_local + rank
+      const int token = m_tile * kTileM + row_local * kSplit + static_cast<int>(rank);
+      const bool valid = token < p.tokens;
+      float4 acc[8];
 #pragma unroll
-    for (int source = 0; source < kRpSplit; ++source) {
-      const float4* source_row = reinterpret_cast<const float4*>(&smem->received[source][row_local][0]);
+      for (int source = 0; source < kSplit; ++source) {
+        const float4* source_row =
+            reinterpret_cast<const float4*>(smem->received + (source * kOwnRows + row_local) * kExperts);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float4 v = source_row[received_chunk_position(part * 8 + i, row_local)];
-        if (source == 0) {
-          acc[i] = v;
-        } else {
-          acc[i].x = __fadd_rn(acc[i].x, v.x);
-          acc[i].y = __fadd_rn(acc[i].y, v.y);
-          acc[i].z = __fadd_rn(acc[i].z, v.z);
-          acc[i].w = __fadd_rn(acc[i].w, v.w);
+        for (int i = 0; i < 8; ++i) {
+          const float4 v = source_row[received_chunk_position(part * 8 + i, row_local)];
+          if (source == 0) {
+            acc[i] = v;
+          } else {
+            acc[i].x = __fadd_rn(acc[i].x, v.x);
+            acc[i].y = __fadd_rn(acc[i].y, v.y);
+            acc[i].z = __fadd_rn(acc[i].z, v.z);
+            acc[i].w = __fadd_rn(acc[i].w, v.w);
+          }
         }
       }
-    }
-    uint32_t packed[16];
+      uint32_t packed[16];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float4 v = acc[i];
-      if (p.bias) {
-        const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias) + part * 8 + i);
-        v.x = __fadd_rn(v.x, b.x);
-        v.y = __fadd_rn(v.y, b.y);
-        v.z = __fadd_rn(v.z, b.z);
-        v.w = __fadd_rn(v.w, b.w);
+      for (int i = 0; i < 8; ++i) {
+        float4 v = acc[i];
+        if (p.bias) {
+          const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias) + part * 8 + i);
+          v.x = __fadd_rn(v.x, b.x);
+          v.y = __fadd_rn(v.y, b.y);
+          v.z = __fadd_rn(v.z, b.z);
+          v.w = __fadd_rn(v.w, b.w);
+        }
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y);
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(v.z, v.w);
+        packed[2 * i] = *reinterpret_cast<const uint32_t*>(&lo);
+        packed[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&hi);
       }
-      const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y);
-      const __nv_bfloat162 hi = __floats2bfloat162_rn(v.z, v.w);
-      packed[2 * i] = *reinterpret_cast<const uint32_t*>(&lo);
-      packed[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&hi);
-    }
-    const size_t safe_token = valid ? static_cast<size_t>(token) : 0;
-    if (p.logits_out && valid) {
-      uint4* out = reinterpret_cast<uint4*>(p.logits_out + safe_token * kExperts + 32 * part);
+      const size_t safe_token = valid ? static_cast<size_t>(token) : 0;
+      if (p.logits_out && valid) {
+        uint4* out = reinterpret_cast<uint4*>(p.logits_out + safe_token * kExperts + 32 * part);
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        out[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+        for (int i = 0; i < 4; ++i)
+          out[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+      }
+      // the reference's rescale of an unscaled FP8 GEMM output (routing_sampling.cuh:405-411)
+      const float rescale = kFp8 ? __fmul_rn(p.activation_scales[safe_token], p.weight_scale[0]) : 1.0f;
+      route_top8_quad(packed, part, kFp8, rescale, valid, p.expert_scale, p.weights + safe_token * kTopK,
+                      p.ids + safe_token * kTopK);
     }
-    // the reference's rescale of an unscaled FP8 GEMM output (routing_sampling.cuh:405-411)
-    const float rescale = kFp8 ? __fmul_rn(p.activation_scales[safe_token], p.weight_scale[0]) : 1.0f;
-    route_top8_quad(packed, part, kFp8, rescale, valid, p.expert_scale, p.weights + safe_token * kTopK,
-                    p.ids + safe_token * kTopK);
   }
 
   tc_fence_before_sync();
@@ -295,7 +304,7 @@ route_project_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
   }
 }
 
-template <bool kFp8>
+template <bool kFp8, int kSplit>
 cudaError_t launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_w, const RouterParams& p,
                            cudaStream_t stream) {
   static bool prepared[64] = {};
@@ -303,25 +312,34 @@ cudaError_t launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_w, c
   cudaError_t e = cudaGetDevice(&device);
   if (e != cudaSuccess) return e;
   if (device >= 0 && device < 64 && !prepared[device]) {
-    e = cudaFuncSetAttribute(route_project_kernel<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(route_project_kernel<kFp8, kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(kRpSmemBytes));
     if (e != cudaSuccess) return e;
     prepared[device] = true;
   }
   const int m_tiles = (p.tokens + kTileM - 1) / kTileM;
   cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(static_cast<unsigned>(m_tiles * kRpSplit));
+  config.gridDim = dim3(static_cast<unsigned>(m_tiles * kSplit));
   config.blockDim = dim3(kRpThreads);
   config.dynamicSmemBytes = kRpSmemBytes;
   config.stream = stream;
   cudaLaunchAttribute attribute[1];
   attribute[0].id = cudaLaunchAttributeClusterDimension;
-  attribute[0].val.clusterDim.x = kRpSplit;
+  attribute[0].val.clusterDim.x = kSplit;
   attribute[0].val.clusterDim.y = 1;
   attribute[0].val.clusterDim.z = 1;
   config.attrs = attribute;
   config.numAttrs = 1;
-  return cudaLaunchKernelEx(&config, route_project_kernel<kFp8>, map_x, map_w, p);
+  return cudaLaunchKernelEx(&config, route_project_kernel<kFp8, kSplit>, map_x, map_w, p);
+}
+
+template <bool kFp8>
+cudaError_t launch_split(const CUtensorMap& map_x, const CUtensorMap& map_w, const RouterParams& p,
+                         cudaStream_t stream) {
+  const int m_tiles = (p.tokens + kTileM - 1) / kTileM;
+  if (m_tiles * 4 <= 160) return launch_variant<kFp8, 4>(map_x, map_w, p, stream);
+  if (m_tiles * 2 <= 160) return launch_variant<kFp8, 2>(map_x, map_w, p, stream);
+  return launch_variant<kFp8, 1>(map_x, map_w, p, stream);
 }
 
 }  // namespace
@@ -346,8 +364,7 @@ int launch_route_project(const void* x, const void* router_w, bool fp8, const fl
   p.status = status;
   p.tokens = tokens;
   p.k_blocks = static_cast<int>(row_bytes / kTileKBytes);
-  const cudaError_t e = fp8 ? launch_variant<true>(map_x, map_w, p, stream)
-                            : launch_variant<false>(map_x, map_w, p, stream);
+  const cudaError_t e = fp8 ? launch_split<true>(map_x, map_w, p, stream) : launch_split<false>(map_x, map_w, p, stream);
   return static_cast<int>(e);
 }
 

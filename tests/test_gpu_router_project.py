@@ -48,7 +48,9 @@ def check_against_oracle(oracle, logits_bits, want_bits, magnitude, ids, weights
 
 
 @pytest.mark.parametrize("rows,biased", [(1, False), (16, False), (40, True), (64, False), (129, True),
-                                         (4096, True), (4096, False)])
+                                         (4096, True), (4096, False),
+                                         (6000, True),     # K split over two CTAs per tile
+                                         (11000, True)])   # one CTA per tile
 def test_bf16_router_projection(oracle, cuda_device, rows, biased):
     import gevva_b200 as gm
     gen = torch.Generator().manual_seed(1000 + rows)
@@ -71,7 +73,7 @@ def test_bf16_router_projection(oracle, cuda_device, rows, biased):
     assert torch.equal(ids, ids2) and torch.equal(w, w2)
 
 
-@pytest.mark.parametrize("rows", [1, 40, 300, 4096])
+@pytest.mark.parametrize("rows", [1, 40, 300, 4096, 6000, 11000])
 def test_fp8_router_projection(oracle, cuda_device, rows):
     import gevva_b200 as gm
     gen = torch.Generator().manual_seed(2000 + rows)

@@ -626,7 +626,7 @@ def run_gpu(args):
     chunk = 500
     sustained_ms, sustained_steps = 0.0, 0
     wall = time.perf_counter()
-    while True:
+    while not args.no_sustained:
         sustained_ms += timed_loop(step, chunk)
         sustained_steps += chunk
         go_on = torch.tensor([1 if time.perf_counter() - wall < 2.0 else 0], device=device)
@@ -747,10 +747,11 @@ def run_gpu(args):
                        "dispatch/combine by stores into peer memory over NVLink",
                        "l2": "inputs larger than L2: 428 MB of expert weights stream every step"},
             "layer_tflops": FLOP_PER_TOKEN * TOKENS / (elapsed_ms / args.steps * 1e-3) / 1e12,
-            "sustained": {"tokens_per_s": TOKENS * world * sustained_steps / (sustained_ms * 1e-3),
-                          "ms_per_step": sustained_ms / sustained_steps, "steps": sustained_steps,
-                          "seconds": sustained_ms * 1e-3, "clocks": sustained_clocks,
-                          "note": "the same step looped back to back for at least two seconds"},
+            "sustained": None if args.no_sustained else {
+                "tokens_per_s": TOKENS * world * sustained_steps / (sustained_ms * 1e-3),
+                "ms_per_step": sustained_ms / sustained_steps, "steps": sustained_steps,
+                "seconds": sustained_ms * 1e-3, "clocks": sustained_clocks,
+                "note": "the same step looped back to back for at least two seconds"},
             "roofline": {"bound": "tensor", "kernel": "grouped_nvfp4_gemm_kernel<kGeglu> (w13 + GeGLU + requantise)",
                          "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s",
                          "frac": achieved / fp4_peak,
@@ -830,6 +831,8 @@ def main():
     parser.add_argument("--no-decode", action="store_true", help="skip the decode-size sweep")
     parser.add_argument("--no-config3", action="store_true", help="skip the 30-layer FFN stack record")
     parser.add_argument("--no-config4", action="store_true", help="skip the 16384-token single-GPU record")
+    parser.add_argument("--no-sustained", action="store_true",
+                        help="skip the two-second loop (for a profiler, which would replay thousands of launches)")
     parser.add_argument("--no-ep-config4", action="store_true",
                         help="with several GPUs: skip the 16384-token Zipf expert-parallel records")
     args = parser.parse_args()

@@ -1,0 +1,438 @@
+// Both expert GEMMs of a decode-sized batch in one persistent kernel.
+//
+// With a few rows per expert the layer is bound by streaming the routed experts' weights from
+// HBM once (3.3 MB per expert).  As two launches (grouped_gemm.cu) the stream stops twice: w13's
+// last items drain while most SMs idle, w2 ramps up from empty pipelines, and 768 + 1408 items of
+// two sizes are dealt to 148 CTAs in two separate, coarse rounds.  Here one grid walks one list,
+// all w13 items (fused GeGLU + requantise epilogue) followed by all w2 items, so weight bytes keep
+// arriving across the boundary and the tail is that of the whole list.
+//
+// A w2 item needs the w2 operand rows of its row tile, which the six w13 items of that tile write.
+// Every epilogue warp of a w13 item adds one to the tile's counter after its stores (release);
+// the activation-side producer of a w2 item waits until the counter says that all 6 x 16 warps
+// have done so (bounded acquire spin), then crosses to the async proxy and issues its TMA loads.
+// The weight-side producer waits for nothing, which is the point.  No cycle of waits exists:
+// every CTA reaches its w2 items only after its own w13 items, and w13 items wait for nothing
+// outside their CTA.  The grid is one CTA per SM, all co-resident.
+//
+// Tile shape, pipeline, roles and epilogue arithmetic are those of the 128 x 256 kernel of
+// grouped_gemm.cu (three stages, store staging for the plain epilogue).  At most 128 tokens, so
+// every expert has at most one row tile.
+#include "gv_common.cuh"
+#include "gv_gemm_parts.cuh"
+#include "gv_launchers.h"
+
+namespace gv {
+
+namespace {
+
+constexpr int kDecStages = 3;
+constexpr int kDecWeightProducerWarp = 2 + 4 * kEpilogueWarpsPerQuarter;  // 18
+constexpr int kDecScaleCopyWarp = kDecWeightProducerWarp + 1;             // 19
+constexpr int kDecThreads = (kDecScaleCopyWarp + 1) * 32;                 // 640
+constexpr uint32_t kDecTmemColumns = 512;
+constexpr uint32_t kDecSfColumn = 256;
+constexpr uint32_t kDecSfColumnsPerStage = 64;
+constexpr int kDecTileBytes = kTileM * kTileKBytes;  // 16 KiB
+constexpr int kW13Items = kFusedItems;               // 6 per row tile
+constexpr int kW13KBlocks = kHidden / kTileK;        // 11
+constexpr int kW2Items = kHidden / 256;              // 11 per row tile
+constexpr int kW2KBlocks = (kInter / 2 + kTileKBytes - 1) / kTileKBytes;             // 3
+constexpr int kW2LastMmas = (kInter / 2 - (kW2KBlocks - 1) * kTileKBytes) / 32;      // 3
+constexpr int kReadyPerTile = kW13Items * 4 * kEpilogueWarpsPerQuarter;              // 96 warp arrivals
+
+struct alignas(1024) DecodeSmem {
+  uint8_t a[kDecStages][kDecTileBytes];
+  uint8_t b[kDecStages][2 * kDecTileBytes];
+  uint8_t sfa[kDecStages][kSfStageBytes];
+  uint8_t sfb[kDecStages][2 * kSfStageBytes];
+  uint8_t staging[4][kStagingBytesPerWarp];
+  uint64_t full[kDecStages];
+  uint64_t empty[kDecStages];
+  uint64_t sf_full[kDecStages];
+  uint64_t acc_full;
+  uint64_t acc_empty;
+  uint32_t tmem_base;
+  volatile int abort;
+  int quarter_left[4];
+  alignas(16) float erf_table[GV_ERF_TABLE_FLOATS];
+};
+
+constexpr size_t kDecSmemBytes = sizeof(DecodeSmem) + 1024;
+static_assert(kDecSmemBytes <= 232448, "shared memory budget");
+static_assert(kDecSfColumn + kDecSfColumnsPerStage * kDecStages <= kDecTmemColumns, "tensor memory budget");
+
+struct DecodeParams {
+  GemmParams w13;   // fused form: next_codes / next_scales / next_scale_q set
+  GemmParams w2;    // plain form: out (and optionally row_dest) set
+  int* tile_ready;  // [row tiles], zero on entry
+};
+
+struct DecodeItem {
+  bool down;   // false: w13 item, true: w2 item
+  int m_tile;
+  int n_tile;
+};
+
+// One list: the w13 items in cost order (the half-filled sixth item of every row tile after all
+// full ones), then the w2 items; dealt to the CTAs in snake order.
+__device__ __forceinline__ bool decode_item(int round, int m_tiles, DecodeItem& item) {
+  const int grid = static_cast<int>(gridDim.x);
+  const int slot = (round & 1) ? grid - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
+  int index = round * grid + slot;
+  const int up_items = m_tiles * kW13Items;
+  if (index < up_items) {
+    item.down = false;
+    const int full = m_tiles * (kW13Items - 1);
+    if (index < full) {
+      item.m_tile = index / (kW13Items - 1);
+      item.n_tile = index - item.m_tile * (kW13Items - 1);
+    } else {
+      item.m_tile = index - full;
+      item.n_tile = kW13Items - 1;
+    }
+    return true;
+  }
+  index -= up_items;
+  if (index >= m_tiles * kW2Items) return false;
+  item.down = true;
+  item.m_tile = index / kW2Items;
+  item.n_tile = index - item.m_tile * kW2Items;
+  return true;
+}
+
+__device__ __forceinline__ int load_acquire_gpu(const int* address) {
+  int value;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(value) : "l"(address) : "memory");
+  return value;
+}
+
+__global__ void __launch_bounds__(kDecThreads, 1)
+decode_experts_kernel(const __grid_constant__ CUtensorMap map_a13, const __grid_constant__ CUtensorMap map_a13_32,
+                      const __grid_constant__ CUtensorMap map_b13, const __grid_constant__ CUtensorMap map_b13_64,
+                      const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_a2_32,
+                      const __grid_constant__ CUtensorMap map_b2, const DecodeParams params) {
+  extern __shared__ uint8_t smem_raw[];
+  DecodeSmem* smem =
+      reinterpret_cast<DecodeSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  int* const status = params.w13.status;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kDecStages; ++s) {
+      mbar_init(&smem->full[s], 2);
+      mbar_init(&smem->empty[s], 1);
+      mbar_init(&smem->sf_full[s], 1);
+    }
+    mbar_init(&smem->acc_full, 1);
+    mbar_init(&smem->acc_empty, kEpilogueThreads);
+    smem->abort = 0;
+    for (int s = 0; s < 4; ++s) smem->quarter_left[s] = 0;
+    fence_barrier_init();
+    prefetch_tensor_map(&map_a13);
+    prefetch_tensor_map(&map_a13_32);
+    prefetch_tensor_map(&map_b13);
+    prefetch_tensor_map(&map_b13_64);
+    prefetch_tensor_map(&map_a2);
+    prefetch_tensor_map(&map_a2_32);
+    prefetch_tensor_map(&map_b2);
+  }
+  if (warp == 1) {
+    tmem_alloc(&smem->tmem_base, kDecTmemColumns);
+    tmem_relinquish();
+  }
+  load_erf_table(smem->erf_table);
+  grid_launch_dependents();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = smem->tmem_base;
+  grid_dependency_wait();
+
+  const int m_tiles = params.w13.num_m_tiles[0];
+  const int total_items = m_tiles * (kW13Items + kW2Items);
+  const int rounds = (total_items + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+
+  if (warp == 0 || warp == kDecWeightProducerWarp) {
+    // ---------------- TMA producers ----------------
+    const bool weight_side = warp == kDecWeightProducerWarp;
+    int stage = 0;
+    uint32_t phase = 0;
+    int issued = 0;
+    bool ok = true;
+    for (int round = 0; ok && round < rounds; ++round) {
+      DecodeItem item;
+      if (!decode_item(round, m_tiles, item)) continue;
+      const GemmParams& p = item.down ? params.w2 : params.w13;
+      const int k_blocks = item.down ? kW2KBlocks : kW13KBlocks;
+      const int last_mmas = item.down ? kW2LastMmas : 4;
+      const int expert = p.tile_expert[item.m_tile];
+      int row = 0, row2 = 0;
+      const uint8_t* sf_src;
+      const uint8_t* sf_src2 = nullptr;
+      bool short_tile = false, half_item = false;
+      if (!weight_side) {
+        row = p.expert_offsets[expert] + (item.m_tile * kTileM - p.scale_row_offsets[expert]);
+        short_tile = p.expert_offsets[expert + 1] - row <= 32;
+        sf_src = p.a_scales + static_cast<size_t>(item.m_tile) * kTileM * p.groups;
+        if (item.down) {
+          // the w2 operand rows of this tile exist once every epilogue warp of its six w13 items
+          // has stored and counted itself
+          const long long start = clock64();
+          bool ready = false;
+          for (uint32_t spin = 0; !ready; ++spin) {
+            ready = load_acquire_gpu(params.tile_ready + item.m_tile) >= kReadyPerTile;
+            if (!ready) {
+              __nanosleep(64);
+              if ((spin & 63u) == 63u && (smem->abort || clock64() - start > kWaitLimitCycles)) {
+                if (!smem->abort) {
+                  smem->abort = 1;
+                  atomicExch(status, static_cast<int>(kWaitTimeout));
+                }
+                break;
+              }
+            }
+          }
+          ok = __all_sync(0xffffffffu, ready);
+          if (!ok) break;
+          // the rows were written by ordinary stores of other SMs; the copies below read them
+          // through the async proxy
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
+      } else if (!item.down) {
+        row = expert * kW13Out + item.n_tile * 128;
+        row2 = row + kInter;
+        half_item = (item.n_tile + 1) * 128 > kInter;
+        sf_src = p.b_scales + (static_cast<size_t>(expert) * kW13Items + item.n_tile) * 256 * p.groups;
+      } else {
+        row = expert * p.n_out + item.n_tile * 256;
+        row2 = row + 128;
+        sf_src = p.b_scales + static_cast<size_t>(row) * p.groups;
+        sf_src2 = sf_src + static_cast<size_t>(128) * p.groups;
+      }
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        ok = __all_sync(0xffffffffu, wait_or_abort<true>(&smem->empty[stage], phase ^ 1u, smem, status));
+        if (!ok) break;
+        if (elect_one()) {
+          const uint32_t sf_bytes = static_cast<uint32_t>(kb + 1 == k_blocks ? last_mmas : 4) * kSfAtomBytes;
+          const int x = kb * kTileKBytes;
+          if (!weight_side) {
+            mbar_arrive_expect_tx(&smem->full[stage], (short_tile ? kDecTileBytes / 4 : kDecTileBytes) + sf_bytes);
+            const CUtensorMap* map = item.down ? (short_tile ? &map_a2_32 : &map_a2) : (short_tile ? &map_a13_32 : &map_a13);
+            tma_load_2d(smem->a[stage], map, &smem->full[stage], x, row);
+            bulk_load_1d(smem->sfa[stage], sf_src + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes, &smem->full[stage]);
+          } else if (!item.down) {
+            mbar_arrive_expect_tx(&smem->full[stage], (half_item ? kDecTileBytes : 2 * kDecTileBytes) + 2 * kSfStageBytes);
+            const CUtensorMap* map = half_item ? &map_b13_64 : &map_b13;
+            tma_load_2d(smem->b[stage], map, &smem->full[stage], x, row);
+            tma_load_2d(smem->b[stage] + kDecTileBytes, map, &smem->full[stage], x, row2);
+            bulk_load_1d(smem->sfb[stage], sf_src + static_cast<size_t>(kb) * 2 * kSfStageBytes, 2 * kSfStageBytes,
+                         &smem->full[stage]);
+          } else {
+            mbar_arrive_expect_tx(&smem->full[stage], 2 * kDecTileBytes + 2 * sf_bytes);
+            tma_load_2d(smem->b[stage], &map_b2, &smem->full[stage], x, row);
+            tma_load_2d(smem->b[stage] + kDecTileBytes, &map_b2, &smem->full[stage], x, row2);
+            bulk_load_1d(smem->sfb[stage], sf_src + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes, &smem->full[stage]);
+            bulk_load_1d(smem->sfb[stage] + kSfStageBytes, sf_src2 + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes,
+                         &smem->full[stage]);
+          }
+        }
+        __syncwarp();
+        ++issued;
+        if (++stage == kDecStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+    if (!ok && lane == 0) {
+      const int pending = issued < kDecStages ? issued : kDecStages;
+      int s = stage;
+      uint32_t ph = phase;
+      for (int i = 0; i < pending; ++i) {
+        if (--s < 0) {
+          s = kDecStages - 1;
+          ph ^= 1u;
+        }
+        mbar_wait_bounded(&smem->full[s], ph, 40000000ll);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    int stage = 0;
+    uint32_t phase = 0, acc_phase = 0;
+    const uint32_t a_lo0 = (smem_u32(smem->a[0]) & 0x3ffffu) >> 4;
+    const uint32_t b_lo0 = (smem_u32(smem->b[0]) & 0x3ffffu) >> 4;
+    constexpr uint32_t hi_ab = (1024u >> 4) | (1u << 14) | (2u << 29);
+    const bool leader = elect_one();
+    for (int round = 0; round < rounds; ++round) {
+      DecodeItem item;
+      if (!decode_item(round, m_tiles, item)) continue;
+      const int k_blocks = item.down ? kW2KBlocks : kW13KBlocks;
+      if (!__all_sync(0xffffffffu, wait_or_abort<false>(&smem->acc_empty, acc_phase ^ 1u, smem, status))) break;
+      acc_phase ^= 1u;
+      bool ok = true;
+      tc_fence_after_sync();
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        ok = wait_or_abort<false>(&smem->sf_full[stage], phase, smem, status);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * (kDecTileBytes >> 4);
+        const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(stage) * (2 * kDecTileBytes >> 4);
+        const uint32_t tmem_sf = tmem_base + kDecSfColumn + kDecSfColumnsPerStage * stage;
+        if (leader) {
+          const uint32_t accumulate = kb != 0 ? 1u : 0u;
+          if (item.down && kb + 1 == k_blocks) issue_mmas<kW2LastMmas, 256>(tmem_base, tmem_sf, a_lo, b_lo, hi_ab, accumulate);
+          else issue_mmas<4, 256>(tmem_base, tmem_sf, a_lo, b_lo, hi_ab, accumulate);
+          tc_commit(&smem->empty[stage]);
+          if (kb + 1 == k_blocks) tc_commit(&smem->acc_full);
+        }
+        if (++stage == kDecStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (!ok) break;
+    }
+  } else if (warp == kDecScaleCopyWarp) {
+    // ---------------- scale-factor copier ----------------
+    int stage = 0;
+    uint32_t phase = 0;
+    const uint32_t sfa_lo0 = (smem_u32(smem->sfa[0]) & 0x3ffffu) >> 4;
+    const uint32_t sfb_lo0 = (smem_u32(smem->sfb[0]) & 0x3ffffu) >> 4;
+    constexpr uint32_t hi_sf = (128u >> 4) | (1u << 14);
+    const bool leader = elect_one();
+    bool ok = true;
+    for (int round = 0; ok && round < rounds; ++round) {
+      DecodeItem item;
+      if (!decode_item(round, m_tiles, item)) continue;
+      const int k_blocks = item.down ? kW2KBlocks : kW13KBlocks;
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        ok = wait_or_abort<false>(&smem->full[stage], phase, smem, status);
+        if (!ok) break;
+        const uint32_t sfa_lo = sfa_lo0 + static_cast<uint32_t>(stage) * (kSfStageBytes >> 4);
+        const uint32_t sfb_lo = sfb_lo0 + static_cast<uint32_t>(stage) * (2 * kSfStageBytes >> 4);
+        const uint32_t tmem_sf = tmem_base + kDecSfColumn + kDecSfColumnsPerStage * stage;
+        if (leader) {
+          if (item.down && kb + 1 == k_blocks) issue_sf_copies<kW2LastMmas, 256>(tmem_sf, sfa_lo, sfb_lo, hi_sf);
+          else issue_sf_copies<4, 256>(tmem_sf, sfa_lo, sfb_lo, hi_sf);
+          tc_commit(&smem->sf_full[stage]);
+        }
+        if (++stage == kDecStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ---------------- epilogue: 16 warps ----------------
+    const int quarter = warp & 3;
+    const int sub = (warp - 2) >> 2;
+    uint32_t acc_phase = 0;
+    uint8_t* staging = smem->staging[quarter];
+    for (int round = 0; round < rounds; ++round) {
+      DecodeItem item;
+      if (!decode_item(round, m_tiles, item)) continue;
+      const GemmParams& p = item.down ? params.w2 : params.w13;
+      const int m_tile = item.m_tile, n_tile = item.n_tile;
+      const int expert = p.tile_expert[m_tile];
+      const int row0 = p.expert_offsets[expert] + (m_tile * kTileM - p.scale_row_offsets[expert]);
+      const int rows_valid = p.expert_offsets[expert + 1] - row0;
+      const float alpha = p.alpha[expert];
+      const bool acc_ready = wait_or_abort<true>(&smem->acc_full, acc_phase, smem, status);
+      acc_phase ^= 1u;
+      // the four warps of a quarter meet at named barriers in the plain epilogue: they leave together
+      if (!acc_ready) smem->quarter_left[quarter] = 1;
+      named_barrier(1 + quarter, kEpilogueWarpsPerQuarter * 32);
+      if (*reinterpret_cast<volatile int*>(&smem->quarter_left[quarter])) break;
+      tc_fence_after_sync();
+      const int row_local = quarter * 32 + lane;
+      const uint32_t tmem_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      if (item.down) {
+        uint32_t r0[32], r1[32];
+        tmem_load_32x32(tmem_row + sub * 32, r0);
+        tmem_load_32x32(tmem_row + kStoreColumns + sub * 32, r1);
+        tmem_load_wait();
+        tc_fence_before_sync();
+        mbar_arrive(&smem->acc_empty);
+        if (quarter * 32 < rows_valid) {
+          stage_and_store(r0, alpha, staging, quarter, sub, lane, rows_valid, row0, n_tile * 256, p);
+          stage_and_store(r1, alpha, staging, quarter, sub, lane, rows_valid, row0, n_tile * 256 + kStoreColumns, p);
+        }
+      } else {
+        uint32_t up0[16], gate0[16], up1[16], gate1[16];
+        tmem_load_32x16(tmem_row + sub * 32, up0);
+        tmem_load_32x16(tmem_row + 128 + sub * 32, gate0);
+        tmem_load_32x16(tmem_row + sub * 32 + 16, up1);
+        tmem_load_32x16(tmem_row + 128 + sub * 32 + 16, gate1);
+        tmem_load_wait();
+        tc_fence_before_sync();
+        mbar_arrive(&smem->acc_empty);
+        const bool columns_exist = n_tile * 128 + sub * 32 < kInter;
+        if (row_local < rows_valid && columns_exist) {
+          const float multiplier = p.next_scale_q[expert];
+          uint4 codes;
+          const uint32_t scale0 = geglu_block(up0, gate0, alpha, multiplier, smem->erf_table, codes.x, codes.y);
+          const uint32_t scale1 = geglu_block(up1, gate1, alpha, multiplier, smem->erf_table, codes.z, codes.w);
+          *reinterpret_cast<uint4*>(p.next_codes + static_cast<size_t>(row0 + row_local) * (kInter / 2) +
+                                    n_tile * 64 + sub * 16) = codes;
+          constexpr int groups = kInter / 16;
+          *reinterpret_cast<uint16_t*>(p.next_scales + static_cast<size_t>(m_tile) * kTileM * groups +
+                                       sf_offset(row_local, 8 * n_tile + 2 * sub, groups)) =
+              static_cast<uint16_t>(scale0 | (scale1 << 8));
+        }
+        // this warp's share of the tile's w2 operand is written: publish it
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(params.tile_ready + m_tile, 1);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    __syncwarp();
+    tmem_dealloc(tmem_base, kDecTmemColumns);
+  }
+}
+
+void fill_params(GemmParams& p, const GemmOperands& op, const RoutePlan& plan) {
+  p = GemmParams{};
+  p.a_scales = op.a_scales;
+  p.b_scales = op.b_scales;
+  p.alpha = op.alpha;
+  p.out = static_cast<__nv_bfloat16*>(op.out);
+  p.row_dest = op.row_dest;
+  p.next_codes = op.next_codes;
+  p.next_scales = op.next_scales;
+  p.next_scale_q = op.next_scale_q;
+  p.tile_expert = plan.tile_expert;
+  p.expert_offsets = plan.expert_offsets;
+  p.scale_row_offsets = plan.scale_row_offsets;
+  p.num_m_tiles = plan.num_m_tiles;
+  p.status = plan.status;
+  p.n_out = op.n_out;
+  p.groups = op.k_in / 16;
+}
+
+}  // namespace
+
+int prepare_decode_experts() {
+  return static_cast<int>(cudaFuncSetAttribute(decode_experts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(kDecSmemBytes)));
+}
+
+void launch_decode_experts(const GemmOperands& w13_fused, const GemmOperands& w2, const RoutePlan& plan, int sm_count,
+                           cudaStream_t stream) {
+  DecodeParams params{};
+  fill_params(params.w13, w13_fused, plan);
+  fill_params(params.w2, w2, plan);
+  params.tile_ready = plan.tile_ready;
+  launch_chained(decode_experts_kernel, dim3(sm_count), dim3(kDecThreads), kDecSmemBytes, stream, w13_fused.map_a,
+                 w13_fused.map_a32, w13_fused.map_b, w13_fused.map_b64, w2.map_a, w2.map_a32, w2.map_b, params);
+}
+
+}  // namespace gv

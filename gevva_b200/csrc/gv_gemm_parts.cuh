@@ -110,5 +110,90 @@ __device__ __forceinline__ uint32_t geglu_block(const uint32_t (&up)[16], const 
 constexpr int kFusedItems = (kInter + 127) / 128;  // 6
 
 
+// Instruction descriptor: E2M1 x E2M1 (format 1 in the mxf4 kinds), both K-major,
+// UE4M3 scales (bit 23 clear), N at [17,23) in units of 8, M at [24,29) in units of 16,
+// K = 64 (bit 31 clear), scale ids 0.
+template <int kN>
+constexpr uint32_t kInstrDesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kN >> 3) << 17) |
+                                (static_cast<uint32_t>(kTileM >> 4) << 24);
+
+// One K block's worth of tensor-core work, issued by two threads.  The scale copier issues
+// kMmas scale-factor atom copies per operand half (shared -> tensor memory, issue_sf_copies); the
+// MMA thread, once those have landed, issues kMmas MMAs of K = 64 (issue_mmas).  Everything is
+// derived from 32-bit descriptor bases with immediate offsets so that an issuing thread spends
+// a handful of integer instructions per tcgen05 instruction.
+//   a_lo / b_lo     low words of the operand descriptors of this stage (address >> 4)
+//   sfa_lo / sfb_lo low words of the scale-factor descriptors of this stage
+//   hi_ab / hi_sf   high words (stride, version, swizzle) shared by all stages
+// Scale columns of a K block in tensor memory: at N = 128, A of MMA j at +4j and B at +16+4j;
+// at N = 256, A at +16j, B rows 0..127 at +16j+4, B rows 128..255 at +16j+8 (the second half of
+// the weight scales lies 2 KiB = 128 descriptor units after the first in shared memory).
+template <int kMmas, int kN>
+__device__ __forceinline__ void issue_sf_copies(uint32_t tmem_sf, uint32_t sfa_lo, uint32_t sfb_lo, uint32_t hi_sf) {
+  static_assert(kMmas >= 1 && kMmas <= 4, "a K block holds one to four MMAs");
+#define GV_SF_OPERANDS ::"r"(tmem_sf), "r"(sfa_lo), "r"(sfb_lo), "r"(hi_sf) : "memory"
+#define GV_SF_PROLOGUE "{\n\t.reg .b32 lo, ta;\n\t.reg .b64 d0;\n\t"
+#define GV_SF_ONE(source, source_offset, column)                             \
+  "add.u32 lo, " source ", " source_offset ";\n\t"                           \
+  "mov.b64 d0, {lo, %3};\n\t"                                                \
+  "add.u32 ta, %0, " column ";\n\t"                                          \
+  "tcgen05.cp.cta_group::1.32x128b.warpx4 [ta], d0;\n\t"
+  if constexpr (kN == 128) {
+#define GV_SF_COPY(j) GV_SF_ONE("%1", #j "*32", #j "*4") GV_SF_ONE("%2", #j "*32", "16+" #j "*4")
+    asm volatile(GV_SF_PROLOGUE GV_SF_COPY(0) "}" GV_SF_OPERANDS);
+    if constexpr (kMmas >= 2) asm volatile(GV_SF_PROLOGUE GV_SF_COPY(1) "}" GV_SF_OPERANDS);
+    if constexpr (kMmas >= 3) asm volatile(GV_SF_PROLOGUE GV_SF_COPY(2) "}" GV_SF_OPERANDS);
+    if constexpr (kMmas >= 4) asm volatile(GV_SF_PROLOGUE GV_SF_COPY(3) "}" GV_SF_OPERANDS);
+#undef GV_SF_COPY
+  } else {
+#define GV_SF_COPY(j)                                                        \
+  GV_SF_ONE("%1", #j "*32", #j "*16") GV_SF_ONE("%2", #j "*32", "4+" #j "*16") \
+  GV_SF_ONE("%2", "128+" #j "*32", "8+" #j "*16")
+    asm volatile(GV_SF_PROLOGUE GV_SF_COPY(0) "}" GV_SF_OPERANDS);
+    if constexpr (kMmas >= 2) asm volatile(GV_SF_PROLOGUE GV_SF_COPY(1) "}" GV_SF_OPERANDS);
+    if constexpr (kMmas >= 3) asm volatile(GV_SF_PROLOGUE GV_SF_COPY(2) "}" GV_SF_OPERANDS);
+    if constexpr (kMmas >= 4) asm volatile(GV_SF_PROLOGUE GV_SF_COPY(3) "}" GV_SF_OPERANDS);
+#undef GV_SF_COPY
+  }
+#undef GV_SF_ONE
+#undef GV_SF_PROLOGUE
+#undef GV_SF_OPERANDS
+}
+
+template <int kMmas, int kN>
+__device__ __forceinline__ void issue_mmas(uint32_t tmem_acc, uint32_t tmem_sf, uint32_t a_lo, uint32_t b_lo,
+                                           uint32_t hi_ab, uint32_t accumulate) {
+  static_assert(kMmas >= 1 && kMmas <= 4, "a K block holds one to four MMAs");
+#define GV_OPERANDS                                                                                  \
+  ::"r"(tmem_acc), "r"(tmem_sf), "r"(a_lo), "r"(b_lo), "r"(hi_ab), "r"(kInstrDesc<kN>), "r"(accumulate) \
+  : "memory"
+#define GV_PROLOGUE "{\n\t.reg .pred p, pt;\n\t.reg .b32 lo, ta, tb;\n\t.reg .b64 d0, d1;\n\t" \
+                    "setp.ne.b32 p, %6, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+#define GV_MMA(j, step, sfb_column, pred)                                  \
+  "add.u32 lo, %2, " #j "*2;\n\t"                                          \
+  "mov.b64 d0, {lo, %4};\n\t"                                              \
+  "add.u32 lo, %3, " #j "*2;\n\t"                                          \
+  "mov.b64 d1, {lo, %4};\n\t"                                              \
+  "add.u32 ta, %1, " #j "*" #step ";\n\t"                                  \
+  "add.u32 tb, %1, " #j "*" #step "+" #sfb_column ";\n\t"                  \
+  "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X"      \
+  " [%0], d0, d1, %5, [ta], [tb], " pred ";\n\t"
+  if constexpr (kN == 128) {
+    asm volatile(GV_PROLOGUE GV_MMA(0, 4, 16, "p") "}" GV_OPERANDS);
+    if constexpr (kMmas >= 2) asm volatile(GV_PROLOGUE GV_MMA(1, 4, 16, "pt") "}" GV_OPERANDS);
+    if constexpr (kMmas >= 3) asm volatile(GV_PROLOGUE GV_MMA(2, 4, 16, "pt") "}" GV_OPERANDS);
+    if constexpr (kMmas >= 4) asm volatile(GV_PROLOGUE GV_MMA(3, 4, 16, "pt") "}" GV_OPERANDS);
+  } else {
+    asm volatile(GV_PROLOGUE GV_MMA(0, 16, 4, "p") "}" GV_OPERANDS);
+    if constexpr (kMmas >= 2) asm volatile(GV_PROLOGUE GV_MMA(1, 16, 4, "pt") "}" GV_OPERANDS);
+    if constexpr (kMmas >= 3) asm volatile(GV_PROLOGUE GV_MMA(2, 16, 4, "pt") "}" GV_OPERANDS);
+    if constexpr (kMmas >= 4) asm volatile(GV_PROLOGUE GV_MMA(3, 16, 4, "pt") "}" GV_OPERANDS);
+  }
+#undef GV_MMA
+#undef GV_OPERANDS
+#undef GV_PROLOGUE
+}
+
+
 }  // namespace
 }  // namespace gv

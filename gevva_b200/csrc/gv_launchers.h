@@ -21,6 +21,8 @@ struct RoutePlan {
   int* pair_tile;          // optional [R/128 + 128]: 2 * (first tile of a pair) + (1 if the pair has two
                            // tiles); a pair = two consecutive 128-row tiles of one expert, or its last odd one
   int* num_pairs;          // optional [1]
+  int* tile_ready;         // optional [R/128 + 128]: per row tile, epilogue warps of its w13 items that have
+                           // stored their share of the w2 operand (merged decode kernel); zeroed by the sort
   const int* tile_first;   // optional [1]: a GEMM launch covers tiles [tile_first, tile_first + num_m_tiles)
   int* chunk_hist;         // [ceil(R/1024) * 128] scratch of the multi-block sort
   int* status;             // [1]   device status word (gv::Status)
@@ -103,6 +105,12 @@ bool make_operand_tensor_map(CUtensorMap* map, const void* base, uint64_t rows, 
 // The CTA-pair form (grouped_gemm_pair.cu): fused w13 (op.fused_geglu) or plain w2 (n_out % 256 == 0).
 void launch_grouped_gemm_pairs(const GemmOperands& op, const RoutePlan& plan, int sm_count, cudaStream_t stream);
 int prepare_grouped_gemm_pairs();
+
+// Both expert GEMMs of a batch of at most 128 tokens in one persistent launch (grouped_gemm_decode.cu):
+// the fused w13 form, then w2, with per-tile readiness counters (plan.tile_ready) in between.
+void launch_decode_experts(const GemmOperands& w13_fused, const GemmOperands& w2, const RoutePlan& plan,
+                           int sm_count, cudaStream_t stream);
+int prepare_decode_experts();
 
 // Must be called once per device before launch_grouped_gemm (sets the dynamic
 // shared-memory limit).  Returns a cudaError_t value.

@@ -26,7 +26,7 @@ inline ScratchSizes scratch_sizes(int tokens) {
   const size_t padded_rows = s.routes + kExpertCount * 127;
   s.tile_capacity = s.routes / 128 + kExpertCount + 1;
   s.chunks = (s.routes + 1023) / 1024;
-  s.int_count = 3 * s.routes + 2 * (kExpertCount + 1) + 2 * (s.tile_capacity + 1) + s.chunks * kExpertCount + 1 + 64;
+  s.int_count = 3 * s.routes + 2 * (kExpertCount + 1) + 3 * (s.tile_capacity + 1) + s.chunks * kExpertCount + 1 + 64;
   s.bytes[0] = s.routes * (kHiddenWidth / 2);
   s.bytes[1] = padded_rows * (kHiddenWidth / 16);
   s.bytes[2] = s.routes * 2 * kInterWidth * 2;

@@ -144,6 +144,7 @@ int make_scratch(int tokens, Scratch** out) {
   s->plan.num_m_tiles = carve(1);
   s->plan.pair_tile = carve(s->tile_capacity);
   s->plan.num_pairs = carve(1);
+  s->plan.tile_ready = carve(s->tile_capacity + 1);
   s->plan.chunk_hist = carve(chunks * kExperts);
   s->plan.status = carve(1);
   s->plan.sync = carve(2);  // taken from the 64 spare ints; zero like everything else here
@@ -184,6 +185,7 @@ struct gevva_moe {
   uint8_t* w13_sf_tiled = nullptr;  // runner-owned re-tiling of weights.w13_sf
   int sm_count = 0;
   bool pairs = false;               // GEVVA_MOE_OPTION_PAIRS: prefill-sized launches run the expert GEMMs as CTA pairs
+  bool merged_decode = true;        // batches of at most 128 tokens: w13 and w2 in one launch (GEVVA_MOE_DECODE_MERGED=0: two)
   bool nvtx = false;                // GEVVA_MOE_OPTION_NVTX: one range per stage around its launches
 };
 
@@ -241,6 +243,8 @@ int gevva_moe_create(gevva_moe** out, const gevva_moe_weights* weights, int max_
   // The CTA-pair form (tcgen05 cta_group::2) is bit-identical but measured slower than one CTA per
   // tile on this part (175 against 102 us for w13 at 4096 tokens), so it is opt-in: by option, or
   // for a whole process by GEVVA_MOE_PAIRS=1.
+  const char* merged_env = std::getenv("GEVVA_MOE_DECODE_MERGED");
+  m->merged_decode = !(merged_env && merged_env[0] == '0');
   const char* pairs_env = std::getenv("GEVVA_MOE_PAIRS");
   m->pairs = (options && (options->flags & GEVVA_MOE_OPTION_PAIRS)) || (pairs_env && pairs_env[0] == '1');
   m->sm_count = prop.multiProcessorCount;
@@ -396,6 +400,15 @@ int gevva_moe_launch_stages(gevva_moe* runner, const void* in, const int* ids,
                                 s->input_sf, stream);
   }
   const unsigned both = GEVVA_MOE_STAGE_W13 | GEVVA_MOE_STAGE_GEGLU;
+  const unsigned gemms = both | GEVVA_MOE_STAGE_W2;
+  if ((stages & gemms) == gemms && !(stages & GEVVA_MOE_STAGE_UNFUSED) && runner->merged_decode &&
+      tokens <= gv::kFusedSortQuantizeMaxTokens && (stages & front) == front) {
+    // decode-sized batch: both GEMMs in one persistent launch, weights streaming across the boundary
+    // (the readiness counters it needs are zeroed by the fused sort + quantise launch above)
+    StageRange range(runner->nvtx, "gevva_moe.w13+geglu+w2");
+    gv::launch_decode_experts(runner->w13_fused, runner->w2, s->plan, runner->sm_count, stream);
+    stages &= ~gemms;
+  }
   if ((stages & both) == both && !(stages & GEVVA_MOE_STAGE_UNFUSED)) {
     // production path: GeGLU + requantise inside the w13 epilogue, no bf16 w13 output
     StageRange range(runner->nvtx, "gevva_moe.w13+geglu");

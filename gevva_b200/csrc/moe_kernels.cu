@@ -538,7 +538,10 @@ route_sort_quantize_small_kernel(const __nv_bfloat16* __restrict__ input, const 
         plan.expert_offsets[expert] = row;
         plan.scale_row_offsets[expert] = tile * kTileM;
         const int expert_tiles = (counts[i] + kTileM - 1) / kTileM;
-        for (int j = 0; j < expert_tiles; ++j) plan.tile_expert[tile + j] = expert;
+        for (int j = 0; j < expert_tiles; ++j) {
+          plan.tile_expert[tile + j] = expert;
+          if (plan.tile_ready) plan.tile_ready[tile + j] = 0;
+        }
       }
       row += counts[i];
       tile += (counts[i] + kTileM - 1) / kTileM;

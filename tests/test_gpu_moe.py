@@ -532,6 +532,34 @@ def test_cta_pair_gemms_equal_the_single_cta_gemms(gm, weights, cuda_device, tok
     assert results[0][0].float().abs().max() > 0
 
 
+@pytest.mark.parametrize("tokens,kind", [(1, "random"), (8, "random"), (40, "skewed"), (64, "random"),
+                                         (128, "skewed")])
+def test_merged_decode_launch_equals_two_launches(gm, weights, cuda_device, tokens, kind, monkeypatch):
+    """Batches of at most 128 tokens run both expert GEMMs in one persistent launch (w2 items wait
+    on per-tile readiness counters); the bits must be those of the two separate launches, also when
+    the launch is repeated on the same scratch (the counters are reset by the sort)."""
+    from gevva_b200 import runtime as rt
+    ids = random_ids(tokens, 17) if kind == "random" else skewed_ids(tokens)
+    x = hashgen.activations(tokens, HIDDEN, 73, cuda_device)
+    dev_ids = torch.from_numpy(ids).to(cuda_device)
+    rw = torch.full((tokens, TOP_K), 0.125, device=cuda_device)
+    routes = tokens * TOP_K
+    results = []
+    for merged in ("0", "1"):
+        monkeypatch.setenv("GEVVA_MOE_DECODE_MERGED", merged)
+        runner = gm.Nvfp4ExpertRunner(weights[0], max(tokens, 2))
+        out = torch.empty_like(x)
+        for _ in range(3):
+            out.zero_()
+            runner.launch_batch(x, dev_ids, rw, out, tokens)
+        runner.check()
+        results.append((out, runner.buffer(rt.BUF_INTER_CODES)[: routes * INTER // 2].clone(),
+                        runner.buffer(rt.BUF_W2_OUT, torch.bfloat16)[: routes * HIDDEN].clone()))
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
+    assert results[0][0].float().abs().max() > 0
+
+
 def test_nvtx_ranges_do_not_change_results(gm, weights, cuda_device):
     """A runner created with the NVTX option marks its stages and computes the same bits; unknown
     option flags are refused."""

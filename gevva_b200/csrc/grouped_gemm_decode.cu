@@ -16,8 +16,9 @@
 // outside their CTA.  The grid is one CTA per SM, all co-resident.
 //
 // Tile shape, pipeline, roles and epilogue arithmetic are those of the 128 x 256 kernel of
-// grouped_gemm.cu (three stages, store staging for the plain epilogue).  At most 128 tokens, so
-// every expert has at most one row tile.
+// grouped_gemm.cu, with four stages: the plain epilogue stores its few rows straight from
+// registers (64 bytes per thread and half tile), so no staging tile takes shared memory from the
+// pipeline.  At most 128 tokens, so every expert has at most one row tile.
 #include "gv_common.cuh"
 #include "gv_gemm_parts.cuh"
 #include "gv_launchers.h"
@@ -26,7 +27,7 @@ namespace gv {
 
 namespace {
 
-constexpr int kDecStages = 3;
+constexpr int kDecStages = 4;
 constexpr int kDecWeightProducerWarp = 2 + 4 * kEpilogueWarpsPerQuarter;  // 18
 constexpr int kDecScaleCopyWarp = kDecWeightProducerWarp + 1;             // 19
 constexpr int kDecThreads = (kDecScaleCopyWarp + 1) * 32;                 // 640
@@ -46,7 +47,6 @@ struct alignas(1024) DecodeSmem {
   uint8_t b[kDecStages][2 * kDecTileBytes];
   uint8_t sfa[kDecStages][kSfStageBytes];
   uint8_t sfb[kDecStages][2 * kSfStageBytes];
-  uint8_t staging[4][kStagingBytesPerWarp];
   uint64_t full[kDecStages];
   uint64_t empty[kDecStages];
   uint64_t sf_full[kDecStages];
@@ -54,7 +54,6 @@ struct alignas(1024) DecodeSmem {
   uint64_t acc_empty;
   uint32_t tmem_base;
   volatile int abort;
-  int quarter_left[4];
   alignas(16) float erf_table[GV_ERF_TABLE_FLOATS];
 };
 
@@ -74,8 +73,8 @@ struct DecodeItem {
   int n_tile;
 };
 
-// One list: the w13 items in cost order (the half-filled sixth item of every row tile after all
-// full ones), then the w2 items; dealt to the CTAs in snake order.
+// One list: the w13 items tile by tile (so that the first tiles' w2 operands are complete long
+// before the last w13 item ends), then the w2 items; dealt to the CTAs in snake order.
 __device__ __forceinline__ bool decode_item(int round, int m_tiles, DecodeItem& item) {
   const int grid = static_cast<int>(gridDim.x);
   const int slot = (round & 1) ? grid - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
@@ -83,14 +82,8 @@ __device__ __forceinline__ bool decode_item(int round, int m_tiles, DecodeItem& 
   const int up_items = m_tiles * kW13Items;
   if (index < up_items) {
     item.down = false;
-    const int full = m_tiles * (kW13Items - 1);
-    if (index < full) {
-      item.m_tile = index / (kW13Items - 1);
-      item.n_tile = index - item.m_tile * (kW13Items - 1);
-    } else {
-      item.m_tile = index - full;
-      item.n_tile = kW13Items - 1;
-    }
+    item.m_tile = index / kW13Items;
+    item.n_tile = index - item.m_tile * kW13Items;
     return true;
   }
   index -= up_items;
@@ -99,6 +92,20 @@ __device__ __forceinline__ bool decode_item(int round, int m_tiles, DecodeItem& 
   item.m_tile = index / kW2Items;
   item.n_tile = index - item.m_tile * kW2Items;
   return true;
+}
+
+// 32 accumulator columns of one row, scaled, rounded to bf16 and stored: 64 contiguous bytes.
+__device__ __forceinline__ void store_row_piece(const uint32_t (&r)[32], float alpha, __nv_bfloat16* destination) {
+  uint4* out = reinterpret_cast<uint4*>(destination);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 v;
+    v.x = pack_bf16x2(__fmul_rn(alpha, __uint_as_float(r[8 * i])), __fmul_rn(alpha, __uint_as_float(r[8 * i + 1])));
+    v.y = pack_bf16x2(__fmul_rn(alpha, __uint_as_float(r[8 * i + 2])), __fmul_rn(alpha, __uint_as_float(r[8 * i + 3])));
+    v.z = pack_bf16x2(__fmul_rn(alpha, __uint_as_float(r[8 * i + 4])), __fmul_rn(alpha, __uint_as_float(r[8 * i + 5])));
+    v.w = pack_bf16x2(__fmul_rn(alpha, __uint_as_float(r[8 * i + 6])), __fmul_rn(alpha, __uint_as_float(r[8 * i + 7])));
+    out[i] = v;
+  }
 }
 
 __device__ __forceinline__ int load_acquire_gpu(const int* address) {
@@ -128,7 +135,6 @@ decode_experts_kernel(const __grid_constant__ CUtensorMap map_a13, const __grid_
     mbar_init(&smem->acc_full, 1);
     mbar_init(&smem->acc_empty, kEpilogueThreads);
     smem->abort = 0;
-    for (int s = 0; s < 4; ++s) smem->quarter_left[s] = 0;
     fence_barrier_init();
     prefetch_tensor_map(&map_a13);
     prefetch_tensor_map(&map_a13_32);
@@ -330,7 +336,6 @@ decode_experts_kernel(const __grid_constant__ CUtensorMap map_a13, const __grid_
     const int quarter = warp & 3;
     const int sub = (warp - 2) >> 2;
     uint32_t acc_phase = 0;
-    uint8_t* staging = smem->staging[quarter];
     for (int round = 0; round < rounds; ++round) {
       DecodeItem item;
       if (!decode_item(round, m_tiles, item)) continue;
@@ -342,10 +347,7 @@ decode_experts_kernel(const __grid_constant__ CUtensorMap map_a13, const __grid_
       const float alpha = p.alpha[expert];
       const bool acc_ready = wait_or_abort<true>(&smem->acc_full, acc_phase, smem, status);
       acc_phase ^= 1u;
-      // the four warps of a quarter meet at named barriers in the plain epilogue: they leave together
-      if (!acc_ready) smem->quarter_left[quarter] = 1;
-      named_barrier(1 + quarter, kEpilogueWarpsPerQuarter * 32);
-      if (*reinterpret_cast<volatile int*>(&smem->quarter_left[quarter])) break;
+      if (!acc_ready) break;
       tc_fence_after_sync();
       const int row_local = quarter * 32 + lane;
       const uint32_t tmem_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -356,9 +358,11 @@ decode_experts_kernel(const __grid_constant__ CUtensorMap map_a13, const __grid_
         tmem_load_wait();
         tc_fence_before_sync();
         mbar_arrive(&smem->acc_empty);
-        if (quarter * 32 < rows_valid) {
-          stage_and_store(r0, alpha, staging, quarter, sub, lane, rows_valid, row0, n_tile * 256, p);
-          stage_and_store(r1, alpha, staging, quarter, sub, lane, rows_valid, row0, n_tile * 256 + kStoreColumns, p);
+        if (row_local < rows_valid) {
+          __nv_bfloat16* row = p.row_dest ? reinterpret_cast<__nv_bfloat16*>(p.row_dest[row0 + row_local])
+                                          : p.out + static_cast<size_t>(row0 + row_local) * p.n_out;
+          store_row_piece(r0, alpha, row + n_tile * 256 + sub * 32);
+          store_row_piece(r1, alpha, row + n_tile * 256 + kStoreColumns + sub * 32);
         }
       } else {
         uint32_t up0[16], gate0[16], up1[16], gate1[16];

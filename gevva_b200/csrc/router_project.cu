@@ -139,6 +139,9 @@ route_project_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     tmem_alloc(&smem->tmem_base, kExperts);
     tmem_relinquish();
   }
+  // The next kernel of the stream (launched with programmatic serialization) may take its place on
+  // the SMs now; it waits at its own top for this grid to complete.
+  grid_launch_dependents();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();

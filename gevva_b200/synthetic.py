@@ -110,7 +110,7 @@ class SyntheticLayer:
                                     (ones / s1).contiguous(), ones.clone())
         tokens = x.shape[0]
         runner = Nvfp4ExpertRunner(provisional, tokens)
-        _, ids = route_128_top8(self.logits(x), self.expert_scale)
+        _, ids = self.route(x, runner=runner)
         runner.launch_stages(STAGE_SORT | STAGE_QUANTIZE | STAGE_W13, tokens, input=x,
                              expert_ids=ids)
         runner.check()

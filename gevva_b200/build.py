@@ -10,7 +10,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libgevva_moe.so")
-SOURCES = ["moe_kernels.cu", "grouped_gemm.cu", "grouped_gemm_pair.cu", "grouped_gemm_decode.cu", "moe_abi.cu", "router_project.cu", "route_sort_noalloc.cu", "ep.cu", "dense_ff.cu", "dense_abi.cu", "sidecar.cpp"]
+SOURCES = ["moe_kernels.cu", "grouped_gemm.cu", "grouped_gemm_pair.cu", "grouped_gemm_w13_pair.cu", "grouped_gemm_decode.cu", "moe_abi.cu", "router_project.cu", "route_sort_noalloc.cu", "ep.cu", "dense_ff.cu", "dense_abi.cu", "sidecar.cpp"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",

@@ -14,17 +14,18 @@
 // pairs of persistent CTAs (a cluster of two) take items in the order of grouped_gemm.cu.
 //
 // Protocol, per pipeline stage.  Every CTA runs its own two TMA producers into its own shared
-// memory (plain loads, no multicast, completion on its own `full` barrier).  The second CTA of a
-// pair relays "my stage has landed" to the first by a remote mbarrier arrive.  The first CTA (the
-// leader) issues everything tensor: its scale copier waits for both stages, copies the scale
+// memory (tensor-map loads in their cta_group::2 form, no multicast), and all of them complete on
+// the `full` barrier of the first CTA (the leader), whose producers announce the byte count of both
+// CTAs' loads; the scale atoms travel through tensor maps too, because an untiled bulk copy can
+// only signal a barrier of its own CTA.  The leader's MMA thread waits for `full`, copies the scale
 // atoms of both CTAs into tensor memory (tcgen05.cp.cta_group::2 copies in each CTA from its own
-// shared memory) and commits to `sf_full`; its MMA thread then issues the four MMAs and commits
+// shared memory; copies and MMAs of one thread execute in order), issues the four MMAs and commits
 // to `empty` of both CTAs (the commit's multicast form), and after the last K block to both
 // `acc_full`.  The epilogue warps of both CTAs drain their own 128 accumulator rows exactly as in
 // the single-CTA kernel and release the accumulator to the leader (the second CTA by remote
 // arrives).  Tensor memory is allocated by each CTA for itself (all 512 columns, so both get the
 // same addresses).  Every wait is bounded; a CTA that gives up still reaches the cluster barrier
-// at the end, which keeps both CTAs resident until no remote arrive can be in flight.
+// at the end, which keeps both CTAs resident until no remote arrive or copy can be in flight.
 #include "gv_common.cuh"
 #include "gv_gemm_parts.cuh"
 #include "gv_launchers.h"
@@ -33,13 +34,12 @@ namespace gv {
 
 namespace {
 
-constexpr int kPairStages = 4;
+constexpr int kPairStages = 5;
 constexpr int kPairWeightProducerWarp = 2 + 4 * kEpilogueWarpsPerQuarter;  // 18
-constexpr int kPairScaleCopyWarp = kPairWeightProducerWarp + 1;            // 19
-constexpr int kPairThreads = (kPairScaleCopyWarp + 1) * 32;                // 640
+constexpr int kPairThreads = (kPairWeightProducerWarp + 1) * 32;           // 608
 constexpr uint32_t kPairTmemColumns = 512;
 constexpr uint32_t kPairSfColumn = 256;        // accumulator: columns [0, 256)
-constexpr uint32_t kPairSfColumnsPerStage = 64;  // per MMA j: A at +16j, B rows 0..127 at +16j+4, 128..255 at +16j+8
+constexpr uint32_t kPairSfColumnsPerStage = 48;  // per MMA j: A at +12j, B rows 0..127 at +12j+4, 128..255 at +12j+8
 constexpr int kPairTileBytes = kTileM * kTileKBytes;  // 16 KiB
 
 template <int kMode>
@@ -49,10 +49,8 @@ struct alignas(1024) PairSmem {
   uint8_t sfa[kPairStages][kSfStageBytes];       // scales of this CTA's rows
   uint8_t sfb[kPairStages][2 * kSfStageBytes];   // scales of all 256 weight rows
   uint8_t staging[4][kMode != kGeglu ? kStagingBytesPerWarp : 16];
-  uint64_t full[kPairStages];       // this CTA's two producers
-  uint64_t peer_full[kPairStages];  // leader: the second CTA's stage has landed
+  uint64_t full[kPairStages];       // leader: the stage's bytes have landed in both CTAs
   uint64_t empty[kPairStages];      // both CTAs: the MMAs that read the stage have completed
-  uint64_t sf_full[kPairStages];    // leader: the stage's scale factors are in tensor memory
   uint64_t acc_full;                // both CTAs: the item's accumulator is complete
   uint64_t acc_empty;               // leader: both CTAs' epilogues have copied the accumulator out
   uint32_t tmem_base;
@@ -86,10 +84,15 @@ __device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
       : "memory");
 }
 
-// The same, on the issuing CTA's barrier only.
-__device__ __forceinline__ void tc_commit_pair_local(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
+// Tensor-map load into this CTA's shared memory that completes on a barrier of either CTA of the
+// pair (`barrier` is a shared::cluster address).  No multicast: every CTA loads its own bytes.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* tensor_map, uint32_t barrier, int x,
+                                                 int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.cta_group::2"
+      " [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(smem_dst)),
+      "l"(tensor_map), "r"(x), "r"(y), "r"(barrier)
+      : "memory");
 }
 
 // Scale copies of one K block for both CTAs (each from its own shared memory at these offsets
@@ -105,8 +108,8 @@ __device__ __forceinline__ void issue_pair_sf_copies(uint32_t tmem_sf, uint32_t 
   "add.u32 ta, %0, " column ";\n\t"                                          \
   "tcgen05.cp.cta_group::2.32x128b.warpx4 [ta], d0;\n\t"
 #define GV_PSF_COPY(j)                                                           \
-  GV_PSF_ONE("%1", #j "*32", #j "*16") GV_PSF_ONE("%2", #j "*32", "4+" #j "*16") \
-  GV_PSF_ONE("%2", "128+" #j "*32", "8+" #j "*16")
+  GV_PSF_ONE("%1", #j "*32", #j "*12") GV_PSF_ONE("%2", #j "*32", "4+" #j "*12") \
+  GV_PSF_ONE("%2", "128+" #j "*32", "8+" #j "*12")
   asm volatile(GV_PSF_PROLOGUE GV_PSF_COPY(0) "}" GV_PSF_OPERANDS);
   if constexpr (kMmas >= 2) asm volatile(GV_PSF_PROLOGUE GV_PSF_COPY(1) "}" GV_PSF_OPERANDS);
   if constexpr (kMmas >= 3) asm volatile(GV_PSF_PROLOGUE GV_PSF_COPY(2) "}" GV_PSF_OPERANDS);
@@ -130,8 +133,8 @@ __device__ __forceinline__ void issue_pair_mmas(uint32_t tmem_acc, uint32_t tmem
   "mov.b64 d0, {lo, %4};\n\t"                                              \
   "add.u32 lo, %3, " #j "*2;\n\t"                                          \
   "mov.b64 d1, {lo, %4};\n\t"                                              \
-  "add.u32 ta, %1, " #j "*16;\n\t"                                         \
-  "add.u32 tb, %1, " #j "*16+4;\n\t"                                       \
+  "add.u32 ta, %1, " #j "*12;\n\t"                                         \
+  "add.u32 tb, %1, " #j "*12+4;\n\t"                                       \
   "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X"      \
   " [%0], d0, d1, %5, [ta], [tb], " pred ";\n\t"
   asm volatile(GV_PM_PROLOGUE GV_PM_MMA(0, "p") "}" GV_PM_OPERANDS);
@@ -191,7 +194,8 @@ template <int kMode>
 __global__ void __launch_bounds__(kPairThreads, 1)
 grouped_nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a32,
                                const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_b64,
-                               const GemmParams p, const int* __restrict__ pair_tile,
+                               const __grid_constant__ CUtensorMap map_a_sf,
+                               const __grid_constant__ CUtensorMap map_b_sf, const GemmParams p, const int* __restrict__ pair_tile,
                                const int* __restrict__ num_pairs) {
   using Smem = PairSmem<kMode>;
   extern __shared__ uint8_t smem_raw[];
@@ -203,10 +207,8 @@ grouped_nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const 
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; ++s) {
-      mbar_init(&smem->full[s], 2);       // one arrival (with its byte count) per producer warp
-      mbar_init(&smem->peer_full[s], 1);
+      mbar_init(&smem->full[s], 2);       // one arrival (with both CTAs' byte count) per producer warp of the leader
       mbar_init(&smem->empty[s], 1);
-      mbar_init(&smem->sf_full[s], 1);
     }
     mbar_init(&smem->acc_full, 1);
     mbar_init(&smem->acc_empty, kEpilogueThreads + kEpilogueThreads / 32);  // leader's threads + the second CTA's warps
@@ -217,6 +219,8 @@ grouped_nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const 
     prefetch_tensor_map(&map_a32);
     prefetch_tensor_map(&map_b);
     if (kMode == kGeglu) prefetch_tensor_map(&map_b64);
+    prefetch_tensor_map(&map_a_sf);
+    prefetch_tensor_map(&map_b_sf);
   }
   if (warp == 1) {
     tmem_alloc(&smem->tmem_base, kPairTmemColumns);  // the whole tensor memory: both CTAs get address 0
@@ -249,20 +253,29 @@ grouped_nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const 
     uint32_t phase = 0;
     int issued = 0;
     bool ok = true;
+    const int atoms_per_block = p.groups >> 2;  // 512-byte scale atoms of one 128-row block
     for (int round = 0; ok && round < rounds; ++round) {
       PairItem item;
       if (!pair_item(round, total_items, p.n_tiles, pair_begin, pair_tile, rank, item)) continue;
       const int n_tile = item.n_tile;
       const int expert = p.tile_expert[item.first];
-      int row = 0;
-      const uint8_t* sf_src = nullptr;
-      const uint8_t* sf_src2 = nullptr;
+      int row = 0, sf_row = 0, sf_row2 = 0;
+      uint32_t my_bytes = 0, both_bytes = 0;   // per K block: this CTA's loads; the leader's and the second CTA's
       bool short_tile = false, half_item = false;
       if (!weight_side) {
+        // activation rows: tile `first` in the leader, `first + 1` (if the pair has it) in the second CTA
+        const int local0 = item.first * kTileM - p.scale_row_offsets[expert];
+        const int rows_after = p.expert_offsets[expert + 1] - p.expert_offsets[expert] - local0;  // from the first tile on
+        const bool second_exists = rows_after > kTileM;
+        const uint32_t leader_bytes = (rows_after <= 32 ? kPairTileBytes / 4 : kPairTileBytes) + kSfStageBytes;
+        const uint32_t second_bytes =
+            second_exists ? (rows_after - kTileM <= 32 ? kPairTileBytes / 4 : kPairTileBytes) + kSfStageBytes : 0u;
+        both_bytes = leader_bytes + second_bytes;
+        my_bytes = is_leader ? leader_bytes : second_bytes;
         if (item.tile >= 0) {
           row = p.expert_offsets[expert] + (item.tile * kTileM - p.scale_row_offsets[expert]);
           short_tile = p.expert_offsets[expert + 1] - row <= 32;
-          sf_src = p.a_scales + static_cast<size_t>(item.tile) * kTileM * p.groups;
+          sf_row = item.tile * atoms_per_block;
         }
       } else if (kMode == kGeglu) {
         // leader: up rows [128 j, +128); second CTA: gate rows [704 + 128 j, +128); the sixth item
@@ -270,40 +283,37 @@ grouped_nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const 
         // its scales are zero in the re-tiled copy and the epilogue drops its columns)
         row = expert * kW13Out + n_tile * 128 + (is_leader ? 0 : kInter);
         half_item = (n_tile + 1) * 128 > kInter;
-        sf_src = p.b_scales + (static_cast<size_t>(expert) * p.n_tiles + n_tile) * 256 * p.groups;
+        sf_row = (expert * p.n_tiles + n_tile) * 2 * atoms_per_block;  // 8 atoms per K block
+        my_bytes = (half_item ? kPairTileBytes / 2 : kPairTileBytes) + 2 * kSfStageBytes;
+        both_bytes = 2 * my_bytes;
       } else {
         row = expert * p.n_out + n_tile * 256 + (is_leader ? 0 : 128);
-        sf_src = p.b_scales + static_cast<size_t>(expert * p.n_out + n_tile * 256) * p.groups;
-        sf_src2 = sf_src + static_cast<size_t>(128) * p.groups;
+        sf_row = ((expert * p.n_out + n_tile * 256) >> 7) * atoms_per_block;
+        sf_row2 = sf_row + atoms_per_block;
+        my_bytes = kPairTileBytes + 2 * kSfStageBytes;
+        both_bytes = 2 * my_bytes;
       }
-      const bool nothing = !weight_side && item.tile < 0;
       for (int kb = 0; kb < p.k_blocks; ++kb) {
         ok = __all_sync(0xffffffffu, wait_or_abort<true>(&smem->empty[stage], phase ^ 1u, smem, p.status));
         if (!ok) break;
         if (elect_one()) {
-          const bool last = kb + 1 == p.k_blocks;
-          const uint32_t sf_bytes = static_cast<uint32_t>(last ? p.last_mmas : 4) * kSfAtomBytes;
           const int x = kb * kTileKBytes;
-          if (nothing) {
-            mbar_arrive(&smem->full[stage]);
+          const uint32_t bar = is_leader ? smem_u32(&smem->full[stage])
+                                         : cluster_map_shared(smem_u32(&smem->full[stage]), 0);
+          if (is_leader) mbar_arrive_expect_tx(&smem->full[stage], both_bytes);
+          if (my_bytes == 0) {
+            // second CTA of a pair with one tile: no activation rows
           } else if (!weight_side) {
-            mbar_arrive_expect_tx(&smem->full[stage], (short_tile ? kPairTileBytes / 4 : kPairTileBytes) + sf_bytes);
-            tma_load_2d(smem->a[stage], short_tile ? &map_a32 : &map_a, &smem->full[stage], x, row);
-            bulk_load_1d(smem->sfa[stage], sf_src + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes,
-                         &smem->full[stage]);
+            tma_load_2d_pair(smem->a[stage], short_tile ? &map_a32 : &map_a, bar, x, row);
+            tma_load_2d_pair(smem->sfa[stage], &map_a_sf, bar, 0, sf_row + 4 * kb);
           } else if (kMode == kGeglu) {
-            mbar_arrive_expect_tx(&smem->full[stage], (half_item ? kPairTileBytes / 2 : kPairTileBytes) + 2 * kSfStageBytes);
-            tma_load_2d(smem->b[stage], half_item ? &map_b64 : &map_b, &smem->full[stage], x, row);
+            tma_load_2d_pair(smem->b[stage], half_item ? &map_b64 : &map_b, bar, x, row);
             // re-tiled scales: [rows 0..127 | rows 128..255] x four MMAs, 4 KiB per K block
-            bulk_load_1d(smem->sfb[stage], sf_src + static_cast<size_t>(kb) * 2 * kSfStageBytes, 2 * kSfStageBytes,
-                         &smem->full[stage]);
+            tma_load_2d_pair(smem->sfb[stage], &map_b_sf, bar, 0, sf_row + 8 * kb);
           } else {
-            mbar_arrive_expect_tx(&smem->full[stage], kPairTileBytes + 2 * sf_bytes);
-            tma_load_2d(smem->b[stage], &map_b, &smem->full[stage], x, row);
-            bulk_load_1d(smem->sfb[stage], sf_src + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes,
-                         &smem->full[stage]);
-            bulk_load_1d(smem->sfb[stage] + kSfStageBytes, sf_src2 + static_cast<size_t>(kb) * kSfStageBytes, sf_bytes,
-                         &smem->full[stage]);
+            tma_load_2d_pair(smem->b[stage], &map_b, bar, x, row);
+            tma_load_2d_pair(smem->sfb[stage], &map_b_sf, bar, 0, sf_row + 4 * kb);
+            tma_load_2d_pair(smem->sfb[stage] + kSfStageBytes, &map_b_sf, bar, 0, sf_row2 + 4 * kb);
           }
         }
         __syncwarp();
@@ -314,8 +324,9 @@ grouped_nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const 
         }
       }
     }
-    if (!ok && lane == 0) {
-      // Unwinding: let the copies already issued land before shared memory is given up.
+    if (!ok && lane == 0 && is_leader) {
+      // Unwinding: let the copies already issued (by either CTA) land before shared memory is
+      // given up; the second CTA stays resident until the cluster barrier at the end.
       const int pending = issued < kPairStages ? issued : kPairStages;
       int s = stage;
       uint32_t ph = phase;
@@ -328,31 +339,17 @@ grouped_nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const 
       }
     }
   } else if (warp == 1) {
-    int stage = 0;
-    uint32_t phase = 0;
-    if (!is_leader) {
-      // ---------------- second CTA: relay "stage landed" to the leader ----------------
-      bool ok = true;
-      for (int round = 0; ok && round < rounds; ++round) {
-        PairItem item;
-        if (!pair_item(round, total_items, p.n_tiles, pair_begin, pair_tile, rank, item)) continue;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          ok = wait_or_abort<false>(&smem->full[stage], phase, smem, p.status);
-          if (!ok) break;
-          if (lane == 0) mbar_arrive_remote(&smem->peer_full[stage], 0);
-          __syncwarp();
-          if (++stage == kPairStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
-        }
-      }
-    } else {
-      // ---------------- leader: MMA issuer for both CTAs ----------------
+    if (is_leader) {
+      // ---------------- leader: scale copies and MMAs for both CTAs ----------------
+      int stage = 0;
+      uint32_t phase = 0;
       uint32_t acc_phase = 0;
       const uint32_t a_lo0 = (smem_u32(smem->a[0]) & 0x3ffffu) >> 4;
       const uint32_t b_lo0 = (smem_u32(smem->b[0]) & 0x3ffffu) >> 4;
+      const uint32_t sfa_lo0 = (smem_u32(smem->sfa[0]) & 0x3ffffu) >> 4;
+      const uint32_t sfb_lo0 = (smem_u32(smem->sfb[0]) & 0x3ffffu) >> 4;
       constexpr uint32_t hi_ab = (1024u >> 4) | (1u << 14) | (2u << 29);  // 8 rows x 128 B, 128B swizzle
+      constexpr uint32_t hi_sf = (128u >> 4) | (1u << 14);                // 8 rows x 16 B, no swizzle
       const bool full_last = p.last_mmas == 4;
       const bool leader_lane = elect_one();
       for (int round = 0; round < rounds; ++round) {
@@ -363,18 +360,29 @@ grouped_nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const 
         bool ok = true;
         tc_fence_after_sync();
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          ok = wait_or_abort<false>(&smem->sf_full[stage], phase, smem, p.status);
+          ok = wait_or_abort<false>(&smem->full[stage], phase, smem, p.status);
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * (kPairTileBytes >> 4);
           const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(stage) * (kPairTileBytes >> 4);
+          const uint32_t sfa_lo = sfa_lo0 + static_cast<uint32_t>(stage) * (kSfStageBytes >> 4);
+          const uint32_t sfb_lo = sfb_lo0 + static_cast<uint32_t>(stage) * (2 * kSfStageBytes >> 4);
           const uint32_t tmem_sf = tmem_base + kPairSfColumn + kPairSfColumnsPerStage * stage;
           if (leader_lane) {
             const uint32_t accumulate = kb != 0 ? 1u : 0u;
-            if (kb != p.k_blocks - 1 || full_last) issue_pair_mmas<4>(tmem_base, tmem_sf, a_lo, b_lo, hi_ab, accumulate);
-            else if (p.last_mmas == 3) issue_pair_mmas<3>(tmem_base, tmem_sf, a_lo, b_lo, hi_ab, accumulate);
-            else if (p.last_mmas == 2) issue_pair_mmas<2>(tmem_base, tmem_sf, a_lo, b_lo, hi_ab, accumulate);
-            else issue_pair_mmas<1>(tmem_base, tmem_sf, a_lo, b_lo, hi_ab, accumulate);
+            if (kb != p.k_blocks - 1 || full_last) {
+              issue_pair_sf_copies<4>(tmem_sf, sfa_lo, sfb_lo, hi_sf);
+              issue_pair_mmas<4>(tmem_base, tmem_sf, a_lo, b_lo, hi_ab, accumulate);
+            } else if (p.last_mmas == 3) {
+              issue_pair_sf_copies<3>(tmem_sf, sfa_lo, sfb_lo, hi_sf);
+              issue_pair_mmas<3>(tmem_base, tmem_sf, a_lo, b_lo, hi_ab, accumulate);
+            } else if (p.last_mmas == 2) {
+              issue_pair_sf_copies<2>(tmem_sf, sfa_lo, sfb_lo, hi_sf);
+              issue_pair_mmas<2>(tmem_base, tmem_sf, a_lo, b_lo, hi_ab, accumulate);
+            } else {
+              issue_pair_sf_copies<1>(tmem_sf, sfa_lo, sfb_lo, hi_sf);
+              issue_pair_mmas<1>(tmem_base, tmem_sf, a_lo, b_lo, hi_ab, accumulate);
+            }
             tc_commit_pair(&smem->empty[stage]);   // both CTAs may refill the stage
             if (kb + 1 == p.k_blocks) tc_commit_pair(&smem->acc_full);
           }
@@ -384,41 +392,6 @@ grouped_nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const 
           }
         }
         if (!ok) break;
-      }
-    }
-  } else if (warp == kPairScaleCopyWarp) {
-    // ---------------- leader: scale-factor copier for both CTAs ----------------
-    if (is_leader) {
-      int stage = 0;
-      uint32_t phase = 0;
-      const uint32_t sfa_lo0 = (smem_u32(smem->sfa[0]) & 0x3ffffu) >> 4;
-      const uint32_t sfb_lo0 = (smem_u32(smem->sfb[0]) & 0x3ffffu) >> 4;
-      constexpr uint32_t hi_sf = (128u >> 4) | (1u << 14);  // 8 rows x 16 B, no swizzle
-      const bool full_last = p.last_mmas == 4;
-      const bool leader_lane = elect_one();
-      bool ok = true;
-      for (int round = 0; ok && round < rounds; ++round) {
-        PairItem item;
-        if (!pair_item(round, total_items, p.n_tiles, pair_begin, pair_tile, rank, item)) continue;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          ok = wait_or_abort<false>(&smem->full[stage], phase, smem, p.status) &&
-               wait_or_abort<false>(&smem->peer_full[stage], phase, smem, p.status);
-          if (!ok) break;
-          const uint32_t sfa_lo = sfa_lo0 + static_cast<uint32_t>(stage) * (kSfStageBytes >> 4);
-          const uint32_t sfb_lo = sfb_lo0 + static_cast<uint32_t>(stage) * (2 * kSfStageBytes >> 4);
-          const uint32_t tmem_sf = tmem_base + kPairSfColumn + kPairSfColumnsPerStage * stage;
-          if (leader_lane) {
-            if (kb != p.k_blocks - 1 || full_last) issue_pair_sf_copies<4>(tmem_sf, sfa_lo, sfb_lo, hi_sf);
-            else if (p.last_mmas == 3) issue_pair_sf_copies<3>(tmem_sf, sfa_lo, sfb_lo, hi_sf);
-            else if (p.last_mmas == 2) issue_pair_sf_copies<2>(tmem_sf, sfa_lo, sfb_lo, hi_sf);
-            else issue_pair_sf_copies<1>(tmem_sf, sfa_lo, sfb_lo, hi_sf);
-            tc_commit_pair_local(&smem->sf_full[stage]);
-          }
-          if (++stage == kPairStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
-        }
       }
     }
   } else {
@@ -524,7 +497,7 @@ cudaError_t launch_pair_variant(const GemmOperands& op, const GemmParams& p, con
   config.attrs = attributes;
   config.numAttrs = op.serial_launch ? 1 : 2;
   return cudaLaunchKernelEx(&config, grouped_nvfp4_gemm_pair_kernel<kMode>, op.map_a, op.map_a32, op.map_b,
-                            op.map_b64, p, static_cast<const int*>(plan.pair_tile),
+                            op.map_b64, op.map_a_sf, op.map_b_sf, p, static_cast<const int*>(plan.pair_tile),
                             static_cast<const int*>(plan.num_pairs));
 }
 

@@ -69,6 +69,8 @@ struct GemmOperands {
   CUtensorMap map_a32;      // same matrix through a 32-row box (groups of at most 32 rows)
   CUtensorMap map_b;        // [128*N, K/2] bytes, same box
   CUtensorMap map_b64;      // fused w13 form only: the same matrix through a 64-row box
+  CUtensorMap map_a_sf;     // CTA-pair form: a_scales as [atoms of 512 B][128 x u32], box of four atoms
+  CUtensorMap map_b_sf;     // CTA-pair form: b_scales likewise; box of eight atoms (fused w13) or four (w2)
   const uint8_t* a_scales;  // activation scale regions
   const uint8_t* b_scales;  // [128, N, K/16] swizzled per expert
   const float* alpha;       // [128]
@@ -102,9 +104,32 @@ void launch_retile_w13_scales(const uint8_t* sidecar_scales, uint8_t* tiled, int
 bool make_operand_tensor_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes,
                              int box_rows);
 
+// Scale-factor bytes seen as rows of one 512-byte atom each (128 x u32), through a box of
+// `box_atoms` consecutive atoms; no swizzle.
+bool make_scale_tensor_map(CUtensorMap* map, const void* base, uint64_t bytes, int box_atoms);
+
 // The CTA-pair form (grouped_gemm_pair.cu): fused w13 (op.fused_geglu) or plain w2 (n_out % 256 == 0).
 void launch_grouped_gemm_pairs(const GemmOperands& op, const RoutePlan& plan, int sm_count, cudaStream_t stream);
 int prepare_grouped_gemm_pairs();
+
+// Fused w13 + GeGLU + requantise run by CTA pairs with the weights on the MMA's M side and up to
+// 256 rows of one expert on its N side (grouped_gemm_w13_pair.cu); needs the plan's tile-pair list.
+struct W13PairOperands {
+  CUtensorMap map_x[16];  // activation codes [row capacity, 1408] bytes through boxes of 8, 16, ... 128 rows x 128 B
+  CUtensorMap map_w;      // w13 codes as [experts * 2 halves, 704 rows, 1408] bytes, box 2 x 64 rows x 128 B: the
+                          // up rows and the gate rows of one unit in one copy
+  CUtensorMap map_x_sf;   // activation scale regions as [128-row blocks, 44 atoms, 512 B], box 2 blocks x 4 atoms
+  CUtensorMap map_w_sf;   // unit-tiled weight scales (launch_retile_w13_unit_scales), box of four atoms
+  const float* alpha;           // [experts]
+  uint8_t* next_codes;          // [row capacity, 352]
+  uint8_t* next_scales;         // scale regions of the w2 operand
+  const float* next_scale_q;    // [experts]
+  bool serial_launch;
+};
+size_t w13_unit_scale_bytes(int experts);
+void launch_retile_w13_unit_scales(const uint8_t* sidecar_scales, uint8_t* tiled, int experts, cudaStream_t stream);
+void launch_w13_pairs(const W13PairOperands& op, const RoutePlan& plan, int sm_count, cudaStream_t stream);
+int prepare_w13_pairs();
 
 // Both expert GEMMs of a batch of at most 128 tokens in one persistent launch (grouped_gemm_decode.cu):
 // the fused w13 form, then w2, with per-tile readiness counters (plan.tile_ready) in between.

@@ -88,6 +88,47 @@ bool make_operand_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+bool make_scale_map(CUtensorMap* map, const void* base, uint64_t bytes, int box_atoms) {
+  const cuuint64_t dims[2] = {128, bytes / 512};
+  const cuuint64_t strides[1] = {512};
+  const cuuint32_t box[2] = {128, static_cast<cuuint32_t>(box_atoms)};
+  const cuuint32_t element_strides[2] = {1, 1};
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn || dims[1] == 0) return false;
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box,
+            element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// w13 codes [experts, 2 halves (up, gate), 704 rows, 1408 bytes] through a box of both halves x
+// 64 rows x 128 bytes (128-byte swizzle): one copy brings a unit's up rows and gate rows.
+bool make_w13_unit_map(CUtensorMap* map, const void* base, uint64_t experts) {
+  const cuuint64_t dims[3] = {kHidden / 2, kInter, experts * 2};
+  const cuuint64_t strides[2] = {kHidden / 2, static_cast<cuuint64_t>(kInter) * (kHidden / 2)};
+  const cuuint32_t box[3] = {static_cast<cuuint32_t>(kTileKBytes), 64, 2};
+  const cuuint32_t element_strides[3] = {1, 1, 1};
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return false;
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box,
+            element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Scale bytes of an activation operand as [128-row blocks, atoms per block, 128 x u32] through a
+// box of two blocks x four atoms: the scales of one K block for up to 256 rows in one copy.
+bool make_block_scale_map(CUtensorMap* map, const void* base, uint64_t bytes, int atoms_per_block) {
+  const uint64_t block_bytes = static_cast<uint64_t>(atoms_per_block) * 512;
+  const cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(atoms_per_block), bytes / block_bytes};
+  const cuuint64_t strides[2] = {512, block_bytes};
+  const cuuint32_t box[3] = {128, 4, 2};
+  const cuuint32_t element_strides[3] = {1, 1, 1};
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn || dims[2] == 0) return false;
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(base), dims, strides, box,
+            element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 thread_local char g_error_text[256] = "";
 
 int cuda_failure(cudaError_t error, const char* what) {
@@ -159,6 +200,9 @@ bool make_operand_tensor_map(CUtensorMap* map, const void* base, uint64_t rows, 
                              int box_rows) {
   return make_operand_map(map, base, rows, row_bytes, box_rows);
 }
+bool make_scale_tensor_map(CUtensorMap* map, const void* base, uint64_t bytes, int box_atoms) {
+  return make_scale_map(map, base, bytes, box_atoms);
+}
 }  // namespace gv
 
 namespace {
@@ -183,6 +227,9 @@ struct gevva_moe {
   gv::GemmOperands w13_fused{};  // GeGLU + requantise in the epilogue (the production path)
   gv::GemmOperands w2{};
   uint8_t* w13_sf_tiled = nullptr;  // runner-owned re-tiling of weights.w13_sf
+  gv::W13PairOperands w13_pairs{};  // the CTA-pair form of the fused w13 stage
+  uint8_t* w13_sf_units = nullptr;  // runner-owned re-tiling of weights.w13_sf for it
+  bool w13_pair_form = false;       // GEVVA_MOE_OPTION_W13_PAIRS, or GEVVA_MOE_W13_PAIRS=1 for a whole process
   int sm_count = 0;
   bool pairs = false;               // GEVVA_MOE_OPTION_PAIRS: prefill-sized launches run the expert GEMMs as CTA pairs
   bool merged_decode = true;        // batches of at most 128 tokens: w13 and w2 in one launch (GEVVA_MOE_DECODE_MERGED=0: two)
@@ -220,7 +267,7 @@ const char* gevva_moe_strerror(int status) {
 
 int gevva_moe_create(gevva_moe** out, const gevva_moe_weights* weights, int max_tokens,
                      gevva_moe* share_scratch_with, const gevva_moe_options* options) {
-  if (options && (options->flags & ~static_cast<uint32_t>(GEVVA_MOE_OPTION_NVTX | GEVVA_MOE_OPTION_PAIRS)))
+  if (options && (options->flags & ~static_cast<uint32_t>(GEVVA_MOE_OPTION_NVTX | GEVVA_MOE_OPTION_PAIRS | GEVVA_MOE_OPTION_W13_PAIRS)))
     return GEVVA_MOE_BAD_ARGUMENT;
   if (!out || !weights || !weights->w13 || !weights->w13_sf || !weights->w2 || !weights->w2_sf ||
       !weights->alpha1 || !weights->alpha2 || !weights->in_scale_q1 || !weights->in_scale_q2)
@@ -290,6 +337,51 @@ int gevva_moe_create(gevva_moe** out, const gevva_moe_weights* weights, int max_
     gevva_moe_destroy(m);
     return cuda_failure(tiled_error, "w13 scale re-tiling");
   }
+  ok = make_scale_map(&m->w13.map_a_sf, s->input_sf, s->input_sf_bytes, 4) &&
+       make_scale_map(&m->w13.map_b_sf, m->w13_sf_tiled, gv::retiled_w13_scale_bytes(kExperts), 8) &&
+       make_scale_map(&m->w2.map_a_sf, s->inter_sf, s->inter_sf_bytes, 4) &&
+       make_scale_map(&m->w2.map_b_sf, weights->w2_sf, static_cast<uint64_t>(kExperts) * kHidden * (kInter / 16), 4);
+  if (!ok) {
+    gevva_moe_destroy(m);
+    std::snprintf(g_error_text, sizeof(g_error_text), "cuTensorMapEncodeTiled failed (scale maps)");
+    return GEVVA_MOE_CUDA_ERROR;
+  }
+  const char* w13_pairs_env = std::getenv("GEVVA_MOE_W13_PAIRS");
+  m->w13_pair_form = (options && (options->flags & GEVVA_MOE_OPTION_W13_PAIRS)) || (w13_pairs_env && w13_pairs_env[0] == '1');
+  if (m->w13_pair_form) {
+    // opt-in (measured slower than the one-CTA kernel on this part): its 35 MB re-tiled scale copy
+    // and its tensor maps exist only when asked for
+    cudaError_t e = static_cast<cudaError_t>(gv::prepare_w13_pairs());
+    if (e == cudaSuccess)
+      e = cudaMalloc(reinterpret_cast<void**>(&m->w13_sf_units), gv::w13_unit_scale_bytes(kExperts));
+    if (e == cudaSuccess) {
+      gv::launch_retile_w13_unit_scales(static_cast<const uint8_t*>(weights->w13_sf), m->w13_sf_units, kExperts,
+                                        nullptr);
+      e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(nullptr);
+    if (e != cudaSuccess) {
+      gevva_moe_destroy(m);
+      return cuda_failure(e, "w13 unit scale re-tiling");
+    }
+    gv::W13PairOperands& wp = m->w13_pairs;
+    ok = true;
+    for (int i = 0; i < 16; ++i)
+      ok = ok && make_operand_map(&wp.map_x[i], s->input_codes, rows, kHidden / 2, 8 * (i + 1));
+    ok = ok && make_w13_unit_map(&wp.map_w, weights->w13, kExperts) &&
+         make_block_scale_map(&wp.map_x_sf, s->input_sf, s->input_sf_bytes, kHidden / 64) &&
+         make_scale_map(&wp.map_w_sf, m->w13_sf_units, gv::w13_unit_scale_bytes(kExperts), 4);
+    if (!ok) {
+      gevva_moe_destroy(m);
+      std::snprintf(g_error_text, sizeof(g_error_text), "cuTensorMapEncodeTiled failed (w13 pair maps)");
+      return GEVVA_MOE_CUDA_ERROR;
+    }
+    wp.alpha = weights->alpha1;
+    wp.next_codes = s->inter_codes;
+    wp.next_scales = s->inter_sf;
+    wp.next_scale_q = weights->in_scale_q2;
+    wp.serial_launch = false;
+  }
   m->w13.a_scales = s->input_sf;
   m->w13.b_scales = static_cast<const uint8_t*>(weights->w13_sf);
   m->w13.alpha = weights->alpha1;
@@ -317,6 +409,7 @@ void gevva_moe_destroy(gevva_moe* runner) {
   if (!runner) return;
   if (runner->scratch && --runner->scratch->references == 0) free_scratch(runner->scratch);
   cudaFree(runner->w13_sf_tiled);
+  cudaFree(runner->w13_sf_units);
   delete runner;
 }
 
@@ -412,9 +505,14 @@ int gevva_moe_launch_stages(gevva_moe* runner, const void* in, const int* ids,
   if ((stages & both) == both && !(stages & GEVVA_MOE_STAGE_UNFUSED)) {
     // production path: GeGLU + requantise inside the w13 epilogue, no bf16 w13 output
     StageRange range(runner->nvtx, "gevva_moe.w13+geglu");
-    gv::GemmOperands w13 = runner->w13_fused;
-    w13.use_pairs = use_pairs;
-    gv::launch_grouped_gemm(w13, s->plan, runner->sm_count, stream);
+    if (runner->w13_pair_form && tokens > gv::kFusedSortQuantizeMaxTokens && s->plan.pair_tile &&
+        runner->sm_count >= 2) {
+      gv::launch_w13_pairs(runner->w13_pairs, s->plan, runner->sm_count, stream);
+    } else {
+      gv::GemmOperands w13 = runner->w13_fused;
+      w13.use_pairs = use_pairs;
+      gv::launch_grouped_gemm(w13, s->plan, runner->sm_count, stream);
+    }
   } else {
     if (stages & GEVVA_MOE_STAGE_W13)
       gv::launch_grouped_gemm(runner->w13, s->plan, runner->sm_count, stream);

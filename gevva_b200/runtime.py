@@ -47,6 +47,7 @@ class _Options(ctypes.Structure):
 
 OPTION_NVTX = 1
 OPTION_PAIRS = 2
+OPTION_W13_PAIRS = 4
 
 
 class _Weights(ctypes.Structure):
@@ -152,9 +153,10 @@ class Nvfp4ExpertRunner:
     """Mirror of gevva::Nvfp4ExpertRunner (include/gevva/gpu.hpp:217-247)."""
 
     def __init__(self, experts: ExpertWeights, maximum_tokens: int = 1, shared_scratch=None, nvtx=False,
-                 pairs=False):
+                 pairs=False, w13_pairs=False):
         """nvtx: wrap every stage's launches in a named NVTX range; pairs: run the expert GEMMs of
-        batches above 128 tokens as CTA pairs (both additions of this build)."""
+        batches above 128 tokens as CTA pairs; w13_pairs: run the fused w13 stage of such batches as
+        CTA pairs with the weights on the MMA's M side (all additions of this build, same bits)."""
         experts.validate()
         self._weights = experts  # keeps the tensors alive, as the DeviceModel arena does
         self._device = experts.w13.device
@@ -166,7 +168,8 @@ class Nvfp4ExpertRunner:
         share = shared_scratch._handle if shared_scratch is not None else None
         self._shared = shared_scratch
         with torch.cuda.device(self._device):
-            options = _Options((OPTION_NVTX if nvtx else 0) | (OPTION_PAIRS if pairs else 0))
+            options = _Options((OPTION_NVTX if nvtx else 0) | (OPTION_PAIRS if pairs else 0) |
+                               (OPTION_W13_PAIRS if w13_pairs else 0))
             status = library().gevva_moe_create(ctypes.byref(handle), ctypes.byref(packed),
                                                 self.maximum_tokens, share, ctypes.byref(options))
         if status != 0:

@@ -66,6 +66,10 @@ typedef struct {
 #define GEVVA_MOE_OPTION_PAIRS 2u /* batches of more than 128 tokens run the two expert GEMMs as CTA pairs
                                      (tcgen05 cta_group::2, two row tiles of an expert against shared weight
                                      rows); same bits, measured slower than the default on B200 */
+#define GEVVA_MOE_OPTION_W13_PAIRS 4u /* batches of more than 128 tokens run the fused w13 stage as CTA pairs with the
+                                         weight rows on the MMA's M side and up to 256 rows of an expert (any
+                                         multiple of 16) on its N side; same bits, measured slower than the default
+                                         on B200; holds a second re-tiled copy of the w13 scales (35 MB) */
 typedef struct {
   uint32_t flags; /* 0 or GEVVA_MOE_OPTION_* */
   uint32_t reserved[7];

@@ -532,6 +532,37 @@ def test_cta_pair_gemms_equal_the_single_cta_gemms(gm, weights, cuda_device, tok
     assert results[0][0].float().abs().max() > 0
 
 
+@pytest.mark.parametrize("tokens,kind", [(129, "random"), (130, "skewed"), (300, "skewed"), (777, "random"),
+                                         (4096, "random")])
+def test_weight_major_pair_w13_equals_the_single_cta_w13(gm, weights, cuda_device, tokens, kind):
+    """The fused w13 stage run by CTA pairs with the weights on the MMA's M side and up to 256 rows of
+    an expert on its N side (any multiple of 16) writes the same w2 operand codes and scale bytes as
+    the one-CTA-per-tile kernel, and the layer output follows."""
+    from gevva_b200 import runtime as rt
+    ids = random_ids(tokens, 23) if kind == "random" else skewed_ids(tokens)
+    x = hashgen.activations(tokens, HIDDEN, 79, cuda_device)
+    dev_ids = torch.from_numpy(ids).to(cuda_device)
+    rw = torch.full((tokens, TOP_K), 0.125, device=cuda_device)
+    routes = tokens * TOP_K
+    results = []
+    for form in (False, True):
+        runner = gm.Nvfp4ExpertRunner(weights[0], tokens, w13_pairs=form)
+        out = torch.empty_like(x)
+        runner.buffer(rt.BUF_INTER_CODES).zero_()
+        runner.buffer(rt.BUF_INTER_SF).zero_()
+        for _ in range(2):
+            runner.launch_batch(x, dev_ids, rw, out, tokens)
+        runner.check()
+        results.append((out, runner.buffer(rt.BUF_INTER_CODES)[: routes * INTER // 2].clone(),
+                        runner.buffer(rt.BUF_INTER_SF).clone()))
+    sf_a, sf_b = results[0][2], results[1][2]
+    codes_a, codes_b = results[0][1], results[1][1]
+    assert torch.equal(codes_a, codes_b), f"{(codes_a != codes_b).sum().item()} code bytes differ"
+    assert torch.equal(sf_a, sf_b), f"{(sf_a != sf_b).sum().item()} scale bytes differ"
+    assert torch.equal(results[0][0], results[1][0])
+    assert results[0][0].float().abs().max() > 0
+
+
 @pytest.mark.parametrize("tokens,kind", [(1, "random"), (8, "random"), (40, "skewed"), (64, "random"),
                                          (128, "skewed")])
 def test_merged_decode_launch_equals_two_launches(gm, weights, cuda_device, tokens, kind, monkeypatch):

@@ -22,7 +22,9 @@ def needs_build():
     if not os.path.exists(LIB):
         return True
     built = os.path.getmtime(LIB)
-    for root, _, files in os.walk(CSRC):
+    for root, dirs, files in os.walk(CSRC):
+        if "probes" in dirs:
+            dirs.remove("probes")  # stand-alone programs, not part of the library
         for name in files:
             if name.endswith((".cu", ".cuh", ".h", ".cpp")) and os.path.getmtime(os.path.join(root, name)) > built:
                 return True
@@ -42,6 +44,30 @@ def build(force=False, verbose=False):
     return LIB
 
 
+PROBES = ["tensor_pipe_probe", "tma_intake_probe"]
+
+
+def build_probes():
+    """Stand-alone measurement programs (csrc/probes/*.cu -> gevva_b200/probes/<name>): what the tensor
+    pipe and the TMA intake of an SM sustain for the stage shapes of the expert GEMMs."""
+    out_dir = os.path.join(HERE, "probes")
+    os.makedirs(out_dir, exist_ok=True)
+    built = []
+    for name in PROBES:
+        target = os.path.join(out_dir, name)
+        cmd = [NVCC, "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-o", target,
+               os.path.join(CSRC, "probes", name + ".cu")]
+        result = subprocess.run(cmd, capture_output=True, text=True)
+        if result.returncode != 0:
+            sys.stderr.write(result.stdout + result.stderr)
+            raise RuntimeError("nvcc failed building " + name)
+        built.append(target)
+    return built
+
+
 if __name__ == "__main__":
-    build(force=True, verbose=True)
-    print(LIB)
+    if "--probes" in sys.argv:
+        print("\n".join(build_probes()))
+    else:
+        build(force=True, verbose=True)
+        print(LIB)

@@ -242,7 +242,7 @@ def decode_eager(layer, device, tokens, steps):
 
 
 def config3_stack(device, passes=5):
-    """BASELINE.json config 3: 30 random-init layers (MoE + dense FP8 GeGLU MLP of width 2112 +
+    """The 30-layer configuration: 30 random-init layers (MoE + dense FP8 GeGLU MLP of width 2112 +
     the pre/post norm steps, attention = identity), 2048 tokens, distinct weights per layer."""
     import torch
     from gevva_b200.synthetic import SyntheticStack
@@ -270,7 +270,7 @@ def config3_stack(device, passes=5):
 
 
 def config4_layer(base_layer, device):
-    """The Zipf(1.1)-biased router of BASELINE.json config 4 over the same experts."""
+    """The Zipf(1.1)-biased router of the 16384-token expert-parallel configuration over the same experts."""
     from gevva_b200.synthetic import SyntheticLayer
     layer = SyntheticLayer(seed=0, max_tokens=16, device=device, zipf=True, packed=base_layer.packed)
     layer.weights = base_layer.weights      # same calibrated static scales

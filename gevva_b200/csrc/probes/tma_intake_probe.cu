@@ -62,6 +62,8 @@ int main() {
       {"L2-resident, 3 x 54 KiB in flight", hot, 54 * 1024, 3, 2, 1},
       {"L2-resident, 8 x 27 KiB in flight", hot, 27 * 1024, 8, 1, 1},
       {"L2-resident, 5 x 38 KiB in flight", hot, 38 * 1024, 5, 2, 1},
+      {"L2-resident, 2 CTAs read the same bytes, 4 x 54 KiB", hot, 54 * 1024, 4, 2, 2},
+      {"L2-resident, 4 CTAs read the same bytes, 4 x 54 KiB", hot, 54 * 1024, 4, 2, 4},
       {"from HBM,    4 x 54 KiB in flight", cold, 54 * 1024, 4, 2, 1},
       {"from HBM,    5 x 38 KiB in flight", cold, 38 * 1024, 5, 2, 1},
       {"from HBM, 2 CTAs read the same bytes, 4 x 54 KiB", cold, 54 * 1024, 4, 2, 2},

@@ -540,8 +540,13 @@ grouped_nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           uint4 codes;
           const uint32_t scale0 = geglu_block(up0, gate0, alpha, multiplier, smem->erf_table, codes.x, codes.y);
           const uint32_t scale1 = geglu_block(up1, gate1, alpha, multiplier, smem->erf_table, codes.z, codes.w);
-          *reinterpret_cast<uint4*>(p.next_codes + static_cast<size_t>(row0 + row_local) * (kInter / 2) +
-                                    n_tile * 64 + sub * 16) = codes;
+          // the w2 operand: read eleven times by the next launch, so L2 is asked to keep it
+          unsigned long long keep_in_l2;
+          asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(keep_in_l2));
+          asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(
+                           p.next_codes + static_cast<size_t>(row0 + row_local) * (kInter / 2) + n_tile * 64 + sub * 16),
+                       "r"(codes.x), "r"(codes.y), "r"(codes.z), "r"(codes.w), "l"(keep_in_l2)
+                       : "memory");
           // scale groups 8*n_tile+2*sub and the next one (same 4-group word) of row
           // (128*m_tile + row_local) of the w2 operand
           constexpr int groups = kInter / 16;

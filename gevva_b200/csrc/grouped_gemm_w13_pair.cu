@@ -73,13 +73,6 @@ __device__ __forceinline__ void wp_arrive_remote(uint64_t* local_bar, uint32_t t
   asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
 }
 
-// Arrives on this CTA's barrier once every tcgen05 operation issued so far by this thread has
-// completed in both CTAs.
-__device__ __forceinline__ void wp_commit_local(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-
 // Arrives on the barrier at the same shared-memory offset in both CTAs of the pair once every
 // tcgen05 operation issued so far by this thread has completed.
 __device__ __forceinline__ void wp_commit_both(uint64_t* bar) {
@@ -303,7 +296,6 @@ w13_geglu_pair_kernel(const __grid_constant__ WpTokenMaps map_x, const __grid_co
   const int slots = static_cast<int>(gridDim.x) >> 1;
   plan.rounds = (plan.total_items + slots - 1) / slots;
   constexpr int k_blocks = kHidden / 2 / kTileKBytes;   // 11
-  constexpr int atoms_per_block = kHidden / 64;         // 44 scale atoms per 128-row block of tokens
 
   if (warp == 0) {
     // ---------------- TMA producer (one warp in each CTA) ----------------

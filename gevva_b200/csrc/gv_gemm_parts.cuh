@@ -74,6 +74,8 @@ __device__ __forceinline__ void stage_and_store(const uint32_t (&r)[32], float a
     *reinterpret_cast<uint4*>(staging + lane * kStageRowBytes + ((c ^ (lane & 15)) << 4)) = v;
   }
   named_barrier(1 + quarter, kEpilogueWarpsPerQuarter * 32);
+  unsigned long long keep_in_l2;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(keep_in_l2));
   const int c = lane & 15;
   __nv_bfloat16* dst = p.out + static_cast<size_t>(row0 + quarter * 32) * p.n_out + column0 + c * 8;
 #pragma unroll
@@ -86,7 +88,12 @@ __device__ __forceinline__ void stage_and_store(const uint32_t (&r)[32], float a
         __nv_bfloat16* remote = reinterpret_cast<__nv_bfloat16*>(p.row_dest[row0 + quarter * 32 + r2]);
         *reinterpret_cast<uint4*>(remote + column0 + c * 8) = v;
       } else {
-        *reinterpret_cast<uint4*>(dst + static_cast<size_t>(r2) * p.n_out) = v;
+        // The rows are read back by the weighted reduce (or the next stage) right after this
+        // launch: ask L2 to keep them (without the hint the reduce finds 2 % of them there).
+        asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(
+                         dst + static_cast<size_t>(r2) * p.n_out),
+                     "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "l"(keep_in_l2)
+                     : "memory");
       }
     }
   }

@@ -351,6 +351,8 @@ __device__ __forceinline__ void quantize_routes_of_token(const float (&values)[1
                                                          uint8_t* __restrict__ packed,
                                                          uint8_t* __restrict__ scales) {
   static_assert(kBlocks == 2 || kBlocks == 4, "two or four blocks per thread");
+  unsigned long long keep_in_l2;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(keep_in_l2));
   // scale groups kBlocks*part .. +kBlocks-1 lie in one 4-group word of the swizzled layout
   const unsigned scale_offset = kBlocks == 4
                                     ? static_cast<unsigned>(part) * 512u
@@ -393,7 +395,10 @@ __device__ __forceinline__ void quantize_routes_of_token(const float (&values)[1
       }
     }
     uint4* row = reinterpret_cast<uint4*>(packed + static_cast<size_t>(dst) * (kHidden / 2)) + (kBlocks / 2) * part;
-    row[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+    // the codes are the w13 operand, read six times by the next launch: L2 is asked to keep them
+    asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(row), "r"(codes[0]), "r"(codes[1]),
+                 "r"(codes[2]), "r"(codes[3]), "l"(keep_in_l2)
+                 : "memory");
     if constexpr (kBlocks == 4) {
       row[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
       *reinterpret_cast<uint32_t*>(scales + route_scale_base[k] + scale_offset) = scale_word;
@@ -660,6 +665,8 @@ reduce_routes_kernel(const __nv_bfloat16* __restrict__ routed, const float* __re
                      const int* __restrict__ inverse_routes, __nv_bfloat16* __restrict__ output) {
   const int token = blockIdx.x;
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  unsigned long long read_once;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(read_once));
   grid_launch_dependents();
   grid_dependency_wait();  // the down GEMM's rows
 #pragma unroll
@@ -668,9 +675,13 @@ reduce_routes_kernel(const __nv_bfloat16* __restrict__ routed, const float* __re
     const int source = inverse_routes[index];
     const float weight = route_weights[index];
     float v[8];
-    unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(routed + static_cast<size_t>(source) * kHidden) +
-                        threadIdx.x),
-                  v);
+    // read once and dead afterwards: the rows must not push the rows that other CTAs have not yet read out of L2
+    uint4 raw;
+    asm volatile("ld.global.nc.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
+                 : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+                 : "l"(reinterpret_cast<const uint4*>(routed + static_cast<size_t>(source) * kHidden) + threadIdx.x),
+                   "l"(read_once));
+    unpack_bf16x8(raw, v);
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = __fmaf_rn(v[i], weight, acc[i]);
   }

@@ -401,8 +401,12 @@ __device__ __forceinline__ void quantize_routes_of_token(const float (&values)[1
       row[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
       *reinterpret_cast<uint32_t*>(scales + route_scale_base[k] + scale_offset) = scale_word;
     } else {
-      *reinterpret_cast<uint16_t*>(scales + route_scale_base[k] + scale_offset) =
-          static_cast<uint16_t>(scale_word);
+      // two neighbouring threads hold the four scale bytes of one aligned word: one store, kept in L2
+      const uint32_t neighbour = __shfl_down_sync(__activemask(), scale_word, 1);
+      if ((part & 1) == 0)
+        asm volatile("st.global.L2::cache_hint.b32 [%0], %1, %2;" ::"l"(scales + route_scale_base[k] + scale_offset),
+                     "r"((scale_word & 0xffffu) | (neighbour << 16)), "l"(keep_in_l2)
+                     : "memory");
     }
   }
 }

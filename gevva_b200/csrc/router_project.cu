@@ -30,7 +30,7 @@ namespace {
 
 // CTAs per cluster = K slices per token tile: 4, 2 or 1, the largest that keeps the launch within
 // one wave of SMs (a tile's pass is a chain of latencies, so waves cost more than depth)
-constexpr int kRpStages = 4;
+constexpr int kRpStages = 5;
 constexpr int kRpThreads = 192;
 constexpr int kRpTileBytes = kTileM * kTileKBytes;  // 16 KiB: 128 rows of one 128-byte K block
 

@@ -154,7 +154,7 @@ def launches_per_step(world, tokens, sm_count=148, ep_chunks=2):
     sort = 1 if tokens * TOP_K <= 1024 or (tokens * TOP_K + 1023) // 1024 <= sm_count else 3
     if world == 1:
         if tokens <= 128:
-            return 1 + 1 + 1 + 1      # fused router; sort+quantise in one launch; both expert GEMMs in one launch; reduce
+            return 1 + 1 + 1          # fused router; sort, quantiser and both expert GEMMs in one launch; reduce
         return 1 + sort + 1 + 3       # fused router; sort; quantise; w13, w2, reduce
     # fused router; sort + publish counts; send bases, dispatch, receive plan, row destinations;
     # scale swizzle + (w13, w2) per compute part; reduce; three flag barriers

@@ -19,9 +19,20 @@
 // grouped_gemm.cu, with four stages: the plain epilogue stores its few rows straight from
 // registers (64 bytes per thread and half tile), so no staging tile takes shared memory from the
 // pipeline.  At most 128 tokens, so every expert has at most one row tile.
+//
+// In its kFront form the kernel also does what route_sort_quantize_small_kernel does, so a decode
+// layer step is three launches (router, this, reduce) and the weights start streaming while the
+// input is still being quantised.  Every CTA counts the batch's at most 1024 routes per expert
+// and derives the group geometry into its own shared memory (the same redundant counting sort,
+// 148 times instead of once per token); CTA t < tokens ranks the eight routes of token t and
+// quantises the token with three of its epilogue warps, then adds one to a counter (release).
+// The activation-side producer waits (bounded) until the counter has reached `tokens` before
+// its first load; the weight side waits for nothing.  The last CTA to finish puts the counters
+// back to zero for the next launch: no CTA can still be waiting on them then.
 #include "gv_common.cuh"
 #include "gv_gemm_parts.cuh"
 #include "gv_launchers.h"
+#include "gv_quantize.cuh"
 
 namespace gv {
 
@@ -55,8 +66,20 @@ struct alignas(1024) DecodeSmem {
   uint32_t tmem_base;
   volatile int abort;
   alignas(16) float erf_table[GV_ERF_TABLE_FLOATS];
+  // kFront: the group geometry of the batch, computed by this CTA, and the routes of its token
+  int expert_offsets[kExperts + 1];
+  int scale_row_offsets[kExperts + 1];
+  int tile_expert[kExperts];
+  int histogram[kExperts];
+  int m_tiles;
+  int own_expert[kTopK];
+  int own_rank[kTopK];
+  int route_row[kTopK];
+  float route_multiplier[kTopK];
+  unsigned long long route_scale_base[kTopK];
 };
 
+constexpr int kFrontQuantizeWarps = (kQuantizeThreadsPerToken + 31) / 32;  // epilogue warps 2..4
 constexpr size_t kDecSmemBytes = sizeof(DecodeSmem) + 1024;
 static_assert(kDecSmemBytes <= 232448, "shared memory budget");
 static_assert(kDecSfColumn + kDecSfColumnsPerStage * kDecStages <= kDecTmemColumns, "tensor memory budget");
@@ -64,7 +87,15 @@ static_assert(kDecSfColumn + kDecSfColumnsPerStage * kDecStages <= kDecTmemColum
 struct DecodeParams {
   GemmParams w13;   // fused form: next_codes / next_scales / next_scale_q set
   GemmParams w2;    // plain form: out (and optionally row_dest) set
-  int* tile_ready;  // [row tiles], zero on entry
+  int* tile_ready;  // [row tiles], zero on entry; zero again on exit where plan.front_sync exists
+  RoutePlan plan;   // kFront: written by CTA 0 (geometry) and by each token's CTA (its routes)
+  // kFront only
+  const __nv_bfloat16* input;   // bf16 [tokens, 2816]
+  const int* expert_ids;        // i32 [tokens, 8]
+  const float* in_scale_q;      // f32 [128]
+  uint8_t* packed;              // w13 operand codes
+  uint8_t* scales;              // w13 operand scale factors
+  int tokens;
 };
 
 struct DecodeItem {
@@ -114,6 +145,7 @@ __device__ __forceinline__ int load_acquire_gpu(const int* address) {
   return value;
 }
 
+template <bool kFront>
 __global__ void __launch_bounds__(kDecThreads, 1)
 decode_experts_kernel(const __grid_constant__ CUtensorMap map_a13, const __grid_constant__ CUtensorMap map_a13_32,
                       const __grid_constant__ CUtensorMap map_b13, const __grid_constant__ CUtensorMap map_b13_64,
@@ -156,7 +188,116 @@ decode_experts_kernel(const __grid_constant__ CUtensorMap map_a13, const __grid_
   const uint32_t tmem_base = smem->tmem_base;
   grid_dependency_wait();
 
-  const int m_tiles = params.w13.num_m_tiles[0];
+  // The geometry both GEMMs walk: the plan of an earlier launch, or this CTA's own copy.
+  const int* tile_expert = params.w13.tile_expert;
+  const int* expert_offsets = params.w13.expert_offsets;
+  const int* scale_row_offsets = params.w13.scale_row_offsets;
+  int m_tiles;
+  const bool has_token = kFront && static_cast<int>(blockIdx.x) < params.tokens;
+  if constexpr (kFront) {
+    constexpr int groups = kHidden / 16;
+    const int tid = threadIdx.x;
+    const int token = blockIdx.x;
+    const int routes = params.tokens * kTopK;
+    const RoutePlan& plan = params.plan;
+    if (tid < kExperts) smem->histogram[tid] = 0;
+    if (tid < kTopK) {
+      int expert = kExperts;
+      if (has_token) {
+        expert = params.expert_ids[token * kTopK + tid];
+        if (expert < 0 || expert >= kExperts) expert = kExperts;
+        else if (plan.remap) expert = plan.remap[expert];
+      }
+      smem->own_expert[tid] = expert;
+      smem->own_rank[tid] = 0;
+    }
+    __syncthreads();
+    for (int route = tid; route < routes; route += kDecThreads) {
+      int expert = params.expert_ids[route];
+      if (expert < 0 || expert >= kExperts) {
+        if (token == 0) atomicExch(status, static_cast<int>(kBadExpertId));
+        continue;
+      }
+      if (plan.remap) expert = plan.remap[expert];
+      atomicAdd(&smem->histogram[expert], 1);
+      if (has_token) {
+#pragma unroll
+        for (int k = 0; k < kTopK; ++k)
+          if (expert == smem->own_expert[k] && route < token * kTopK + k) atomicAdd(&smem->own_rank[k], 1);
+      }
+    }
+    __syncthreads();
+    if (warp == 0) {
+      // lane l scans experts 4l..4l+3: rows and row tiles (one per expert that has rows)
+      int counts[4], rows = 0, tiles = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        counts[i] = smem->histogram[4 * lane + i];
+        rows += counts[i];
+        tiles += (counts[i] + kTileM - 1) / kTileM;
+      }
+      int rows_inclusive = rows, tiles_inclusive = tiles;
+#pragma unroll
+      for (int offset = 1; offset < 32; offset <<= 1) {
+        const int r = __shfl_up_sync(0xffffffffu, rows_inclusive, offset);
+        const int t = __shfl_up_sync(0xffffffffu, tiles_inclusive, offset);
+        if (lane >= offset) {
+          rows_inclusive += r;
+          tiles_inclusive += t;
+        }
+      }
+      int row = rows_inclusive - rows, tile = tiles_inclusive - tiles;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int expert = 4 * lane + i;
+        const int expert_tiles = (counts[i] + kTileM - 1) / kTileM;
+        smem->expert_offsets[expert] = row;
+        smem->scale_row_offsets[expert] = tile * kTileM;
+        for (int j = 0; j < expert_tiles; ++j) smem->tile_expert[tile + j] = expert;
+        if (token == 0) {
+          plan.expert_offsets[expert] = row;
+          plan.scale_row_offsets[expert] = tile * kTileM;
+          for (int j = 0; j < expert_tiles; ++j) plan.tile_expert[tile + j] = expert;
+        }
+        row += counts[i];
+        tile += expert_tiles;
+      }
+      if (lane == 31) {
+        smem->expert_offsets[kExperts] = row;
+        smem->scale_row_offsets[kExperts] = tile * kTileM;
+        smem->m_tiles = tile;
+        if (token == 0) {
+          plan.expert_offsets[kExperts] = row;
+          plan.scale_row_offsets[kExperts] = tile * kTileM;
+          plan.num_m_tiles[0] = tile;
+        }
+      }
+    }
+    __syncthreads();
+    if (has_token && tid < kTopK) {
+      const int route = token * kTopK + tid;
+      const int expert = smem->own_expert[tid];
+      int dst = -1;
+      if (expert < kExperts) {
+        dst = smem->expert_offsets[expert] + smem->own_rank[tid];
+        plan.sorted_experts[dst] = expert;
+        plan.sorted_routes[dst] = route;
+        plan.inverse_routes[route] = dst;
+        // the static scale belongs to the expert id as the caller numbers it
+        smem->route_multiplier[tid] = params.in_scale_q[params.expert_ids[route]];
+        smem->route_scale_base[tid] = static_cast<unsigned long long>(smem->scale_row_offsets[expert]) * groups +
+                                      sf_offset(smem->own_rank[tid], 0, groups);
+      }
+      smem->route_row[tid] = dst;
+    }
+    __syncthreads();
+    tile_expert = smem->tile_expert;
+    expert_offsets = smem->expert_offsets;
+    scale_row_offsets = smem->scale_row_offsets;
+    m_tiles = smem->m_tiles;
+  } else {
+    m_tiles = params.w13.num_m_tiles[0];
+  }
   const int total_items = m_tiles * (kW13Items + kW2Items);
   const int rounds = (total_items + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
 
@@ -167,20 +308,40 @@ decode_experts_kernel(const __grid_constant__ CUtensorMap map_a13, const __grid_
     uint32_t phase = 0;
     int issued = 0;
     bool ok = true;
+    if (kFront && !weight_side) {
+      // the w13 operand exists once every token's CTA has quantised its token and counted itself
+      const long long start = clock64();
+      bool ready = false;
+      for (uint32_t spin = 0; !ready; ++spin) {
+        ready = load_acquire_gpu(params.plan.front_sync) >= params.tokens;
+        if (!ready) {
+          __nanosleep(64);
+          if ((spin & 63u) == 63u && (smem->abort || clock64() - start > kWaitLimitCycles)) {
+            if (!smem->abort) {
+              smem->abort = 1;
+              atomicExch(status, static_cast<int>(kWaitTimeout));
+            }
+            break;
+          }
+        }
+      }
+      ok = __all_sync(0xffffffffu, ready);
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+    }
     for (int round = 0; ok && round < rounds; ++round) {
       DecodeItem item;
       if (!decode_item(round, m_tiles, item)) continue;
       const GemmParams& p = item.down ? params.w2 : params.w13;
       const int k_blocks = item.down ? kW2KBlocks : kW13KBlocks;
       const int last_mmas = item.down ? kW2LastMmas : 4;
-      const int expert = p.tile_expert[item.m_tile];
+      const int expert = tile_expert[item.m_tile];
       int row = 0, row2 = 0;
       const uint8_t* sf_src;
       const uint8_t* sf_src2 = nullptr;
       bool short_tile = false, half_item = false;
       if (!weight_side) {
-        row = p.expert_offsets[expert] + (item.m_tile * kTileM - p.scale_row_offsets[expert]);
-        short_tile = p.expert_offsets[expert + 1] - row <= 32;
+        row = expert_offsets[expert] + (item.m_tile * kTileM - scale_row_offsets[expert]);
+        short_tile = expert_offsets[expert + 1] - row <= 32;
         sf_src = p.a_scales + static_cast<size_t>(item.m_tile) * kTileM * p.groups;
         if (item.down) {
           // the w2 operand rows of this tile exist once every epilogue warp of its six w13 items
@@ -336,14 +497,28 @@ decode_experts_kernel(const __grid_constant__ CUtensorMap map_a13, const __grid_
     const int quarter = warp & 3;
     const int sub = (warp - 2) >> 2;
     uint32_t acc_phase = 0;
+    if (kFront && has_token && warp < 2 + kFrontQuantizeWarps) {
+      // this CTA's token: quantised once per distinct static scale, stored to its eight sorted rows
+      const int part = threadIdx.x - 64;
+      if (part < kQuantizeThreadsPerToken) {
+        float values[32];
+        float maximum[2];
+        load_token_columns<2>(params.input, static_cast<int>(blockIdx.x), part, values, maximum);
+        quantize_routes_of_token<2>(values, maximum, part, smem->route_row, smem->route_multiplier,
+                                    smem->route_scale_base, params.packed, params.scales);
+      }
+      __threadfence();
+      named_barrier(1, kFrontQuantizeWarps * 32);
+      if (threadIdx.x == 64) atomicAdd(params.plan.front_sync, 1);
+    }
     for (int round = 0; round < rounds; ++round) {
       DecodeItem item;
       if (!decode_item(round, m_tiles, item)) continue;
       const GemmParams& p = item.down ? params.w2 : params.w13;
       const int m_tile = item.m_tile, n_tile = item.n_tile;
-      const int expert = p.tile_expert[m_tile];
-      const int row0 = p.expert_offsets[expert] + (m_tile * kTileM - p.scale_row_offsets[expert]);
-      const int rows_valid = p.expert_offsets[expert + 1] - row0;
+      const int expert = tile_expert[m_tile];
+      const int row0 = expert_offsets[expert] + (m_tile * kTileM - scale_row_offsets[expert]);
+      const int rows_valid = expert_offsets[expert + 1] - row0;
       const float alpha = p.alpha[expert];
       const bool acc_ready = wait_or_abort<true>(&smem->acc_full, acc_phase, smem, status);
       acc_phase ^= 1u;
@@ -401,6 +576,16 @@ decode_experts_kernel(const __grid_constant__ CUtensorMap map_a13, const __grid_
     __syncwarp();
     tmem_dealloc(tmem_base, kDecTmemColumns);
   }
+  if (params.plan.front_sync && threadIdx.x == 0) {
+    // The CTA that finishes last puts the counters back for the next launch.  Every wait on
+    // them lies before a CTA's end, so nobody reads them any more.
+    __threadfence();
+    if (atomicAdd(params.plan.front_sync + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+      for (int tile = 0; tile < m_tiles; ++tile) params.tile_ready[tile] = 0;
+      params.plan.front_sync[0] = 0;
+      params.plan.front_sync[1] = 0;
+    }
+  }
 }
 
 void fill_params(GemmParams& p, const GemmOperands& op, const RoutePlan& plan) {
@@ -425,8 +610,12 @@ void fill_params(GemmParams& p, const GemmOperands& op, const RoutePlan& plan) {
 }  // namespace
 
 int prepare_decode_experts() {
-  return static_cast<int>(cudaFuncSetAttribute(decode_experts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               static_cast<int>(kDecSmemBytes)));
+  cudaError_t e = cudaFuncSetAttribute(decode_experts_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kDecSmemBytes));
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(decode_experts_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(kDecSmemBytes));
+  return static_cast<int>(e);
 }
 
 void launch_decode_experts(const GemmOperands& w13_fused, const GemmOperands& w2, const RoutePlan& plan, int sm_count,
@@ -435,8 +624,29 @@ void launch_decode_experts(const GemmOperands& w13_fused, const GemmOperands& w2
   fill_params(params.w13, w13_fused, plan);
   fill_params(params.w2, w2, plan);
   params.tile_ready = plan.tile_ready;
-  launch_chained(decode_experts_kernel, dim3(sm_count), dim3(kDecThreads), kDecSmemBytes, stream, w13_fused.map_a,
-                 w13_fused.map_a32, w13_fused.map_b, w13_fused.map_b64, w2.map_a, w2.map_a32, w2.map_b, params);
+  params.plan = plan;
+  launch_chained(decode_experts_kernel<false>, dim3(sm_count), dim3(kDecThreads), kDecSmemBytes, stream,
+                 w13_fused.map_a, w13_fused.map_a32, w13_fused.map_b, w13_fused.map_b64, w2.map_a, w2.map_a32, w2.map_b,
+                 params);
+}
+
+void launch_decode_layer(const void* input_bf16, const int* expert_ids, const float* in_scale_q, int tokens,
+                         uint8_t* packed, uint8_t* scales, const GemmOperands& w13_fused, const GemmOperands& w2,
+                         const RoutePlan& plan, int sm_count, cudaStream_t stream) {
+  DecodeParams params{};
+  fill_params(params.w13, w13_fused, plan);
+  fill_params(params.w2, w2, plan);
+  params.tile_ready = plan.tile_ready;
+  params.input = static_cast<const __nv_bfloat16*>(input_bf16);
+  params.expert_ids = expert_ids;
+  params.in_scale_q = in_scale_q;
+  params.plan = plan;
+  params.packed = packed;
+  params.scales = scales;
+  params.tokens = tokens;
+  launch_chained(decode_experts_kernel<true>, dim3(sm_count), dim3(kDecThreads), kDecSmemBytes, stream,
+                 w13_fused.map_a, w13_fused.map_a32, w13_fused.map_b, w13_fused.map_b64, w2.map_a, w2.map_a32, w2.map_b,
+                 params);
 }
 
 }  // namespace gv

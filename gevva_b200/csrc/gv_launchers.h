@@ -28,6 +28,8 @@ struct RoutePlan {
   int* status;             // [1]   device status word (gv::Status)
   const int* remap;        // optional [128]: sort key = remap[expert id] (expert-parallel placement)
   int* sync;               // optional [2], zero on entry: arrival/departure counters of the one-launch sort
+  int* front_sync;         // optional [2], zero on entry and on exit: tokens quantised / CTAs finished, of the
+                           // decode kernel that sorts and quantises by itself
 };
 
 void launch_route(const void* logits_bf16, int ld, const void* expert_scale_bf16, float* weights,
@@ -135,6 +137,11 @@ int prepare_w13_pairs();
 // the fused w13 form, then w2, with per-tile readiness counters (plan.tile_ready) in between.
 void launch_decode_experts(const GemmOperands& w13_fused, const GemmOperands& w2, const RoutePlan& plan,
                            int sm_count, cudaStream_t stream);
+// The same with the route sort and the input quantiser inside (needs plan.front_sync and
+// tokens <= min(128, sm_count)): a decode layer step without the router and the reduce.
+void launch_decode_layer(const void* input_bf16, const int* expert_ids, const float* in_scale_q, int tokens,
+                         uint8_t* packed, uint8_t* scales, const GemmOperands& w13_fused, const GemmOperands& w2,
+                         const RoutePlan& plan, int sm_count, cudaStream_t stream);
 int prepare_decode_experts();
 
 // Must be called once per device before launch_grouped_gemm (sets the dynamic

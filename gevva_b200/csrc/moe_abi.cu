@@ -189,6 +189,7 @@ int make_scratch(int tokens, Scratch** out) {
   s->plan.chunk_hist = carve(chunks * kExperts);
   s->plan.status = carve(1);
   s->plan.sync = carve(2);  // taken from the 64 spare ints; zero like everything else here
+  s->plan.front_sync = carve(2);  // likewise
   *out = s;
   return GEVVA_MOE_OK;
 }
@@ -232,6 +233,7 @@ struct gevva_moe {
   bool w13_pair_form = false;       // GEVVA_MOE_OPTION_W13_PAIRS, or GEVVA_MOE_W13_PAIRS=1 for a whole process
   int sm_count = 0;
   bool pairs = false;               // GEVVA_MOE_OPTION_PAIRS: prefill-sized launches run the expert GEMMs as CTA pairs
+  bool decode_front = true;         // ... and the route sort and the input quantiser in the same launch (GEVVA_MOE_DECODE_FRONT=0: a launch of their own)
   bool merged_decode = true;        // batches of at most 128 tokens: w13 and w2 in one launch (GEVVA_MOE_DECODE_MERGED=0: two)
   bool nvtx = false;                // GEVVA_MOE_OPTION_NVTX: one range per stage around its launches
 };
@@ -292,6 +294,8 @@ int gevva_moe_create(gevva_moe** out, const gevva_moe_weights* weights, int max_
   // for a whole process by GEVVA_MOE_PAIRS=1.
   const char* merged_env = std::getenv("GEVVA_MOE_DECODE_MERGED");
   m->merged_decode = !(merged_env && merged_env[0] == '0');
+  const char* front_env = getenv("GEVVA_MOE_DECODE_FRONT");
+  m->decode_front = !(front_env && front_env[0] == '0');
   const char* pairs_env = std::getenv("GEVVA_MOE_PAIRS");
   m->pairs = (options && (options->flags & GEVVA_MOE_OPTION_PAIRS)) || (pairs_env && pairs_env[0] == '1');
   m->sm_count = prop.multiProcessorCount;
@@ -477,6 +481,16 @@ int gevva_moe_launch_stages(gevva_moe* runner, const void* in, const int* ids,
   // pairing two row tiles of an expert; they keep the one-CTA-per-tile kernel.
   const bool use_pairs = runner->pairs && tokens > gv::kFusedSortQuantizeMaxTokens;
   const unsigned front = GEVVA_MOE_STAGE_SORT | GEVVA_MOE_STAGE_QUANTIZE;
+  const unsigned layer_body = front | GEVVA_MOE_STAGE_W13 | GEVVA_MOE_STAGE_GEGLU | GEVVA_MOE_STAGE_W2;
+  if ((stages & layer_body) == layer_body && !(stages & GEVVA_MOE_STAGE_UNFUSED) && runner->merged_decode &&
+      runner->decode_front && tokens <= gv::kFusedSortQuantizeMaxTokens && tokens <= runner->sm_count) {
+    // decode-sized batch: sort, quantiser and both GEMMs in one persistent launch; the weights start
+    // streaming while the input is still being quantised
+    StageRange range(runner->nvtx, "gevva_moe.sort+quantize+w13+geglu+w2");
+    gv::launch_decode_layer(in, ids, runner->weights.in_scale_q1, tokens, s->input_codes, s->input_sf,
+                            runner->w13_fused, runner->w2, s->plan, runner->sm_count, stream);
+    stages &= ~layer_body;
+  }
   if ((stages & front) == front && tokens <= gv::kFusedSortQuantizeMaxTokens) {
     // decode-sized batch: one launch does both
     StageRange range(runner->nvtx, "gevva_moe.sort+quantize");

@@ -179,7 +179,7 @@ class Nvfp4ExpertRunner:
 
     def __del__(self):
         handle = getattr(self, "_handle", None)
-        if handle:
+        if handle and library is not None:  # module globals are gone at interpreter shutdown
             library().gevva_moe_destroy(handle)
             self._handle = None
 

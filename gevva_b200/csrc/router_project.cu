@@ -7,10 +7,12 @@
 // reach HBM: tokens sit on MMA-M (128 per tile), the 128 experts on MMA-N, K = 2816.
 //
 // A tile's K range is split over a cluster of four CTAs (two, or one, for batches whose tiles
-// would otherwise not fit one wave of SMs), so a 4096-token batch runs on 128 SMs and a
-// decode-sized batch streams the router matrix through four SMs instead of one.  Each
+// would otherwise not fit one wave of SMs; eight for batches of at most 512 tokens), so a
+// 4096-token batch runs on 128 SMs and a decode-sized batch streams the router matrix through
+// eight SMs instead of one.  Each
 // CTA accumulates its K slice in tensor memory (tcgen05.mma kind::f16 for bf16 operands,
-// kind::f8f6f4 for E4M3).  Tile row r belongs to CTA r % 4 of the cluster: every CTA stores its
+// kind::f8f6f4 for E4M3).  With a split of four, tile row r belongs to CTA r % 4 of the cluster:
+// every CTA stores its
 // 128 x 128 fp32 partial sums row by row straight into the owners' shared memory (posted
 // st.shared::cluster stores), and after one cluster barrier each owner sums the four partials of
 // its 32 rows in rank order (a fixed order: results do not depend on timing), adds the optional
@@ -28,8 +30,9 @@ namespace gv {
 
 namespace {
 
-// CTAs per cluster = K slices per token tile: 4, 2 or 1, the largest that keeps the launch within
-// one wave of SMs (a tile's pass is a chain of latencies, so waves cost more than depth)
+// CTAs per cluster = K slices per token tile: 8 for small batches, else 4, 2 or 1, the largest that
+// keeps the launch within one wave of SMs (a tile's pass is a chain of latencies, so waves cost more
+// than depth)
 constexpr int kRpStages = 5;
 constexpr int kRpThreads = 192;
 constexpr int kRpTileBytes = kTileM * kTileKBytes;  // 16 KiB: 128 rows of one 128-byte K block
@@ -245,11 +248,14 @@ route_project_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     const int t = threadIdx.x - 64;
     const int part = t & 3;         // columns [32 * part, 32 * part + 32)
 #pragma unroll 1
-    for (int pass = 0; pass < kOwnRows / 32; ++pass) {
+    for (int pass = 0; pass < (kOwnRows + 31) / 32; ++pass) {
       if (m_tile * kTileM + pass * 32 * kSplit >= p.tokens) break;   // no row of this pass exists
-      const int row_local = pass * 32 + (t >> 2);   // tile row kSplit * row_local + rank
+      // tile row kSplit * row_local + rank; with eight owners a CTA has 16 rows and half of the
+      // threads only keep their quads company (they read row 15 again and store nothing)
+      const bool row_owned = pass * 32 + (t >> 2) < kOwnRows;
+      const int row_local = row_owned ? pass * 32 + (t >> 2) : kOwnRows - 1;
       const int token = m_tile * kTileM + row_local * kSplit + static_cast<int>(rank);
-      const bool valid = token < p.tokens;
+      const bool valid = row_owned && token < p.tokens;
       float4 acc[8];
 #pragma unroll
       for (int source = 0; source < kSplit; ++source) {
@@ -340,6 +346,7 @@ template <bool kFp8>
 cudaError_t launch_split(const CUtensorMap& map_x, const CUtensorMap& map_w, const RouterParams& p,
                          cudaStream_t stream) {
   const int m_tiles = (p.tokens + kTileM - 1) / kTileM;
+  if (m_tiles <= 4) return launch_variant<kFp8, 8>(map_x, map_w, p, stream);
   if (m_tiles * 4 <= 160) return launch_variant<kFp8, 4>(map_x, map_w, p, stream);
   if (m_tiles * 2 <= 160) return launch_variant<kFp8, 2>(map_x, map_w, p, stream);
   return launch_variant<kFp8, 1>(map_x, map_w, p, stream);

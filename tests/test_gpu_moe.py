@@ -591,6 +591,64 @@ def test_merged_decode_launch_equals_two_launches(gm, weights, cuda_device, toke
     assert results[0][0].float().abs().max() > 0
 
 
+def test_decode_kernel_that_sorts_and_quantises_itself(gm, weights, cuda_device, monkeypatch):
+    """Batches of at most 128 tokens sort their routes and quantise their input inside the merged
+    expert launch.  Against a runner that keeps the sort + quantise launch of its own
+    (GEVVA_MOE_DECODE_FRONT=0): the same route plan, operand bytes, routed rows and output, over a
+    sequence of batch sizes on one runner (the launch puts its counters back itself), and an expert
+    id outside [0,128) is reported and its route left out as before."""
+    from gevva_b200 import runtime as rt
+    sequence = [(64, "random"), (8, "random"), (128, "skewed"), (1, "random"), (40, "skewed"), (64, "random")]
+    runners = {}
+    for front in ("0", "1"):
+        monkeypatch.setenv("GEVVA_MOE_DECODE_FRONT", front)
+        runners[front] = gm.Nvfp4ExpertRunner(weights[0], 128)
+    plan_buffers = (rt.BUF_SORTED_EXPERTS, rt.BUF_SORTED_ROUTES, rt.BUF_INVERSE_ROUTES, rt.BUF_EXPERT_OFFSETS,
+                    rt.BUF_SCALE_ROW_OFFSETS, rt.BUF_NUM_TILES)
+    for step, (tokens, kind) in enumerate(sequence):
+        ids = random_ids(tokens, 31 + step) if kind == "random" else skewed_ids(tokens)
+        x = hashgen.activations(tokens, HIDDEN, 90 + step, cuda_device)
+        dev_ids = torch.from_numpy(ids).to(cuda_device)
+        rw = torch.full((tokens, TOP_K), 0.125, device=cuda_device)
+        routes = tokens * TOP_K
+        seen = []
+        for front in ("0", "1"):
+            runner = runners[front]
+            out = torch.zeros_like(x)
+            runner.launch_batch(x, dev_ids, rw, out, tokens)
+            runner.check()
+            record = [out, runner.buffer(rt.BUF_INPUT_CODES)[: routes * HIDDEN // 2].clone(),
+                      runner.buffer(rt.BUF_W2_OUT, torch.bfloat16)[: routes * HIDDEN].clone()]
+            for buffer_id in plan_buffers:
+                view = runner.buffer(buffer_id, torch.int32)
+                record.append((view[:routes] if buffer_id <= rt.BUF_INVERSE_ROUTES else view).clone())
+            tiles = int(runner.buffer(rt.BUF_NUM_TILES, torch.int32)[0])
+            record.append(runner.buffer(rt.BUF_TILE_EXPERT, torch.int32)[:tiles].clone())
+            seen.append(record)
+        for a, b in zip(*seen):
+            assert torch.equal(a, b), f"step {step} ({tokens} tokens)"
+        assert seen[0][0].float().abs().max() > 0
+    # a rejected expert id
+    tokens = 16
+    ids = random_ids(tokens, 5)
+    ids[7, 2] = 128
+    x = hashgen.activations(tokens, HIDDEN, 12, cuda_device)
+    rw = torch.full((tokens, TOP_K), 0.125, device=cuda_device)
+    outs = []
+    for front in ("0", "1"):
+        out = torch.zeros_like(x)
+        runners[front].launch_stages(rt.STAGE_ALL & ~rt.STAGE_REDUCE, tokens, input=x,
+                                     expert_ids=torch.from_numpy(ids).to(cuda_device))
+        assert runners[front].last_status() == -1
+        assert runners[front].last_status() == 0
+        inverse = runners[front].buffer(rt.BUF_INVERSE_ROUTES, torch.int32)[: tokens * TOP_K].clone()
+        rows = runners[front].buffer(rt.BUF_W2_OUT, torch.bfloat16)[: tokens * TOP_K * HIDDEN].view(-1, HIDDEN)
+        keep = torch.ones(tokens * TOP_K, dtype=torch.bool, device=cuda_device)
+        keep[7 * TOP_K + 2] = False
+        outs.append(rows[inverse[keep].long()].clone())
+    assert torch.equal(outs[0], outs[1])
+
+
 def test_nvtx_ranges_do_not_change_results(gm, weights, cuda_device):
     """A runner created with the NVTX option marks its stages and computes the same bits; unknown
     option flags are refused."""

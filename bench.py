@@ -148,7 +148,7 @@ def layer_step(layer, x, out, weights, ids):
     runner.launch_batch(x, ids, weights, out, x.shape[0])
 
 
-def launches_per_step(world, tokens, sm_count=148, ep_chunks=2):
+def launches_per_step(world, tokens, sm_count=148, ep_chunks=2, ep_parts=1):
     """Kernels of the library that one layer step launches, counted from the launch paths
     (gevva_moe_launch_stages in csrc/moe_abi.cu, the four gevva_moe_ep_* calls in csrc/ep.cu)."""
     sort = 1 if tokens * TOP_K <= 1024 or (tokens * TOP_K + 1023) // 1024 <= sm_count else 3
@@ -158,7 +158,11 @@ def launches_per_step(world, tokens, sm_count=148, ep_chunks=2):
         return 1 + sort + 1 + 3       # fused router; sort; quantise; w13, w2, reduce
     # fused router; sort + publish counts; send bases, dispatch, receive plan, row destinations;
     # scale swizzle + (w13, w2) per compute part; reduce; three flag barriers
-    return 1 + (sort + 1) + 4 + (1 + 2 * ep_chunks) + 1 + 3
+    # (the router once; everything else once per micro-batch in flight)
+    if ep_parts > 1:
+        share = (tokens + ep_parts - 1) // ep_parts
+        sort = 1 if share * TOP_K <= 1024 or (share * TOP_K + 1023) // 1024 <= sm_count else 3
+    return 1 + ep_parts * ((sort + 1) + 4 + (1 + 2 * ep_chunks) + 1 + 3)
 
 
 def timed_loop(fn, steps):
@@ -610,6 +614,21 @@ def run_gpu(args):
         dist.all_reduce(equal, op=dist.ReduceOp.MIN)
         ep_parity = "bit-equal" if int(equal[0]) == 1 else "MISMATCH"
         layer.ep = ep
+        if args.ep_parts > 1:
+            # the timed step runs the batch as micro-batches in flight on streams of their own (the
+            # plain runner stays for the phase times); same bits required
+            from gevva_b200.expert_parallel import MicroBatchedExpertParallel
+            micro = MicroBatchedExpertParallel(local_expert_weights(layer.weights, rank, world, placement),
+                                               layer.weights.in_scale_q1, TOKENS, placement=placement,
+                                               parts=args.ep_parts)
+            out.zero_()
+            micro.launch_batch(x, ids, weights, out, TOKENS)
+            status, _ = micro.status()
+            equal = torch.tensor([1 if (status == 0 and torch.equal(out, want)) else 0], device=device)
+            dist.all_reduce(equal, op=dist.ReduceOp.MIN)
+            if int(equal[0]) != 1:
+                ep_parity = "MISMATCH"
+            layer.ep = micro
 
     def check():
         if layer.ep is not None:
@@ -720,8 +739,8 @@ def run_gpu(args):
     w2_ms = sum(a.elapsed_time(b) for a, b in zip(h0, h1)) / args.steps
 
     ep_phases = None
-    if layer.ep is not None:
-        samples = [layer.ep.timed_step(x, ids, weights, out, TOKENS) for _ in range(5)]
+    if ep is not None:
+        samples = [ep.timed_step(x, ids, weights, out, TOKENS) for _ in range(5)]
         ep_phases = {k: sum(s[k] for s in samples[1:]) / (len(samples) - 1) for k in samples[0]}
 
     times = torch.tensor([elapsed_ms, e2e_ms, sustained_ms], dtype=torch.float64, device=device)
@@ -745,7 +764,7 @@ def run_gpu(args):
         achieved = W13_FLOP_PER_TOKEN * TOKENS / (w13_ms * 1e-3) / 1e12
         total_tokens = TOKENS * world * args.steps
         value = total_tokens / (elapsed_ms * 1e-3)
-        per_step = launches_per_step(world, TOKENS)
+        per_step = launches_per_step(world, TOKENS, ep_parts=args.ep_parts if world > 1 else 1)
         line = {
             "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": warmup,
@@ -758,7 +777,9 @@ def run_gpu(args):
                        "parallelism": "single GPU" if world == 1 else
                        f"expert parallel x{world}: 128/{world} experts per GPU placed by the load of a "
                        "calibration batch, tokens data-parallel, "
-                       "dispatch/combine by stores into peer memory over NVLink",
+                       "dispatch/combine by stores into peer memory over NVLink"
+                       + (f", {args.ep_parts} micro-batches of a rank's batch in flight on streams of their own"
+                          if args.ep_parts > 1 else ""),
                        "l2": "inputs larger than L2: 428 MB of expert weights stream every step"},
             "layer_tflops": FLOP_PER_TOKEN * TOKENS / (elapsed_ms / args.steps * 1e-3) / 1e12,
             "sustained": None if args.no_sustained else {
@@ -847,6 +868,9 @@ def main():
     parser.add_argument("--no-config4", action="store_true", help="skip the 16384-token single-GPU record")
     parser.add_argument("--no-sustained", action="store_true",
                         help="skip the two-second loop (for a profiler, which would replay thousands of launches)")
+    parser.add_argument("--ep-parts", type=int, default=1,
+                        help="micro-batches of a rank's batch in flight in the expert-parallel step "
+                             "(measured slower at 2 than at 1 on two GPUs, so 1)")
     parser.add_argument("--no-ep-config4", action="store_true",
                         help="with several GPUs: skip the 16384-token Zipf expert-parallel records")
     args = parser.parse_args()

@@ -11,11 +11,10 @@
 // 4096-token batch runs on 128 SMs and a decode-sized batch streams the router matrix through
 // eight SMs instead of one.  Each
 // CTA accumulates its K slice in tensor memory (tcgen05.mma kind::f16 for bf16 operands,
-// kind::f8f6f4 for E4M3).  With a split of four, tile row r belongs to CTA r % 4 of the cluster:
-// every CTA stores its
-// 128 x 128 fp32 partial sums row by row straight into the owners' shared memory (posted
-// st.shared::cluster stores), and after one cluster barrier each owner sums the four partials of
-// its 32 rows in rank order (a fixed order: results do not depend on timing), adds the optional
+// kind::f8f6f4 for E4M3).  Tile row r belongs to CTA r % split of the cluster: every CTA stores
+// its 128 x 128 fp32 partial sums row by row straight into the owners' shared memory (posted
+// st.shared::cluster stores), and after one cluster barrier each owner sums the partials of its
+// 128 / split rows in rank order (a fixed order: results do not depend on timing), adds the optional
 // per-expert bias, rounds to bf16 as the GEMM would have stored it, and routes its rows with four
 // lanes per token (gv_route.cuh).
 //

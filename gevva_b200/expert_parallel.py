@@ -193,3 +193,65 @@ class ExpertParallelRunner:
         with torch.cuda.device(self.device):
             status = library().gevva_moe_ep_status(self._handle, ctypes.byref(rows))
         return status, rows.value
+
+
+class MicroBatchedExpertParallel:
+    """The same layer with a rank's batch cut into `parts` micro-batches (two by default), each
+    with an ExpertParallelRunner of its own (own peer buffers and flags) on a stream of its own.
+
+    The phases of a step alternate between the NVLink (dispatch, the w2 epilogue's stores) and the
+    SMs (sort, w13); one batch leaves each idle half of the time.  Two micro-batches in flight fill
+    the gaps: while one streams its results to the peers the other computes.  Every token's result
+    is what the single runner gives, bit for bit: a sorted row's arithmetic does not depend on
+    which rows share its tile.  `launch_batch` returns with the caller's stream waiting for all
+    micro-batches, so a step is still a step.
+
+    Measured on two B200s at 4096 tokens per GPU: 0.434 ms per step with two micro-batches against
+    0.394 ms with one (every fixed cost of a step is paid twice and the persistent GEMM launches
+    of the two streams take turns on the SMs rather than sharing them), so the plain runner is
+    what the benchmark uses; this class is kept as the tested way to run it."""
+
+    def __init__(self, local_weights: ExpertWeights, in_scale_q1_global: torch.Tensor, max_tokens: int,
+                 group=None, placement=None, parts: int = 2):
+        if parts < 1:
+            raise ValueError("parts: at least one micro-batch")
+        self.parts = parts
+        self.max_tokens = max_tokens
+        self._share = (max_tokens + parts - 1) // parts
+        self._runners = [ExpertParallelRunner(local_weights, in_scale_q1_global, self._share, group, placement)
+                         for _ in range(parts)]
+        self.device = self._runners[0].device
+        self.rank, self.world = self._runners[0].rank, self._runners[0].world
+        self._streams = [torch.cuda.Stream(device=self.device) for _ in range(parts)]
+
+    def launch_batch(self, input, expert_ids, route_weights, output, tokens, stream=None):
+        """Same contract as ExpertParallelRunner.launch_batch."""
+        _check(input, torch.bfloat16, (tokens, HIDDEN), "input")
+        _check(expert_ids, torch.int32, (tokens, TOP_K), "expert_ids")
+        _check(route_weights, torch.float32, (tokens, TOP_K), "route_weights")
+        _check(output, torch.bfloat16, (tokens, HIDDEN), "output")
+        if tokens > self.max_tokens:
+            raise GevvaMoeError(-3, "MicroBatchedExpertParallel.launch_batch")
+        caller = stream if stream is not None else torch.cuda.current_stream(self.device)
+        # every rank must run the same number of micro-batches (their barriers pair up), so the
+        # cut depends on the capacity only, and ranks are expected to bring equal token counts
+        share = (tokens + self.parts - 1) // self.parts
+        ready = caller.record_event()
+        first = 0
+        for runner, side in zip(self._runners, self._streams):
+            count = min(share, tokens - first)
+            if count <= 0:
+                break
+            side.wait_event(ready)
+            rows = slice(first, first + count)
+            runner.launch_batch(input[rows], expert_ids[rows], route_weights[rows], output[rows], count, side)
+            caller.wait_event(side.record_event())
+            first += count
+
+    def status(self):
+        worst, rows = 0, 0
+        for runner in self._runners:
+            status, received = runner.status()
+            worst = worst or status
+            rows += received
+        return worst, rows

@@ -88,6 +88,19 @@ def _worker(rank, world, port, result_dir):
         status, rows = placed.status()
         assert status == 0, status
         assert torch.equal(got, want), f"rank {rank} explicit stream: {(got != want).sum().item()} differ"
+        # two micro-batches in flight on two streams, each with peer buffers of its own: the same bits,
+        # also when the step is repeated back to back
+        from gevva_b200.expert_parallel import MicroBatchedExpertParallel
+        halves = MicroBatchedExpertParallel(local_expert_weights(full, rank, world, placement), full.in_scale_q1,
+                                            512, placement=placement)
+        for repeat in range(3):
+            got = torch.zeros_like(x)
+            halves.launch_batch(x, ids, rw, got, tokens)
+            status, rows = halves.status()
+            assert status == 0, status
+            assert rows > 0
+            assert torch.equal(got, want), f"rank {rank} micro-batches, repeat {repeat}: " \
+                f"{(got != want).sum().item()} differ"
         open(os.path.join(result_dir, f"ok{rank}"), "w").write("ok")
     finally:
         dist.destroy_process_group()

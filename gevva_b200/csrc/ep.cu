@@ -105,17 +105,27 @@ ep_publish_counts_kernel(EpDevice ep, RoutePlan plan) {
 
 // ---- 2a: where this rank's rows land on their owners ------------------------------
 __global__ void __launch_bounds__(kExperts) ep_send_bases_kernel(EpDevice ep) {
+  // The count matrix is read once, coalesced, into shared memory: the prefix loops below would
+  // otherwise be chains of up to 128 dependent trips to L2 in this single CTA.
+  __shared__ int counts[kMaxWorld][kExperts];
+  __shared__ int totals[kExperts];
   const int v = threadIdx.x;
   const int el = ep.local_experts;
+  int total = 0;
+  for (int s = 0; s < ep.world; ++s) {
+    const int c = ep.counts[s * kExperts + v];
+    counts[s][v] = c;
+    total += c;
+  }
+  totals[v] = total;
+  __syncthreads();
   const int owner_first = (v / el) * el;
   int expert_base = 0, scale_rows = 0, src_prefix = 0;
   for (int u = owner_first; u < v; ++u) {
-    int total = 0;
-    for (int s = 0; s < ep.world; ++s) total += ep.counts[s * kExperts + u];
-    expert_base += total;
-    scale_rows += (total + kTileM - 1) / kTileM * kTileM;
+    expert_base += totals[u];
+    scale_rows += (totals[u] + kTileM - 1) / kTileM * kTileM;
   }
-  for (int s = 0; s < ep.rank; ++s) src_prefix += ep.counts[s * kExperts + v];
+  for (int s = 0; s < ep.rank; ++s) src_prefix += counts[s][v];
   ep.send_row_base[v] = expert_base + src_prefix;
   ep.send_src_prefix[v] = src_prefix;
   ep.send_scale_rows[v] = scale_rows;
@@ -229,12 +239,16 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ input, const int* __restric
 // ---- 3a: group geometry of the local experts ---------------------------------------
 __global__ void __launch_bounds__(kExperts) ep_receive_plan_kernel(EpDevice ep, RoutePlan plan, int* split, int chunks) {
   __shared__ int scan_scratch[16];
+  // the count matrix, read once and coalesced (see ep_send_bases_kernel)
+  __shared__ int counts[kMaxWorld][kExperts];
   const int le = threadIdx.x;
   const int el = ep.local_experts;
+  for (int s = 0; s < ep.world; ++s) counts[s][le] = ep.counts[s * kExperts + le];
+  __syncthreads();
   int count = 0;
   if (le < el) {
     const int v = ep.rank * el + le;
-    for (int s = 0; s < ep.world; ++s) count += ep.counts[s * kExperts + v];
+    for (int s = 0; s < ep.world; ++s) count += counts[s][v];
   }
   publish_groups(count, 0, plan, scan_scratch);
   // sorted position, on source rank s, of the first row it sent to local expert le
@@ -242,7 +256,7 @@ __global__ void __launch_bounds__(kExperts) ep_receive_plan_kernel(EpDevice ep, 
     const int s = index / el, e = index % el;
     const int v = ep.rank * el + e;
     int offset = 0;
-    for (int u = 0; u < v; ++u) offset += ep.counts[s * kExperts + u];
+    for (int u = 0; u < v; ++u) offset += counts[s][u];
     ep.source_offsets[index] = offset;
   }
   // `chunks` parts of the tile list, cut at expert boundaries near equal shares:
@@ -276,8 +290,14 @@ ep_swizzle_scales_kernel(const uint8_t* __restrict__ staged, EpDevice ep, RouteP
                          uint8_t* __restrict__ scales) {
   constexpr int groups = kHidden / 16;
   constexpr int words = groups / 4;  // 44 per row
+  // the group geometry in shared memory: every word's search is a chain of dependent loads
+  __shared__ int expert_offsets[kExperts + 1];
+  __shared__ int scale_row_offsets[kExperts];
+  for (int i = threadIdx.x; i <= kExperts; i += blockDim.x) expert_offsets[i] = plan.expert_offsets[i];
+  for (int i = threadIdx.x; i < kExperts; i += blockDim.x) scale_row_offsets[i] = plan.scale_row_offsets[i];
+  __syncthreads();
   const int el = ep.local_experts;
-  const int total = plan.expert_offsets[kExperts];
+  const int total = expert_offsets[kExperts];
   const long long items = static_cast<long long>(total) * words;
   for (long long index = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; index < items;
        index += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -286,11 +306,11 @@ ep_swizzle_scales_kernel(const uint8_t* __restrict__ staged, EpDevice ep, RouteP
     int lo = 0, hi = el - 1;
     while (lo < hi) {
       const int mid = (lo + hi + 1) >> 1;
-      if (plan.expert_offsets[mid] <= row) lo = mid; else hi = mid - 1;
+      if (expert_offsets[mid] <= row) lo = mid; else hi = mid - 1;
     }
-    const int row_in_expert = row - plan.expert_offsets[lo];
+    const int row_in_expert = row - expert_offsets[lo];
     const uint32_t value = reinterpret_cast<const uint32_t*>(staged + static_cast<size_t>(row) * groups)[word];
-    *reinterpret_cast<uint32_t*>(scales + static_cast<size_t>(plan.scale_row_offsets[lo]) * groups +
+    *reinterpret_cast<uint32_t*>(scales + static_cast<size_t>(scale_row_offsets[lo]) * groups +
                                  sf_offset(row_in_expert, 4 * word, groups)) = value;
   }
 }
@@ -301,25 +321,35 @@ ep_swizzle_scales_kernel(const uint8_t* __restrict__ staged, EpDevice ep, RouteP
 // results cross NVLink while the GEMM is still running and never touch local memory.
 __global__ void __launch_bounds__(256)
 ep_row_destinations_kernel(EpDevice ep, RoutePlan plan, unsigned long long* __restrict__ row_dest) {
+  // the three small tables every row consults, in shared memory: a row's search is a chain of
+  // dependent loads
+  __shared__ int expert_offsets[kExperts + 1];
+  __shared__ int local_counts[kExperts];    // [source][local expert]
+  __shared__ int source_offsets[kExperts];  // [source][local expert]
   const int el = ep.local_experts;
-  const int total = plan.expert_offsets[kExperts];
+  for (int i = threadIdx.x; i <= kExperts; i += blockDim.x) expert_offsets[i] = plan.expert_offsets[i];
+  for (int i = threadIdx.x; i < ep.world * el; i += blockDim.x) {
+    local_counts[i] = ep.counts[(i / el) * kExperts + ep.rank * el + i % el];
+    source_offsets[i] = ep.source_offsets[i];
+  }
+  __syncthreads();
+  const int total = expert_offsets[kExperts];
   for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < total; row += gridDim.x * blockDim.x) {
     // local expert of this row: the last le with expert_offsets[le] <= row
     int lo = 0, hi = el - 1;
     while (lo < hi) {
       const int mid = (lo + hi + 1) >> 1;
-      if (plan.expert_offsets[mid] <= row) lo = mid; else hi = mid - 1;
+      if (expert_offsets[mid] <= row) lo = mid; else hi = mid - 1;
     }
     const int le = lo;
-    int within = row - plan.expert_offsets[le];
-    const int v = ep.rank * el + le;
+    int within = row - expert_offsets[le];
     int s = 0;
     for (; s < ep.world - 1; ++s) {
-      const int c = ep.counts[s * kExperts + v];
+      const int c = local_counts[s * el + le];
       if (within < c) break;
       within -= c;
     }
-    const int dst_row = ep.source_offsets[s * el + le] + within;
+    const int dst_row = source_offsets[s * el + le] + within;
     row_dest[row] = reinterpret_cast<unsigned long long>(ep.peer_combine[s] +
                                                          static_cast<size_t>(dst_row) * kHidden);
   }

@@ -156,13 +156,13 @@ def launches_per_step(world, tokens, sm_count=148, ep_chunks=2, ep_parts=1):
         if tokens <= 128:
             return 1 + 1 + 1          # fused router; sort, quantiser and both expert GEMMs in one launch; reduce
         return 1 + sort + 1 + 3       # fused router; sort; quantise; w13, w2, reduce
-    # fused router; sort + publish counts; send bases, dispatch, receive plan, row destinations;
-    # scale swizzle + (w13, w2) per compute part; reduce; three flag barriers
+    # fused router; sort + count exchange (with the first barrier inside); dispatch, row destinations;
+    # scale re-tiling + (w13, w2) per compute part; reduce; two flag barriers
     # (the router once; everything else once per micro-batch in flight)
     if ep_parts > 1:
         share = (tokens + ep_parts - 1) // ep_parts
         sort = 1 if share * TOP_K <= 1024 or (share * TOP_K + 1023) // 1024 <= sm_count else 3
-    return 1 + ep_parts * ((sort + 1) + 4 + (1 + 2 * ep_chunks) + 1 + 3)
+    return 1 + ep_parts * ((sort + 1) + 2 + (1 + 2 * ep_chunks) + 1 + 2)
 
 
 def timed_loop(fn, steps):
@@ -555,7 +555,7 @@ def ep_record(layer, world, rank, device, tokens_per_gpu, placement_kind, steps,
         "phases_us_rank0": phases,
         "no_comm_us_max_over_ranks": float(worst[1]),
         "exposed_comm_us": step_us - float(worst[1]),
-        "exposed_comm_definition": "step time minus (router + route sort + dispatch with local stores + compute "
+        "exposed_comm_definition": "step time minus (router + route sort with its count exchange + dispatch with local stores + compute "
                                    "with local result stores + reduce), max over ranks",
         "nccl_all_to_all_exchange_only": nccl_exchange_only(counts.cpu(), world, rank, device),
     }

@@ -95,22 +95,41 @@ __global__ void __launch_bounds__(32) ep_barrier_kernel(EpDevice ep, int epoch, 
   }
 }
 
-// ---- 1: publish this rank's per-expert counts into every peer's matrix -------------
+// ---- 1: the count exchange and everything that depends on the counts only ------------
+// One CTA of 128 threads, launched behind the route sort:
+//   - thread v stores this rank's count of sort key v into every peer's count matrix;
+//   - a flag barrier (the protocol of ep_barrier_kernel, same flags and epoch sequence): when it
+//     ends every rank's counts of this step are in this rank's matrix, and every rank has
+//     finished reading its receive buffers of the step before;
+//   - the matrix is read once, coalesced, into shared memory (the prefix loops below would
+//     otherwise be chains of dependent trips to L2);
+//   - send side: where this rank's rows land on their owners;
+//   - receive side: the group geometry of the local experts, the sorted position on each source
+//     of the first row it sends to each local expert, and the parts of the compute phase.
+// These were five launches (publish, barrier, send bases, receive plan; 19 us of kernels and
+// their gaps at one rank); as one they take about 8 us.
 __global__ void __launch_bounds__(kExperts)
-ep_publish_counts_kernel(EpDevice ep, RoutePlan plan) {
-  const int v = threadIdx.x;
-  const int count = plan.expert_offsets[v + 1] - plan.expert_offsets[v];
-  for (int d = 0; d < ep.world; ++d) ep.peer_counts[d][ep.rank * kExperts + v] = count;
-}
-
-// ---- 2a: where this rank's rows land on their owners ------------------------------
-__global__ void __launch_bounds__(kExperts) ep_send_bases_kernel(EpDevice ep) {
-  // The count matrix is read once, coalesced, into shared memory: the prefix loops below would
-  // otherwise be chains of up to 128 dependent trips to L2 in this single CTA.
+ep_exchange_kernel(EpDevice ep, RoutePlan send_plan, RoutePlan plan, int* split, int chunks, int epoch,
+                   int* status) {
   __shared__ int counts[kMaxWorld][kExperts];
   __shared__ int totals[kExperts];
+  __shared__ int scan_scratch[16];
+  __shared__ int first_tile[kExperts + 1];
   const int v = threadIdx.x;
+  const int le = threadIdx.x;
   const int el = ep.local_experts;
+  {
+    const int count = send_plan.expert_offsets[v + 1] - send_plan.expert_offsets[v];
+    for (int d = 0; d < ep.world; ++d) ep.peer_counts[d][ep.rank * kExperts + v] = count;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (v < ep.world) {
+    DeviceFlagPort port{ep, 0};
+    ep_barrier_announce(port, ep.rank, v, epoch);
+    if (!ep_barrier_await(port, v, epoch)) atomicExch(status, static_cast<int>(kWaitTimeout));
+  }
+  __syncthreads();
   int total = 0;
   for (int s = 0; s < ep.world; ++s) {
     const int c = ep.counts[s * kExperts + v];
@@ -119,16 +138,57 @@ __global__ void __launch_bounds__(kExperts) ep_send_bases_kernel(EpDevice ep) {
   }
   totals[v] = total;
   __syncthreads();
-  const int owner_first = (v / el) * el;
-  int expert_base = 0, scale_rows = 0, src_prefix = 0;
-  for (int u = owner_first; u < v; ++u) {
-    expert_base += totals[u];
-    scale_rows += (totals[u] + kTileM - 1) / kTileM * kTileM;
+  // send side
+  {
+    const int owner_first = (v / el) * el;
+    int expert_base = 0, scale_rows = 0, src_prefix = 0;
+    for (int u = owner_first; u < v; ++u) {
+      expert_base += totals[u];
+      scale_rows += (totals[u] + kTileM - 1) / kTileM * kTileM;
+    }
+    for (int s = 0; s < ep.rank; ++s) src_prefix += counts[s][v];
+    ep.send_row_base[v] = expert_base + src_prefix;
+    ep.send_src_prefix[v] = src_prefix;
+    ep.send_scale_rows[v] = scale_rows;
   }
-  for (int s = 0; s < ep.rank; ++s) src_prefix += counts[s][v];
-  ep.send_row_base[v] = expert_base + src_prefix;
-  ep.send_src_prefix[v] = src_prefix;
-  ep.send_scale_rows[v] = scale_rows;
+  // receive side
+  const int count = le < el ? totals[ep.rank * el + le] : 0;
+  publish_groups(count, 0, plan, scan_scratch);
+  // sorted position, on source rank s, of the first row it sent to local expert le
+  for (int index = threadIdx.x; index < ep.world * el; index += kExperts) {
+    const int s = index / el, e = index % el;
+    const int key = ep.rank * el + e;
+    int offset = 0;
+    for (int u = 0; u < key; ++u) offset += counts[s][u];
+    ep.source_offsets[index] = offset;
+  }
+  // `chunks` parts of the tile list, cut at expert boundaries near equal shares:
+  // split = {first tile, tile count} of each part.  Thread 0 walks the experts' first tiles,
+  // which publish_groups has just written, from a copy in shared memory.
+  __syncthreads();
+  first_tile[le] = plan.scale_row_offsets[le] / kTileM;
+  if (le == 0) first_tile[kExperts] = plan.scale_row_offsets[kExperts] / kTileM;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int all_tiles = first_tile[kExperts];
+    int first = 0;
+    int expert = 1;
+    for (int part = 0; part < chunks; ++part) {
+      int cut = all_tiles;
+      if (part + 1 < chunks) {
+        for (; expert < el; ++expert) {
+          const int begin = first_tile[expert];
+          if (chunks * begin >= (part + 1) * all_tiles) {
+            cut = begin;
+            break;
+          }
+        }
+      }
+      split[2 * part] = first;
+      split[2 * part + 1] = cut - first;
+      first = cut;
+    }
+  }
 }
 
 // ---- 2b: quantise and store into the owners' operand buffers -----------------------
@@ -236,82 +296,57 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ input, const int* __restric
   }
 }
 
-// ---- 3a: group geometry of the local experts ---------------------------------------
-__global__ void __launch_bounds__(kExperts) ep_receive_plan_kernel(EpDevice ep, RoutePlan plan, int* split, int chunks) {
-  __shared__ int scan_scratch[16];
-  // the count matrix, read once and coalesced (see ep_send_bases_kernel)
-  __shared__ int counts[kMaxWorld][kExperts];
-  const int le = threadIdx.x;
-  const int el = ep.local_experts;
-  for (int s = 0; s < ep.world; ++s) counts[s][le] = ep.counts[s * kExperts + le];
-  __syncthreads();
-  int count = 0;
-  if (le < el) {
-    const int v = ep.rank * el + le;
-    for (int s = 0; s < ep.world; ++s) count += counts[s][v];
-  }
-  publish_groups(count, 0, plan, scan_scratch);
-  // sorted position, on source rank s, of the first row it sent to local expert le
-  for (int index = threadIdx.x; index < ep.world * el; index += kExperts) {
-    const int s = index / el, e = index % el;
-    const int v = ep.rank * el + e;
-    int offset = 0;
-    for (int u = 0; u < v; ++u) offset += counts[s][u];
-    ep.source_offsets[index] = offset;
-  }
-  // `chunks` parts of the tile list, cut at expert boundaries near equal shares:
-  // split = {first tile, tile count} of each part.
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const int total = plan.num_m_tiles[0];
-    int first = 0;
-    int expert = 1;
-    for (int part = 0; part < chunks; ++part) {
-      int cut = total;
-      if (part + 1 < chunks) {
-        for (; expert < el; ++expert) {
-          const int begin = plan.scale_row_offsets[expert] / kTileM;
-          if (chunks * begin >= (part + 1) * total) {
-            cut = begin;
-            break;
-          }
-        }
-      }
-      split[2 * part] = first;
-      split[2 * part + 1] = cut - first;
-      first = cut;
-    }
-  }
-}
-
 // ---- 3a': received scale rows -> the interleaved layout of the w13 operand -------------
+// One CTA per 128-row tile of the receive plan (grid-stride): the tile's rows are contiguous in
+// the staging buffer (176 bytes each), so they are read as one run of 4-byte words into shared
+// memory, and written as the tile's 44 atoms of 512 bytes, 16 bytes (rows q, q+32, q+64, q+96
+// of one 4-group word) per thread.  Rows past the expert's end get scale zero.
 __global__ void __launch_bounds__(256)
 ep_swizzle_scales_kernel(const uint8_t* __restrict__ staged, EpDevice ep, RoutePlan plan,
                          uint8_t* __restrict__ scales) {
   constexpr int groups = kHidden / 16;
   constexpr int words = groups / 4;  // 44 per row
-  // the group geometry in shared memory: every word's search is a chain of dependent loads
-  __shared__ int expert_offsets[kExperts + 1];
-  __shared__ int scale_row_offsets[kExperts];
-  for (int i = threadIdx.x; i <= kExperts; i += blockDim.x) expert_offsets[i] = plan.expert_offsets[i];
-  for (int i = threadIdx.x; i < kExperts; i += blockDim.x) scale_row_offsets[i] = plan.scale_row_offsets[i];
-  __syncthreads();
-  const int el = ep.local_experts;
-  const int total = expert_offsets[kExperts];
-  const long long items = static_cast<long long>(total) * words;
-  for (long long index = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; index < items;
-       index += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int row = static_cast<int>(index / words);
-    const int word = static_cast<int>(index % words);
-    int lo = 0, hi = el - 1;
-    while (lo < hi) {
-      const int mid = (lo + hi + 1) >> 1;
-      if (expert_offsets[mid] <= row) lo = mid; else hi = mid - 1;
+  __shared__ uint32_t tile[kTileM][words + 1];
+  (void)ep;
+  const int tiles = plan.num_m_tiles[0];
+  for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
+    const int expert = plan.tile_expert[t];
+    const int row0 = plan.expert_offsets[expert] + (t * kTileM - plan.scale_row_offsets[expert]);
+    const int left = plan.expert_offsets[expert + 1] - row0;
+    const int valid = left < kTileM ? left : kTileM;
+    // all of a thread's loads are issued before the first is used: six 16-byte pieces at most
+    const uint4* source = reinterpret_cast<const uint4*>(staged + static_cast<size_t>(row0) * groups);
+    constexpr int kPieces = (kTileM * (groups / 16) + 255) / 256;
+    uint4 piece[kPieces];
+#pragma unroll
+    for (int j = 0; j < kPieces; ++j) {
+      const int i = threadIdx.x + j * 256;
+      piece[j] = i < valid * (groups / 16) ? __ldg(source + i) : make_uint4(0u, 0u, 0u, 0u);
     }
-    const int row_in_expert = row - expert_offsets[lo];
-    const uint32_t value = reinterpret_cast<const uint32_t*>(staged + static_cast<size_t>(row) * groups)[word];
-    *reinterpret_cast<uint32_t*>(scales + static_cast<size_t>(scale_row_offsets[lo]) * groups +
-                                 sf_offset(row_in_expert, 4 * word, groups)) = value;
+#pragma unroll
+    for (int j = 0; j < kPieces; ++j) {
+      const int i = threadIdx.x + j * 256;
+      if (i < valid * (groups / 16)) {
+        const int row = i / (groups / 16), first = 4 * (i % (groups / 16));
+        tile[row][first] = piece[j].x;
+        tile[row][first + 1] = piece[j].y;
+        tile[row][first + 2] = piece[j].z;
+        tile[row][first + 3] = piece[j].w;
+      }
+    }
+    __syncthreads();
+    uint4* out = reinterpret_cast<uint4*>(scales + static_cast<size_t>(t) * kTileM * groups);
+#pragma unroll 2
+    for (int i = threadIdx.x; i < words * 32; i += 256) {
+      const int word = i >> 5, q = i & 31;
+      uint4 v;
+      v.x = q < valid ? tile[q][word] : 0u;
+      v.y = q + 32 < valid ? tile[q + 32][word] : 0u;
+      v.z = q + 64 < valid ? tile[q + 64][word] : 0u;
+      v.w = q + 96 < valid ? tile[q + 96][word] : 0u;
+      out[word * 32 + q] = v;
+    }
+    __syncthreads();
   }
 }
 
@@ -597,21 +632,20 @@ int gevva_moe_ep_barrier(gevva_moe_ep* ep, gevva_stream_t stream) {
 int gevva_moe_ep_route_sort(gevva_moe_ep* ep, const int* ids, int tokens, gevva_stream_t stream) {
   if (!ep || !ids || tokens < 1 || tokens > ep->max_tokens) return GEVVA_MOE_BAD_ARGUMENT;
   gv::launch_route_sort(ids, tokens * kTopK, ep->send_plan, stream);
-  gv::ep_publish_counts_kernel<<<1, kExperts, 0, stream>>>(ep->dev, ep->send_plan);
+  gv::ep_exchange_kernel<<<1, kExperts, 0, stream>>>(ep->dev, ep->send_plan, ep->receive_plan, ep->split,
+                                                      ep->chunks, ++ep->epoch, ep->send_plan.status);
   return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;
 }
 
 int gevva_moe_ep_dispatch(gevva_moe_ep* ep, const void* in, const int* ids, int tokens,
                           gevva_stream_t stream) {
   if (!ep || !in || !ids || tokens < 1 || tokens > ep->max_tokens) return GEVVA_MOE_BAD_ARGUMENT;
-  gv::ep_send_bases_kernel<<<1, kExperts, 0, stream>>>(ep->dev);
   gv::ep_dispatch_kernel<<<(tokens + gv::kDispatchTokensPerBlock - 1) / gv::kDispatchTokensPerBlock,
                           gv::kDispatchThreads, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(in), ids, ep->in_scale_q1_global, ep->dev, ep->send_plan, tokens);
-  // The receive-side geometry and the combine address table depend on the count matrix only,
-  // so they are computed here, while other ranks' rows are still arriving, rather than after
-  // the barrier that precedes gevva_moe_ep_compute.
-  gv::ep_receive_plan_kernel<<<1, kExperts, 0, stream>>>(ep->dev, ep->receive_plan, ep->split, ep->chunks);
+  // The combine address table depends on the count matrix only, so it is computed here, while
+  // other ranks' rows are still arriving, rather than after the barrier that precedes
+  // gevva_moe_ep_compute.
   gv::ep_row_destinations_kernel<<<ep->sm_count * 2, 256, 0, stream>>>(ep->dev, ep->receive_plan,
                                                                         ep->row_dest);
   return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;

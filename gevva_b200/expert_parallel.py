@@ -156,8 +156,8 @@ class ExpertParallelRunner:
         _check(route_weights, torch.float32, (tokens, TOP_K), "route_weights")
         _check(output, torch.bfloat16, (tokens, HIDDEN), "output")
         s = _stream_handle(stream)
+        # route sort + count exchange; the exchange carries the step's first cross-rank barrier
         self._call("gevva_moe_ep_route_sort", _ptr(expert_ids), tokens, s)
-        self._barrier(stream)
         self._call("gevva_moe_ep_dispatch", _ptr(input), _ptr(expert_ids), tokens, s)
         self._barrier(stream)
         self._call("gevva_moe_ep_compute", s)
@@ -166,25 +166,24 @@ class ExpertParallelRunner:
 
     def timed_step(self, input, expert_ids, route_weights, output, tokens):
         """One step with CUDA events between the phases; returns microseconds per phase
-        (barriers include waiting for the slowest rank)."""
-        names = ["route_sort", "barrier1", "dispatch", "barrier2", "compute", "barrier3", "reduce"]
+        (barriers include waiting for the slowest rank; `route_sort` includes the count exchange
+        and the flag barrier inside it)."""
+        names = ["route_sort", "dispatch", "barrier2", "compute", "barrier3", "reduce"]
         events = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
         s = _stream_handle(None)
         events[0].record()
         self._call("gevva_moe_ep_route_sort", _ptr(expert_ids), tokens, s)
         events[1].record()
-        self._barrier()
-        events[2].record()
         self._call("gevva_moe_ep_dispatch", _ptr(input), _ptr(expert_ids), tokens, s)
+        events[2].record()
+        self._barrier()
         events[3].record()
-        self._barrier()
-        events[4].record()
         self._call("gevva_moe_ep_compute", s)
-        events[5].record()
+        events[4].record()
         self._barrier()
-        events[6].record()
+        events[5].record()
         self._call("gevva_moe_ep_reduce", _ptr(route_weights), _ptr(output), tokens, s)
-        events[7].record()
+        events[6].record()
         torch.cuda.synchronize()
         return {n: events[i].elapsed_time(events[i + 1]) * 1e3 for i, n in enumerate(names)}
 

@@ -157,12 +157,12 @@ def launches_per_step(world, tokens, sm_count=148, ep_chunks=2, ep_parts=1):
             return 1 + 1 + 1          # fused router; sort, quantiser and both expert GEMMs in one launch; reduce
         return 1 + sort + 1 + 3       # fused router; sort; quantise; w13, w2, reduce
     # fused router; sort + count exchange (with the first barrier inside); dispatch, row destinations;
-    # scale re-tiling + (w13, w2) per compute part; reduce; two flag barriers
+    # scale re-tiling (waits for every rank's rows) + (w13, w2) per compute part; reduce; one flag barrier
     # (the router once; everything else once per micro-batch in flight)
     if ep_parts > 1:
         share = (tokens + ep_parts - 1) // ep_parts
         sort = 1 if share * TOP_K <= 1024 or (share * TOP_K + 1023) // 1024 <= sm_count else 3
-    return 1 + ep_parts * ((sort + 1) + 2 + (1 + 2 * ep_chunks) + 1 + 2)
+    return 1 + ep_parts * ((sort + 1) + 2 + (1 + 2 * ep_chunks) + 1 + 1)
 
 
 def timed_loop(fn, steps):

@@ -302,12 +302,21 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ input, const int* __restric
 // memory, and written as the tile's 44 atoms of 512 bytes, 16 bytes (rows q, q+32, q+64, q+96
 // of one 4-group word) per thread.  Rows past the expert's end get scale zero.
 __global__ void __launch_bounds__(256)
-ep_swizzle_scales_kernel(const uint8_t* __restrict__ staged, EpDevice ep, RoutePlan plan,
-                         uint8_t* __restrict__ scales) {
+ep_swizzle_scales_kernel(const uint8_t* staged, EpDevice ep, RoutePlan plan, uint8_t* scales, int await_epoch,
+                         int* status) {
   constexpr int groups = kHidden / 16;
   constexpr int words = groups / 4;  // 44 per row
   __shared__ uint32_t tile[kTileM][words + 1];
-  (void)ep;
+  if (await_epoch) {
+    // The barrier between dispatch and compute: every rank announced, behind its dispatch kernel
+    // (ep_row_destinations_kernel), that its rows are in their owners' buffers.  `staged` is written
+    // by peers until this wait ends, so it is read with ordinary loads, after the wait.
+    if (threadIdx.x < ep.world) {
+      DeviceFlagPort port{ep, 0};
+      if (!ep_barrier_await(port, threadIdx.x, await_epoch)) atomicExch(status, static_cast<int>(kWaitTimeout));
+    }
+    __syncthreads();
+  }
   const int tiles = plan.num_m_tiles[0];
   for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
     const int expert = plan.tile_expert[t];
@@ -321,7 +330,7 @@ ep_swizzle_scales_kernel(const uint8_t* __restrict__ staged, EpDevice ep, RouteP
 #pragma unroll
     for (int j = 0; j < kPieces; ++j) {
       const int i = threadIdx.x + j * 256;
-      piece[j] = i < valid * (groups / 16) ? __ldg(source + i) : make_uint4(0u, 0u, 0u, 0u);
+      piece[j] = i < valid * (groups / 16) ? source[i] : make_uint4(0u, 0u, 0u, 0u);
     }
 #pragma unroll
     for (int j = 0; j < kPieces; ++j) {
@@ -355,7 +364,15 @@ ep_swizzle_scales_kernel(const uint8_t* __restrict__ staged, EpDevice ep, RouteP
 // source's own sorted position.  The w2 GEMM epilogue stores through these addresses, so
 // results cross NVLink while the GEMM is still running and never touch local memory.
 __global__ void __launch_bounds__(256)
-ep_row_destinations_kernel(EpDevice ep, RoutePlan plan, unsigned long long* __restrict__ row_dest) {
+ep_row_destinations_kernel(EpDevice ep, RoutePlan plan, unsigned long long* __restrict__ row_dest,
+                           int announce_epoch) {
+  if (announce_epoch && blockIdx.x == 0 && threadIdx.x < ep.world) {
+    // This launch follows the dispatch kernel in its stream, so this rank's rows are in their
+    // owners' buffers: say so to every rank (first half of the barrier before compute; the
+    // scale re-tiling kernel of the compute phase waits for all ranks' announcements).
+    DeviceFlagPort port{ep, 0};
+    ep_barrier_announce(port, ep.rank, threadIdx.x, announce_epoch);
+  }
   // the three small tables every row consults, in shared memory: a row's search is a chain of
   // dependent loads
   __shared__ int expert_offsets[kExperts + 1];
@@ -429,6 +446,7 @@ struct gevva_moe_ep {
   size_t capacity_rows = 0;
   int sm_count = 0;
   int epoch = 0;
+  int dispatch_epoch = 0;  // epoch announced by the last gevva_moe_ep_dispatch, awaited by gevva_moe_ep_compute
   // owned device memory
   int* ints = nullptr;
   uint8_t* input_sf = nullptr;
@@ -646,18 +664,19 @@ int gevva_moe_ep_dispatch(gevva_moe_ep* ep, const void* in, const int* ids, int 
   // The combine address table depends on the count matrix only, so it is computed here, while
   // other ranks' rows are still arriving, rather than after the barrier that precedes
   // gevva_moe_ep_compute.
-  gv::ep_row_destinations_kernel<<<ep->sm_count * 2, 256, 0, stream>>>(ep->dev, ep->receive_plan,
-                                                                        ep->row_dest);
+  ep->dispatch_epoch = ++ep->epoch;
+  gv::ep_row_destinations_kernel<<<ep->sm_count * 2, 256, 0, stream>>>(ep->dev, ep->receive_plan, ep->row_dest,
+                                                                        ep->dispatch_epoch);
   return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;
 }
 
 namespace {
-int run_compute(gevva_moe_ep* ep, const unsigned long long* row_dest, cudaStream_t stream);
+int run_compute(gevva_moe_ep* ep, const unsigned long long* row_dest, cudaStream_t stream, int await_epoch);
 }
 
 int gevva_moe_ep_compute(gevva_moe_ep* ep, gevva_stream_t stream) {
   if (!ep) return GEVVA_MOE_BAD_ARGUMENT;
-  return run_compute(ep, ep->row_dest, stream);
+  return run_compute(ep, ep->row_dest, stream, ep->dispatch_epoch);
 }
 
 int gevva_moe_ep_compute_local(gevva_moe_ep* ep, gevva_stream_t stream) {
@@ -668,7 +687,7 @@ int gevva_moe_ep_compute_local(gevva_moe_ep* ep, gevva_stream_t stream) {
     return GEVVA_MOE_CUDA_ERROR;
   gv::ep_row_destinations_local_kernel<<<ep->sm_count * 2, 256, 0, stream>>>(
       ep->dev, ep->receive_plan, ep->row_dest_local, ep->max_tokens * kTopK);
-  return run_compute(ep, ep->row_dest_local, stream);
+  return run_compute(ep, ep->row_dest_local, stream, 0);
 }
 
 int gevva_moe_ep_dispatch_local(gevva_moe_ep* ep, const void* in, const int* ids, int tokens,
@@ -688,11 +707,12 @@ int gevva_moe_ep_dispatch_local(gevva_moe_ep* ep, const void* in, const int* ids
 }  // extern "C"
 
 namespace {
-int run_compute(gevva_moe_ep* ep, const unsigned long long* row_dest, cudaStream_t stream) {
+int run_compute(gevva_moe_ep* ep, const unsigned long long* row_dest, cudaStream_t stream, int await_epoch) {
   gv::GemmOperands w2 = ep->w2;
   w2.row_dest = row_dest;
   gv::ep_swizzle_scales_kernel<<<ep->sm_count * 4, 256, 0, stream>>>(
-      ep->dev.peer_scales[ep->dev.rank], ep->dev, ep->receive_plan, ep->input_sf);
+      ep->dev.peer_scales[ep->dev.rank], ep->dev, ep->receive_plan, ep->input_sf, await_epoch,
+      ep->send_plan.status);
   // The local experts are processed in `chunks` parts of about equal rows.  A part's w2
   // is bound by the NVLink stores of its epilogue, not by the tensor pipe, so it runs on 64 SMs
   // of a side stream while the next part's w13 takes the other SMs; the first w13 and the

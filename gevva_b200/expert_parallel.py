@@ -158,17 +158,17 @@ class ExpertParallelRunner:
         s = _stream_handle(stream)
         # route sort + count exchange; the exchange carries the step's first cross-rank barrier
         self._call("gevva_moe_ep_route_sort", _ptr(expert_ids), tokens, s)
+        # dispatch ends by announcing its rows; compute starts by waiting for every rank's
         self._call("gevva_moe_ep_dispatch", _ptr(input), _ptr(expert_ids), tokens, s)
-        self._barrier(stream)
         self._call("gevva_moe_ep_compute", s)
         self._barrier(stream)
         self._call("gevva_moe_ep_reduce", _ptr(route_weights), _ptr(output), tokens, s)
 
     def timed_step(self, input, expert_ids, route_weights, output, tokens):
         """One step with CUDA events between the phases; returns microseconds per phase
-        (barriers include waiting for the slowest rank; `route_sort` includes the count exchange
-        and the flag barrier inside it)."""
-        names = ["route_sort", "dispatch", "barrier2", "compute", "barrier3", "reduce"]
+        (`route_sort` includes the count exchange and the flag barrier inside it, `compute` the
+        wait for every rank's dispatched rows; both include waiting for the slowest rank)."""
+        names = ["route_sort", "dispatch", "compute", "barrier", "reduce"]
         events = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
         s = _stream_handle(None)
         events[0].record()
@@ -176,14 +176,12 @@ class ExpertParallelRunner:
         events[1].record()
         self._call("gevva_moe_ep_dispatch", _ptr(input), _ptr(expert_ids), tokens, s)
         events[2].record()
-        self._barrier()
-        events[3].record()
         self._call("gevva_moe_ep_compute", s)
-        events[4].record()
+        events[3].record()
         self._barrier()
-        events[5].record()
+        events[4].record()
         self._call("gevva_moe_ep_reduce", _ptr(route_weights), _ptr(output), tokens, s)
-        events[6].record()
+        events[5].record()
         torch.cuda.synchronize()
         return {n: events[i].elapsed_time(events[i + 1]) * 1e3 for i, n in enumerate(names)}
 

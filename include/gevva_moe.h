@@ -214,13 +214,15 @@ int gevva_moe_route_sort_noalloc(const int* expert_ids, int tokens, int* sorted_
  * index e / world); each rank routes its own tokens, stores the quantised rows straight
  * into the owning rank's operand buffers over NVLink, runs the two grouped GEMMs for its
  * experts and stores result rows back into the source rank's combine buffer.  One step is
- * four calls, the last three separated by a cross-rank barrier (gevva_moe_ep_barrier or any
- * stream-ordered collective):
- *   gevva_moe_ep_route_sort | gevva_moe_ep_dispatch | barrier |
- *   gevva_moe_ep_compute    | barrier | gevva_moe_ep_reduce
- * gevva_moe_ep_route_sort ends with the exchange of the per-expert route counts, which
- * contains the step's first barrier (the flags and the bounded wait of gevva_moe_ep_barrier):
- * every rank must call it once per step, and a rank's dispatch may follow at once.
+ * four calls and one cross-rank barrier (gevva_moe_ep_barrier or any stream-ordered
+ * collective):
+ *   gevva_moe_ep_route_sort | gevva_moe_ep_dispatch | gevva_moe_ep_compute | barrier |
+ *   gevva_moe_ep_reduce
+ * The other two barriers a step needs are inside the calls (the flags and the bounded wait of
+ * gevva_moe_ep_barrier): gevva_moe_ep_route_sort ends with the exchange of the per-expert route
+ * counts and waits for every rank's; gevva_moe_ep_dispatch ends by announcing that this rank's
+ * rows are stored and gevva_moe_ep_compute starts by waiting for every rank's announcement.
+ * Every rank must make the same calls in the same order.
  * The peer-writable buffers are allocated by the caller (e.g. symmetric memory) with the
  * same sizes on every rank and passed as host arrays of `world` device pointers:
  *   peer_counts      i32 [world*128]

@@ -564,6 +564,34 @@ def ep_record(layer, world, rank, device, tokens_per_gpu, placement_kind, steps,
     return record
 
 
+def ep_one_rank(layer, batches, device, steps):
+    """For a profiler (which must not wrap a multi-rank command): the expert-parallel step with a
+    process group of one rank, i.e. the whole protocol (count exchange, dispatch, compute in two
+    halves, barrier, reduce) with every store staying on this GPU.  The result must be the plain
+    runner's, bit for bit."""
+    import torch
+    import torch.distributed as dist
+    from gevva_b200.expert_parallel import ExpertParallelRunner, local_expert_weights
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
+    ep = ExpertParallelRunner(local_expert_weights(layer.weights, 0, 1), layer.weights.in_scale_q1, TOKENS)
+    x = batches[0]
+    weights, ids = layer.route(x)
+    want, got = torch.empty_like(x), torch.empty_like(x)
+    layer.runner.launch_batch(x, ids, weights, want, TOKENS)
+    for _ in range(steps):
+        ep.launch_batch(x, ids, weights, got, TOKENS)
+    status, _ = ep.status()
+    if status != 0 or not torch.equal(got, want):
+        raise RuntimeError(f"one-rank expert-parallel step: status {status}, equal {torch.equal(got, want)}")
+    phases = [ep.timed_step(x, ids, weights, got, TOKENS) for _ in range(4)]
+    print(json.dumps({"ep_one_rank_phases_us": {k: sum(p[k] for p in phases[1:]) / 3 for k in phases[0]}}), flush=True)
+    del ep
+    dist.destroy_process_group()
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -588,6 +616,11 @@ def run_gpu(args):
         decode_eager(layer, device, args.profile_decode, 6)
         if rank == 0:
             print(json.dumps({"profile_decode_tokens": args.profile_decode, "steps": 6}), flush=True)
+        return
+    if args.profile_ep_one_rank:
+        ep_one_rank(layer, batches, device, 8)
+        if rank == 0:
+            print(json.dumps({"profile_ep_one_rank": True, "steps": 8}), flush=True)
         return
     x = batches[0]
     out = torch.empty_like(x)
@@ -859,6 +892,8 @@ def main():
                         help="skip timing the library NVFP4 GEMM that is reported beside the roofline")
     parser.add_argument("--profile-decode", type=int, default=0, metavar="TOKENS",
                         help="run a few eager decode-sized layer steps of TOKENS tokens and exit (for ncu)")
+    parser.add_argument("--profile-ep-one-rank", action="store_true",
+                        help="for a profiler: eight expert-parallel steps with a process group of one rank")
     parser.add_argument("--steps", type=int, default=50)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])

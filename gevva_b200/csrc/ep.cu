@@ -106,15 +106,18 @@ __global__ void __launch_bounds__(32) ep_barrier_kernel(EpDevice ep, int epoch, 
 //   - send side: where this rank's rows land on their owners;
 //   - receive side: the group geometry of the local experts, the sorted position on each source
 //     of the first row it sends to each local expert, and the parts of the compute phase.
-// These were five launches (publish, barrier, send bases, receive plan; 19 us of kernels and
-// their gaps at one rank); as one they take about 8 us.
+// These were four launches (publish, barrier, send bases, receive plan: 19 us of kernels at one
+// rank, plus their gaps); as one kernel 14 us in the same serialised, cold-cache view, and the
+// step is 22 us shorter at two ranks.
 __global__ void __launch_bounds__(kExperts)
 ep_exchange_kernel(EpDevice ep, RoutePlan send_plan, RoutePlan plan, int* split, int chunks, int epoch,
                    int* status) {
   __shared__ int counts[kMaxWorld][kExperts];
-  __shared__ int totals[kExperts];
+  __shared__ int prefix[kMaxWorld + 2][kExperts];   // exclusive sums over the sort keys
+  __shared__ int warp_sums[4][kMaxWorld + 2];
   __shared__ int scan_scratch[16];
   __shared__ int first_tile[kExperts + 1];
+  __shared__ int cuts[kMaxComputeChunks];
   const int v = threadIdx.x;
   const int le = threadIdx.x;
   const int el = ep.local_experts;
@@ -131,59 +134,82 @@ ep_exchange_kernel(EpDevice ep, RoutePlan send_plan, RoutePlan plan, int* split,
   }
   __syncthreads();
   int total = 0;
-  for (int s = 0; s < ep.world; ++s) {
-    const int c = ep.counts[s * kExperts + v];
+  int values[kMaxWorld + 2];
+#pragma unroll
+  for (int s = 0; s < kMaxWorld; ++s) {
+    const int c = s < ep.world ? ep.counts[s * kExperts + v] : 0;
     counts[s][v] = c;
+    values[s] = c;
     total += c;
   }
-  totals[v] = total;
+  values[kMaxWorld] = total;
+  values[kMaxWorld + 1] = (total + kTileM - 1) / kTileM * kTileM;
+  // Exclusive prefix sums over the 128 sort keys of all ten series at once (each source's counts,
+  // the totals, the totals padded to whole tiles): warp scans, then the warps' sums.
+  {
+    const int lane = v & 31, warp = v >> 5;
+    int inclusive[kMaxWorld + 2];
+#pragma unroll
+    for (int i = 0; i < kMaxWorld + 2; ++i) {
+      int x = values[i];
+#pragma unroll
+      for (int offset = 1; offset < 32; offset <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, x, offset);
+        if (lane >= offset) x += y;
+      }
+      inclusive[i] = x;
+      if (lane == 31) warp_sums[warp][i] = x;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < kMaxWorld + 2; ++i) {
+      int base = 0;
+      for (int w = 0; w < warp; ++w) base += warp_sums[w][i];
+      prefix[i][v] = base + inclusive[i] - values[i];
+    }
+  }
   __syncthreads();
-  // send side
+  // send side: rows of the owner's earlier experts, then rows of earlier sources for this expert
   {
     const int owner_first = (v / el) * el;
-    int expert_base = 0, scale_rows = 0, src_prefix = 0;
-    for (int u = owner_first; u < v; ++u) {
-      expert_base += totals[u];
-      scale_rows += (totals[u] + kTileM - 1) / kTileM * kTileM;
-    }
+    int src_prefix = 0;
     for (int s = 0; s < ep.rank; ++s) src_prefix += counts[s][v];
-    ep.send_row_base[v] = expert_base + src_prefix;
+    ep.send_row_base[v] = prefix[kMaxWorld][v] - prefix[kMaxWorld][owner_first] + src_prefix;
     ep.send_src_prefix[v] = src_prefix;
-    ep.send_scale_rows[v] = scale_rows;
+    ep.send_scale_rows[v] = prefix[kMaxWorld + 1][v] - prefix[kMaxWorld + 1][owner_first];
   }
   // receive side
-  const int count = le < el ? totals[ep.rank * el + le] : 0;
-  publish_groups(count, 0, plan, scan_scratch);
+  int local_count = 0;
+  if (le < el)
+    for (int s = 0; s < ep.world; ++s) local_count += counts[s][ep.rank * el + le];
+  publish_groups(local_count, 0, plan, scan_scratch);
   // sorted position, on source rank s, of the first row it sent to local expert le
   for (int index = threadIdx.x; index < ep.world * el; index += kExperts) {
     const int s = index / el, e = index % el;
-    const int key = ep.rank * el + e;
-    int offset = 0;
-    for (int u = 0; u < key; ++u) offset += counts[s][u];
-    ep.source_offsets[index] = offset;
+    ep.source_offsets[index] = prefix[s][ep.rank * el + e];
   }
-  // `chunks` parts of the tile list, cut at expert boundaries near equal shares:
-  // split = {first tile, tile count} of each part.  Thread 0 walks the experts' first tiles,
-  // which publish_groups has just written, from a copy in shared memory.
+  // `chunks` parts of the tile list, cut at expert boundaries near equal shares: part p ends at
+  // the first expert (after the first) whose first tile t satisfies chunks * t >= (p + 1) * tiles,
+  // or at the end.  First tiles are non-decreasing, so the expert that is the cut of a part knows
+  // it from its own value and its predecessor's.
   __syncthreads();
   first_tile[le] = plan.scale_row_offsets[le] / kTileM;
   if (le == 0) first_tile[kExperts] = plan.scale_row_offsets[kExperts] / kTileM;
+  if (le < kMaxComputeChunks) cuts[le] = -1;
+  __syncthreads();
+  const int all_tiles = first_tile[kExperts];
+  if (le >= 1 && le < el) {
+    for (int part = 0; part + 1 < chunks; ++part) {
+      const bool here = chunks * first_tile[le] >= (part + 1) * all_tiles;
+      const bool before = le >= 2 && chunks * first_tile[le - 1] >= (part + 1) * all_tiles;
+      if (here && !before) cuts[part] = first_tile[le];
+    }
+  }
   __syncthreads();
   if (threadIdx.x == 0) {
-    const int all_tiles = first_tile[kExperts];
     int first = 0;
-    int expert = 1;
     for (int part = 0; part < chunks; ++part) {
-      int cut = all_tiles;
-      if (part + 1 < chunks) {
-        for (; expert < el; ++expert) {
-          const int begin = first_tile[expert];
-          if (chunks * begin >= (part + 1) * all_tiles) {
-            cut = begin;
-            break;
-          }
-        }
-      }
+      const int cut = part + 1 < chunks && cuts[part] >= 0 ? cuts[part] : all_tiles;
       split[2 * part] = first;
       split[2 * part + 1] = cut - first;
       first = cut;

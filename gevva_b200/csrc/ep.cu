@@ -399,35 +399,27 @@ ep_row_destinations_kernel(EpDevice ep, RoutePlan plan, unsigned long long* __re
     DeviceFlagPort port{ep, 0};
     ep_barrier_announce(port, ep.rank, threadIdx.x, announce_epoch);
   }
-  // the three small tables every row consults, in shared memory: a row's search is a chain of
-  // dependent loads
-  __shared__ int expert_offsets[kExperts + 1];
-  __shared__ int local_counts[kExperts];    // [source][local expert]
-  __shared__ int source_offsets[kExperts];  // [source][local expert]
+  // (The small tables a row consults stay in global memory: after the first touch they are L1
+  // hits, and staging them in shared memory first made this launch 2 us longer.)
   const int el = ep.local_experts;
-  for (int i = threadIdx.x; i <= kExperts; i += blockDim.x) expert_offsets[i] = plan.expert_offsets[i];
-  for (int i = threadIdx.x; i < ep.world * el; i += blockDim.x) {
-    local_counts[i] = ep.counts[(i / el) * kExperts + ep.rank * el + i % el];
-    source_offsets[i] = ep.source_offsets[i];
-  }
-  __syncthreads();
-  const int total = expert_offsets[kExperts];
+  const int total = plan.expert_offsets[kExperts];
   for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < total; row += gridDim.x * blockDim.x) {
     // local expert of this row: the last le with expert_offsets[le] <= row
     int lo = 0, hi = el - 1;
     while (lo < hi) {
       const int mid = (lo + hi + 1) >> 1;
-      if (expert_offsets[mid] <= row) lo = mid; else hi = mid - 1;
+      if (plan.expert_offsets[mid] <= row) lo = mid; else hi = mid - 1;
     }
     const int le = lo;
-    int within = row - expert_offsets[le];
+    int within = row - plan.expert_offsets[le];
+    const int v = ep.rank * el + le;
     int s = 0;
     for (; s < ep.world - 1; ++s) {
-      const int c = local_counts[s * el + le];
+      const int c = ep.counts[s * kExperts + v];
       if (within < c) break;
       within -= c;
     }
-    const int dst_row = source_offsets[s * el + le] + within;
+    const int dst_row = ep.source_offsets[s * el + le] + within;
     row_dest[row] = reinterpret_cast<unsigned long long>(ep.peer_combine[s] +
                                                          static_cast<size_t>(dst_row) * kHidden);
   }

@@ -252,13 +252,25 @@ route_sort_fused_kernel(const int* __restrict__ expert_ids, int routes, int chun
     plan.chunk_hist[blockIdx.x * kExperts + tid] = total;
   }
   if (!grid_barrier(plan.sync, chunks, plan.status)) return;
-  if (tid < kExperts) {
-    int before = 0, total = 0;
-    for (int c = 0; c < chunks; ++c) {
-      const int v = __ldcg(&plan.chunk_hist[c * kExperts + tid]);
-      if (c < static_cast<int>(blockIdx.x)) before += v;
-      total += v;
+  // All chunk histograms, 32 chunks at a time: the whole CTA fetches them in one round of loads
+  // (128 threads walking them chunk by chunk is a chain of trips to L2), then expert `tid` adds
+  // its column from shared memory.
+  __shared__ int fetched[32 * kExperts];
+  int before = 0, total = 0;
+  for (int first = 0; first < chunks; first += 32) {
+    const int count = chunks - first < 32 ? chunks - first : 32;
+    for (int i = tid; i < count * kExperts; i += kSortChunk) fetched[i] = __ldcg(&plan.chunk_hist[first * kExperts + i]);
+    __syncthreads();
+    if (tid < kExperts) {
+      for (int c = 0; c < count; ++c) {
+        const int v = fetched[c * kExperts + tid];
+        if (first + c < static_cast<int>(blockIdx.x)) before += v;
+        total += v;
+      }
     }
+    __syncthreads();
+  }
+  if (tid < kExperts) {
     int running = publish_groups(total, routes, plan, scan_scratch) + before;
     for (int w = 0; w < 32; ++w) {
       const int c = warp_counts[w * kExperts + tid];

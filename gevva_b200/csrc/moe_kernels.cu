@@ -233,6 +233,7 @@ route_sort_fused_kernel(const int* __restrict__ expert_ids, int routes, int chun
   const int tid = threadIdx.x;
   for (int i = tid; i < 32 * kExperts; i += kSortChunk) warp_counts[i] = 0;
   __syncthreads();
+  grid_dependency_wait();  // the ids are written, and the plan's last readers are done
   const int route = blockIdx.x * kSortChunk + tid;
   int expert = kExperts;
   if (route < routes) {
@@ -314,10 +315,21 @@ void launch_route_sort(const int* expert_ids, int routes, const RoutePlan& plan,
   cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
   if (cudaStreamIsCapturing(stream, &capture) != cudaSuccess) capture = cudaStreamCaptureStatusActive;
   if (plan.sync != nullptr && chunks <= current_sm_count() && capture == cudaStreamCaptureStatusNone) {
-    RoutePlan plan_copy = plan;
-    void* args[] = {&expert_ids, &routes, &chunks, &plan_copy};
-    const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(route_sort_fused_kernel),
-                                                      dim3(chunks), dim3(kSortChunk), args, 0, stream);
+    // A cooperative launch (its CTAs meet at a grid barrier) that may also begin while the previous
+    // kernel of the stream is still running: the kernel clears its shared memory, then waits for
+    // that kernel at grid_dependency_wait before it reads the ids or writes the plan.
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(chunks);
+    config.blockDim = dim3(kSortChunk);
+    config.stream = stream;
+    cudaLaunchAttribute attribute[2];
+    attribute[0].id = cudaLaunchAttributeCooperative;
+    attribute[0].val.cooperative = 1;
+    attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 2;
+    const cudaError_t e = cudaLaunchKernelEx(&config, route_sort_fused_kernel, expert_ids, routes, chunks, plan);
     if (e == cudaSuccess) return;
     (void)cudaGetLastError();  // not launchable as one grid here: fall through to the three launches
   }

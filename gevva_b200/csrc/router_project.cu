@@ -148,7 +148,7 @@ route_project_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = smem->tmem_base;
-  grid_dependency_wait();  // a no-op unless launched behind a predecessor with programmatic serialization
+  grid_dependency_wait();  // the previous kernel of the stream has completed and its writes are visible
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -331,13 +331,18 @@ cudaError_t launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_w, c
   config.blockDim = dim3(kRpThreads);
   config.dynamicSmemBytes = kRpSmemBytes;
   config.stream = stream;
-  cudaLaunchAttribute attribute[1];
+  // Clusters of kSplit CTAs; and the launch may begin while the previous kernel of the stream is
+  // still running (the kernel waits at grid_dependency_wait before it reads or writes global memory),
+  // so that its set-up hides behind a predecessor that lets its dependents go early.
+  cudaLaunchAttribute attribute[2];
   attribute[0].id = cudaLaunchAttributeClusterDimension;
   attribute[0].val.clusterDim.x = kSplit;
   attribute[0].val.clusterDim.y = 1;
   attribute[0].val.clusterDim.z = 1;
+  attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
-  config.numAttrs = 1;
+  config.numAttrs = 2;
   return cudaLaunchKernelEx(&config, route_project_kernel<kFp8, kSplit>, map_x, map_w, p);
 }
 

@@ -87,6 +87,8 @@ struct DeviceFlagPort {
 };
 
 __global__ void __launch_bounds__(32) ep_barrier_kernel(EpDevice ep, int epoch, int* status) {
+  grid_launch_dependents();
+  grid_dependency_wait();  // the previous kernel of the stream has completed and its writes are visible
   const int lane = threadIdx.x;
   if (lane < ep.world) {
     DeviceFlagPort port{ep, 0};
@@ -118,6 +120,8 @@ ep_exchange_kernel(EpDevice ep, RoutePlan send_plan, RoutePlan plan, int* split,
   __shared__ int scan_scratch[16];
   __shared__ int first_tile[kExperts + 1];
   __shared__ int cuts[kMaxComputeChunks];
+  grid_launch_dependents();
+  grid_dependency_wait();  // the previous kernel of the stream has completed and its writes are visible
   const int v = threadIdx.x;
   const int le = threadIdx.x;
   const int el = ep.local_experts;
@@ -234,6 +238,8 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ input, const int* __restric
   __shared__ uint8_t* route_scales[kDispatchTokensPerBlock][kTopK];
   // one 176-byte scale row per route
   __shared__ __align__(16) uint16_t scale_rows[kDispatchTokensPerBlock][kTopK][groups / 2];
+  grid_launch_dependents();
+  grid_dependency_wait();  // the previous kernel of the stream has completed and its writes are visible
   if (threadIdx.x < kDispatchTokensPerBlock * kTopK) {
     const int slot = threadIdx.x / kTopK;
     const int k = threadIdx.x % kTopK;
@@ -333,6 +339,8 @@ ep_swizzle_scales_kernel(const uint8_t* staged, EpDevice ep, RoutePlan plan, uin
   constexpr int groups = kHidden / 16;
   constexpr int words = groups / 4;  // 44 per row
   __shared__ uint32_t tile[kTileM][words + 1];
+  grid_launch_dependents();
+  grid_dependency_wait();  // the previous kernel of the stream has completed and its writes are visible
   if (await_epoch) {
     // The barrier between dispatch and compute: every rank announced, behind its dispatch kernel
     // (ep_row_destinations_kernel), that its rows are in their owners' buffers.  `staged` is written
@@ -392,6 +400,8 @@ ep_swizzle_scales_kernel(const uint8_t* staged, EpDevice ep, RoutePlan plan, uin
 __global__ void __launch_bounds__(256)
 ep_row_destinations_kernel(EpDevice ep, RoutePlan plan, unsigned long long* __restrict__ row_dest,
                            int announce_epoch) {
+  grid_launch_dependents();
+  grid_dependency_wait();  // the previous kernel of the stream has completed and its writes are visible
   if (announce_epoch && blockIdx.x == 0 && threadIdx.x < ep.world) {
     // This launch follows the dispatch kernel in its stream, so this rank's rows are in their
     // owners' buffers: say so to every rank (first half of the barrier before compute; the
@@ -661,14 +671,14 @@ int gevva_moe_ep_create(gevva_moe_ep** out, const gevva_moe_weights* local_weigh
 
 int gevva_moe_ep_barrier(gevva_moe_ep* ep, gevva_stream_t stream) {
   if (!ep) return GEVVA_MOE_BAD_ARGUMENT;
-  gv::ep_barrier_kernel<<<1, 32, 0, stream>>>(ep->dev, ++ep->epoch, ep->send_plan.status);
+  gv::launch_chained(gv::ep_barrier_kernel, dim3(1), dim3(32), 0, stream, ep->dev, ++ep->epoch, ep->send_plan.status);
   return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;
 }
 
 int gevva_moe_ep_route_sort(gevva_moe_ep* ep, const int* ids, int tokens, gevva_stream_t stream) {
   if (!ep || !ids || tokens < 1 || tokens > ep->max_tokens) return GEVVA_MOE_BAD_ARGUMENT;
   gv::launch_route_sort(ids, tokens * kTopK, ep->send_plan, stream);
-  gv::ep_exchange_kernel<<<1, kExperts, 0, stream>>>(ep->dev, ep->send_plan, ep->receive_plan, ep->split,
+  gv::launch_chained(gv::ep_exchange_kernel, dim3(1), dim3(kExperts), 0, stream, ep->dev, ep->send_plan, ep->receive_plan, ep->split,
                                                       ep->chunks, ++ep->epoch, ep->send_plan.status);
   return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;
 }
@@ -676,14 +686,13 @@ int gevva_moe_ep_route_sort(gevva_moe_ep* ep, const int* ids, int tokens, gevva_
 int gevva_moe_ep_dispatch(gevva_moe_ep* ep, const void* in, const int* ids, int tokens,
                           gevva_stream_t stream) {
   if (!ep || !in || !ids || tokens < 1 || tokens > ep->max_tokens) return GEVVA_MOE_BAD_ARGUMENT;
-  gv::ep_dispatch_kernel<<<(tokens + gv::kDispatchTokensPerBlock - 1) / gv::kDispatchTokensPerBlock,
-                          gv::kDispatchThreads, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(in), ids, ep->in_scale_q1_global, ep->dev, ep->send_plan, tokens);
+  gv::launch_chained(gv::ep_dispatch_kernel, dim3((tokens + gv::kDispatchTokensPerBlock - 1) / gv::kDispatchTokensPerBlock),
+                     dim3(gv::kDispatchThreads), 0, stream, static_cast<const __nv_bfloat16*>(in), ids, ep->in_scale_q1_global, ep->dev, ep->send_plan, tokens);
   // The combine address table depends on the count matrix only, so it is computed here, while
   // other ranks' rows are still arriving, rather than after the barrier that precedes
   // gevva_moe_ep_compute.
   ep->dispatch_epoch = ++ep->epoch;
-  gv::ep_row_destinations_kernel<<<ep->sm_count * 2, 256, 0, stream>>>(ep->dev, ep->receive_plan, ep->row_dest,
+  gv::launch_chained(gv::ep_row_destinations_kernel, dim3(ep->sm_count * 2), dim3(256), 0, stream, ep->dev, ep->receive_plan, ep->row_dest,
                                                                         ep->dispatch_epoch);
   return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;
 }
@@ -716,9 +725,8 @@ int gevva_moe_ep_dispatch_local(gevva_moe_ep* ep, const void* in, const int* ids
     local.peer_codes[d] = ep->dev.peer_codes[ep->dev.rank];
     local.peer_scales[d] = ep->dev.peer_scales[ep->dev.rank];
   }
-  gv::ep_dispatch_kernel<<<(tokens + gv::kDispatchTokensPerBlock - 1) / gv::kDispatchTokensPerBlock,
-                          gv::kDispatchThreads, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(in), ids, ep->in_scale_q1_global, local, ep->send_plan, tokens);
+  gv::launch_chained(gv::ep_dispatch_kernel, dim3((tokens + gv::kDispatchTokensPerBlock - 1) / gv::kDispatchTokensPerBlock),
+                     dim3(gv::kDispatchThreads), 0, stream, static_cast<const __nv_bfloat16*>(in), ids, ep->in_scale_q1_global, local, ep->send_plan, tokens);
   return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;
 }
 
@@ -728,8 +736,8 @@ namespace {
 int run_compute(gevva_moe_ep* ep, const unsigned long long* row_dest, cudaStream_t stream, int await_epoch) {
   gv::GemmOperands w2 = ep->w2;
   w2.row_dest = row_dest;
-  gv::ep_swizzle_scales_kernel<<<ep->sm_count * 4, 256, 0, stream>>>(
-      ep->dev.peer_scales[ep->dev.rank], ep->dev, ep->receive_plan, ep->input_sf, await_epoch,
+  gv::launch_chained(gv::ep_swizzle_scales_kernel, dim3(ep->sm_count * 4), dim3(256), 0, stream,
+                     ep->dev.peer_scales[ep->dev.rank], ep->dev, ep->receive_plan, ep->input_sf, await_epoch,
       ep->send_plan.status);
   // The local experts are processed in `chunks` parts of about equal rows.  A part's w2
   // is bound by the NVLink stores of its epilogue, not by the tensor pipe, so it runs on 64 SMs

@@ -112,8 +112,8 @@ __global__ void __launch_bounds__(32) ep_barrier_kernel(EpDevice ep, int epoch, 
 // rank, plus their gaps); as one kernel 14 us in the same serialised, cold-cache view, and the
 // step is 22 us shorter at two ranks.
 __global__ void __launch_bounds__(kExperts)
-ep_exchange_kernel(EpDevice ep, RoutePlan send_plan, RoutePlan plan, int* split, int chunks, int epoch,
-                   int* status) {
+ep_exchange_kernel(EpDevice ep, RoutePlan send_plan, RoutePlan plan, int* split, int chunks, int first_share,
+                   int epoch, int* status) {
   __shared__ int counts[kMaxWorld][kExperts];
   __shared__ int prefix[kMaxWorld + 2][kExperts];   // exclusive sums over the sort keys
   __shared__ int warp_sums[4][kMaxWorld + 2];
@@ -204,8 +204,11 @@ ep_exchange_kernel(EpDevice ep, RoutePlan send_plan, RoutePlan plan, int* split,
   const int all_tiles = first_tile[kExperts];
   if (le >= 1 && le < el) {
     for (int part = 0; part + 1 < chunks; ++part) {
-      const bool here = chunks * first_tile[le] >= (part + 1) * all_tiles;
-      const bool before = le >= 2 && chunks * first_tile[le - 1] >= (part + 1) * all_tiles;
+      // with two parts the first takes `first_share` percent of the tiles (see gevva_moe_ep_create)
+      const int numerator = chunks == 2 ? first_share : 100 * (part + 1);
+      const int denominator = chunks == 2 ? 100 : 100 * chunks;
+      const bool here = denominator * first_tile[le] >= numerator * all_tiles;
+      const bool before = le >= 2 && denominator * first_tile[le - 1] >= numerator * all_tiles;
       if (here && !before) cuts[part] = first_tile[le];
     }
   }
@@ -487,6 +490,7 @@ struct gevva_moe_ep {
   // first half overlaps the w13 of the second: a side stream and two events order them
   int* split = nullptr;  // device [2 * chunks]: first tile and tile count of each part
   int chunks = 2;        // parts of the compute phase
+  int first_share = 50;  // percent of the row tiles in the first of two parts
   cudaStream_t side = nullptr;
   cudaEvent_t fork = nullptr, join = nullptr;
 };
@@ -546,6 +550,12 @@ int gevva_moe_ep_create(gevva_moe_ep** out, const gevva_moe_weights* local_weigh
   // two parts measured best at 2, 4 and 8 GPUs (four parts: 268 against 234 us of compute at
   // 2 GPUs, 383 against 332 us at 8)
   ep->chunks = 2;
+  // The first part's w13 runs with NVLink idle; afterwards the first part's result rows cross
+  // NVLink (W us for all rows) while the second part's w13 has 84 of 148 SMs.  Both end together
+  // when the first part is 176 / (W + 176) of the rows: W grows with the share of rows that
+  // leave the GPU, about 150, 220 and 260 us at 2, 4 and 8 ranks.
+  ep->first_share = world >= 8 ? 40 : world >= 4 ? 44 : world >= 2 ? 54 : 50;
+  if (const char* share = getenv("GEVVA_EP_FIRST_SHARE")) ep->first_share = atoi(share);
   ep->capacity_rows = config->recv_capacity_rows;
   ep->in_scale_q1_global = in_scale_q1_global;
   ep->dev.rank = rank;
@@ -679,7 +689,7 @@ int gevva_moe_ep_route_sort(gevva_moe_ep* ep, const int* ids, int tokens, gevva_
   if (!ep || !ids || tokens < 1 || tokens > ep->max_tokens) return GEVVA_MOE_BAD_ARGUMENT;
   gv::launch_route_sort(ids, tokens * kTopK, ep->send_plan, stream);
   gv::launch_chained(gv::ep_exchange_kernel, dim3(1), dim3(kExperts), 0, stream, ep->dev, ep->send_plan, ep->receive_plan, ep->split,
-                                                      ep->chunks, ++ep->epoch, ep->send_plan.status);
+                                                      ep->chunks, ep->first_share, ++ep->epoch, ep->send_plan.status);
   return cudaGetLastError() == cudaSuccess ? GEVVA_MOE_OK : GEVVA_MOE_CUDA_ERROR;
 }
 

@@ -2,8 +2,9 @@
 
 Given the all-gathered count matrix counts[s, v] (routes of source rank s for virtual expert
 v = owner * EL + local_expert), these functions say where every row goes; the CUDA kernels
-ep_send_bases_kernel / ep_receive_plan_kernel / ep_combine_kernel compute the same numbers.
-Used by the CPU (gloo) tests of the multi-rank path."""
+ep_exchange_kernel (send tables, receive tables, compute parts) and ep_row_destinations_kernel
+(combine destinations) compute the same numbers.  Used by the CPU (gloo) tests of the
+multi-rank path."""
 import numpy as np
 
 EXPERTS = 128
@@ -62,3 +63,29 @@ def combine_destination(counts, rank, row):
             return s, int(source_offsets[s, le] + within)
         within -= counts[s, v]
     raise ValueError("row beyond the received rows")
+
+
+def default_first_share(world):
+    """Percent of an owner's row tiles in the first of its two compute parts, as gevva_moe_ep_create
+    chooses it: the first part's result rows cross NVLink while the second part's w13 runs, and the
+    more ranks there are, the larger the share of rows that must cross."""
+    return 40 if world >= 8 else 44 if world >= 4 else 54 if world >= 2 else 50
+
+
+def compute_parts(counts, rank, first_share=None):
+    """The two parts of owner `rank`'s compute phase as (first tile, tile count) pairs: the tile
+    list is cut at the first local expert, after the first, whose first tile t satisfies
+    100 * t >= first_share * tiles; without such an expert the first part takes everything."""
+    world = counts.shape[0]
+    el = EXPERTS // world
+    share = default_first_share(world) if first_share is None else first_share
+    rows = counts[:, rank * el:(rank + 1) * el].sum(0)
+    tiles = (rows + TILE - 1) // TILE
+    first_tile = np.concatenate([[0], np.cumsum(tiles)])
+    total = int(first_tile[-1])
+    cut = total
+    for e in range(1, el):
+        if 100 * int(first_tile[e]) >= share * total:
+            cut = int(first_tile[e])
+            break
+    return [(0, cut), (cut, total - cut)]

@@ -95,3 +95,29 @@ def test_balanced_placement_is_a_permutation_and_balances():
         assert (ep_plan.remap(world, placement) == np.asarray(placement)).all()
         assert (ep_plan.remap(world) == np.asarray(strided_placement(world))).all()
 
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_compute_parts_cover_the_tiles_and_cut_at_an_expert(world):
+    """The two parts of the compute phase: together every tile once, the cut on an expert boundary,
+    the first part the smallest run of experts that reaches its share."""
+    from gevva_b200 import ep_plan
+    rng = np.random.default_rng(40 + world)
+    el = ep_plan.EXPERTS // world
+    for trial in range(20):
+        counts = rng.integers(0, 700, size=(world, ep_plan.EXPERTS))
+        if trial % 5 == 0:
+            counts[:, rng.integers(0, ep_plan.EXPERTS, size=40)] = 0   # experts without rows
+        for rank in range(world):
+            rows = counts[:, rank * el:(rank + 1) * el].sum(0)
+            tiles = (rows + 127) // 128
+            starts = np.concatenate([[0], np.cumsum(tiles)])
+            (a0, n0), (a1, n1) = ep_plan.compute_parts(counts, rank)
+            assert a0 == 0 and a1 == n0 and n0 + n1 == starts[-1]
+            assert n0 in set(starts.tolist())
+            share = ep_plan.default_first_share(world)
+            if n0 < starts[-1]:
+                assert 100 * n0 >= share * starts[-1]
+                earlier = [t for t in starts[1:el].tolist() if t < n0]
+                assert all(100 * t < share * starts[-1] for t in earlier)
+    assert [ep_plan.default_first_share(w) for w in (1, 2, 4, 8)] == [50, 54, 44, 40]
